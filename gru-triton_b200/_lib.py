@@ -1,0 +1,161 @@
+"""ctypes binding of ``libb200gru.so`` (the C ABI declared in ``include/b200gru.h``).
+
+The library is built in-tree by ``build.py``.  There is no fallback: if it is
+missing, or a call fails, an exception is raised.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+import threading
+from typing import Optional, Tuple
+
+import torch
+
+PKG_DIR = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.environ.get("B200GRU_LIB", os.path.join(PKG_DIR, "lib", "libb200gru.so"))
+
+KIND = {"dense": 0, "diagonal": 1, "monarch": 2, "butterfly": 3}
+Quant = Optional[Tuple[float, int, int]]
+
+
+class CQuant(ctypes.Structure):
+    _fields_ = [("scale", ctypes.c_float), ("qmin", ctypes.c_int), ("qmax", ctypes.c_int),
+                ("enabled", ctypes.c_int)]
+
+
+class CShape(ctypes.Structure):
+    _fields_ = [("kind", ctypes.c_int), ("T", ctypes.c_int), ("B", ctypes.c_int), ("H", ctypes.c_int),
+                ("nblocks", ctypes.c_int), ("log2_hpad", ctypes.c_int)]
+
+
+_P = ctypes.c_void_p
+_QP = ctypes.POINTER(CQuant)
+_SP = ctypes.POINTER(CShape)
+_I = ctypes.c_int
+_Z = ctypes.c_size_t
+
+# name -> (restype, argtypes); every symbol include/b200gru.h declares
+SIGNATURES = {
+    "b200gru_workspace_bytes": (_Z, [_SP, _I]),
+    "b200gru_save_bytes": (_Z, [_SP]),
+    "b200gru_scan_forward": (_I, [_SP, _P, _P, _P, _P, _QP, _QP, _P, _P, _P, _Z, _P]),
+    "b200gru_scan_backward": (_I, [_SP, _P, _P, _P, _P, _P, _P, _P, _QP, _QP, _P, _P, _P, _P, _P, _Z, _P]),
+    "b200gru_dense_forward": (_I, [_P, _P, _P, _P, _I, _I, _I, _QP, _QP, _P, _P, _P, _Z, _P]),
+    "b200gru_dense_backward": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _QP, _QP, _P, _P, _P, _P, _P, _Z, _P]),
+    "b200gru_diagonal_forward": (_I, [_P, _P, _P, _P, _I, _I, _I, _QP, _QP, _P, _P]),
+    "b200gru_diagonal_backward": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _QP, _QP, _P, _P, _P, _P, _P, _Z, _P]),
+    "b200gru_monarch_forward": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _QP, _QP, _P, _P, _P, _Z, _P]),
+    "b200gru_monarch_backward": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _QP, _QP, _P, _P, _P, _P, _P, _Z, _P]),
+    "b200gru_butterfly_forward": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _I, _QP, _QP, _P, _P, _P, _Z, _P]),
+    "b200gru_butterfly_backward": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _QP, _QP, _P, _P, _P, _P, _P, _Z, _P]),
+    "b200gru_launch_count": (ctypes.c_ulonglong, []),
+    "b200gru_strerror": (ctypes.c_char_p, [_I]),
+    "b200gru_last_cuda_error": (ctypes.c_char_p, []),
+    "b200gru_version": (_I, []),
+}
+
+_lock = threading.Lock()
+_lib = None
+
+
+def load() -> ctypes.CDLL:
+    """Load the shared library once and type its entry points."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    with _lock:
+        if _lib is None:
+            if not os.path.exists(LIB_PATH):
+                raise RuntimeError(
+                    f"CUDA library not found at {LIB_PATH}. Build it first: "
+                    "python gru-triton_b200/build.py  (there is no CPU or Triton fallback)")
+            lib = ctypes.CDLL(LIB_PATH)
+            for name, (res, args) in SIGNATURES.items():
+                fn = getattr(lib, name)
+                fn.restype, fn.argtypes = res, args
+            _lib = lib
+    return _lib
+
+
+def _cquant(q: Quant) -> CQuant:
+    if q is None:
+        return CQuant(1.0, 0, 0, 0)
+    scale, qmin, qmax = q
+    return CQuant(float(scale), int(qmin), int(qmax), 1)
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def _raise(rc: int, what: str):
+    lib = load()
+    msg = lib.b200gru_strerror(rc).decode()
+    detail = lib.b200gru_last_cuda_error().decode()
+    text = f"{what}: {msg}" + (f" ({detail})" if detail and rc == 3 else "")
+    raise (ValueError if rc == 1 else RuntimeError)(text)
+
+
+def make_shape(kind: str, T: int, B: int, H: int, nblocks: int = 1, log2_hpad: int = 0) -> CShape:
+    return CShape(KIND[kind], T, B, H, nblocks, log2_hpad)
+
+
+def _workspace(lib, shape: CShape, backward: int, device) -> Optional[torch.Tensor]:
+    n = lib.b200gru_workspace_bytes(ctypes.byref(shape), backward)
+    if n == ctypes.c_size_t(-1).value:
+        raise RuntimeError("shape not supported by the CUDA scan library")
+    return torch.empty(n, dtype=torch.uint8, device=device) if n else None
+
+
+def launch_count() -> int:
+    return int(load().b200gru_launch_count())
+
+
+def scan_forward(kind: str, gi, h0, W, bh, h_in_quant: Quant, h_out_quant: Quant, *, nblocks: int = 1,
+                 log2_hpad: int = 0, want_save: bool = False):
+    """Run the forward scan on the current stream of ``gi``'s device.
+    Returns ``(out, save)``; ``save`` is None unless asked for (and the kind has one)."""
+    lib = load()
+    T, B, _ = gi.shape
+    H = h0.shape[1]
+    shape = make_shape(kind, T, B, H, nblocks, log2_hpad)
+    out = torch.empty((T, B, H), device=gi.device, dtype=torch.float32)
+    save = None
+    if want_save and kind != "diagonal":
+        save = torch.empty((4, T, B, H), device=gi.device, dtype=torch.float32)
+    ws = _workspace(lib, shape, 0, gi.device)
+    qi, qo = _cquant(h_in_quant), _cquant(h_out_quant)
+    with torch.cuda.device(gi.device):
+        stream = torch.cuda.current_stream().cuda_stream
+        rc = lib.b200gru_scan_forward(ctypes.byref(shape), _ptr(gi), _ptr(h0), _ptr(W), _ptr(bh),
+                                      ctypes.byref(qi), ctypes.byref(qo), _ptr(out), _ptr(save), _ptr(ws),
+                                      0 if ws is None else ws.numel(), ctypes.c_void_p(stream))
+    if rc:
+        _raise(rc, f"{kind} scan forward")
+    return out, save
+
+
+def scan_backward(kind: str, gi, h0, W, bh, out, dout, save, h_in_quant: Quant, h_out_quant: Quant, *,
+                  nblocks: int = 1, log2_hpad: int = 0):
+    """Run the backward scan.  Returns ``(dgi, dh0, dW, dbh)``."""
+    lib = load()
+    T, B, _ = gi.shape
+    H = h0.shape[1]
+    shape = make_shape(kind, T, B, H, nblocks, log2_hpad)
+    dgi = torch.empty_like(gi)
+    dh0 = torch.empty_like(h0)
+    dW = torch.empty_like(W)
+    dbh = torch.empty_like(bh)
+    ws = _workspace(lib, shape, 1, gi.device)
+    qi, qo = _cquant(h_in_quant), _cquant(h_out_quant)
+    with torch.cuda.device(gi.device):
+        stream = torch.cuda.current_stream().cuda_stream
+        rc = lib.b200gru_scan_backward(ctypes.byref(shape), _ptr(gi), _ptr(h0), _ptr(W), _ptr(bh), _ptr(out),
+                                       _ptr(dout), _ptr(save), ctypes.byref(qi), ctypes.byref(qo), _ptr(dgi),
+                                       _ptr(dh0), _ptr(dW), _ptr(dbh), _ptr(ws),
+                                       0 if ws is None else ws.numel(), ctypes.c_void_p(stream))
+    if rc:
+        _raise(rc, f"{kind} scan backward")
+    return dgi, dh0, dW, dbh

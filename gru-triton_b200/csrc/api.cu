@@ -1,0 +1,359 @@
+// C ABI of the library: argument checks, workspace carving, kernel dispatch.
+// Nothing here allocates or synchronises; all work is enqueued on the caller's stream.
+
+#include <atomic>
+#include <cstdio>
+#include <cstring>
+
+#include "block_scan.cuh"
+#include "butterfly_scan.cuh"
+
+namespace b200gru {
+
+// diag_scan.cu
+size_t diag_bwd_workspace_bytes(int T, int B, int H);
+int diag_forward(const float* gi, const float* h0, const float* W, const float* bh, float* out, int T, int B,
+                 int H, Quant qi, Quant qo, cudaStream_t st);
+int diag_backward(const float* gi, const float* h0, const float* W, const float* bh, const float* out,
+                  const float* dout, float* dgi, float* dh0, float* dW, float* dbh, void* workspace, int T,
+                  int B, int H, Quant qi, Quant qo, cudaStream_t st);
+
+static std::atomic<unsigned long long> g_launches{0};
+static thread_local char g_last_error[256] = {0};
+
+void note_launch(int n) { g_launches.fetch_add((unsigned long long)n, std::memory_order_relaxed); }
+
+int check_launch(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e == cudaSuccess) return B200GRU_OK;
+  snprintf(g_last_error, sizeof(g_last_error), "%s: %s", what, cudaGetErrorString(e));
+  return B200GRU_LAUNCH_FAILURE;
+}
+
+__global__ void reduce_partials_kernel(const float* __restrict__ src, int nparts, size_t row_stride, size_t n,
+                                       float* __restrict__ dst) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float s = src[i];
+  for (int p = 1; p < nparts; ++p) s += src[(size_t)p * row_stride + i];
+  dst[i] = s;
+}
+
+void launch_reduce_partials(const float* src, int nparts, size_t row_stride, size_t n, float* dst,
+                            cudaStream_t st) {
+  const unsigned grid = (unsigned)((n + 255) / 256);
+  reduce_partials_kernel<<<grid, 256, 0, st>>>(src, nparts, row_stride, n, dst);
+  note_launch();
+}
+
+// ---------------------------------------------------------------------------
+
+struct Dims {
+  int kind, T, B, H, nb, Hb, logn, Hpad, nstages;
+  long long gate_stride, block_stride;
+  size_t w_elems;
+};
+
+static bool parse_shape(const b200gru_shape* s, Dims* d) {
+  if (s == nullptr) return false;
+  if (s->T <= 0 || s->B <= 0 || s->H <= 0) return false;
+  if ((long long)s->T * s->B > 0x7fffffffLL / 4) return false;     // flattened row index stays in int
+  d->kind = s->kind; d->T = s->T; d->B = s->B; d->H = s->H;
+  d->nb = 1; d->Hb = s->H; d->logn = 0; d->Hpad = s->H; d->nstages = 0;
+  switch (s->kind) {
+    case B200GRU_DENSE:
+      d->gate_stride = (long long)s->H * s->H; d->block_stride = 0;
+      d->w_elems = (size_t)3 * s->H * s->H;
+      return true;
+    case B200GRU_DIAGONAL:
+      d->gate_stride = s->H; d->block_stride = 0; d->w_elems = (size_t)3 * s->H;
+      return true;
+    case B200GRU_MONARCH:
+      if (s->nblocks <= 0 || s->H % s->nblocks != 0) return false;
+      d->nb = s->nblocks; d->Hb = s->H / s->nblocks;
+      d->gate_stride = (long long)d->nb * d->Hb * d->Hb; d->block_stride = (long long)d->Hb * d->Hb;
+      d->w_elems = (size_t)3 * d->nb * d->Hb * d->Hb;
+      return true;
+    case B200GRU_BUTTERFLY:
+      if (s->nblocks <= 0 || s->log2_hpad <= 0 || s->log2_hpad > 20) return false;
+      d->logn = s->log2_hpad; d->Hpad = 1 << s->log2_hpad;
+      if (d->Hpad < s->H) return false;
+      d->nb = s->nblocks; d->nstages = s->nblocks * s->log2_hpad;
+      d->w_elems = (size_t)3 * d->nstages * (d->Hpad / 2) * 4;
+      return true;
+    default:
+      return false;
+  }
+}
+
+static size_t s_bytes(const Dims& d) { return align_up((size_t)4 * d.T * d.B * d.H * sizeof(float), 256); }
+
+static size_t workspace_bytes(const Dims& d, int backward) {
+  switch (d.kind) {
+    case B200GRU_DENSE:
+    case B200GRU_MONARCH:
+      if (!backward) return align_up(d.w_elems * sizeof(float), 256);
+      return s_bytes(d) + weight_grads_scratch_bytes(d.T, d.B, d.H, d.nb, d.Hb);
+    case B200GRU_DIAGONAL:
+      return backward ? diag_bwd_workspace_bytes(d.T, d.B, d.H) : 0;
+    case B200GRU_BUTTERFLY: {
+      if (!backward) return 0;
+      const size_t w = bfly_wgrad_scratch_bytes(d.T, d.B, d.Hpad, d.nstages);
+      if (w == (size_t)-1) return (size_t)-1;
+      return s_bytes(d) + w + bias_grads_scratch_bytes(d.T, d.B, d.H);
+    }
+  }
+  return (size_t)-1;
+}
+
+static int fill_bfly(const Dims& d, BflyArgs* a) {
+  memset(a, 0, sizeof(*a));
+  a->T = d.T; a->B = d.B; a->H = d.H; a->Hpad = d.Hpad; a->logn = d.logn; a->nstages = d.nstages;
+  a->h0_rows = d.B;
+  a->npasses = build_bfly_passes(d.logn, d.nb, a->passes, BFLY_MAX_PASSES);
+  return a->npasses > 0 ? 0 : B200GRU_UNSUPPORTED;
+}
+
+}  // namespace b200gru
+
+using namespace b200gru;
+
+extern "C" {
+
+size_t b200gru_workspace_bytes(const b200gru_shape* shape, int backward) {
+  Dims d;
+  if (!parse_shape(shape, &d)) return (size_t)-1;
+  return workspace_bytes(d, backward);
+}
+
+size_t b200gru_save_bytes(const b200gru_shape* shape) {
+  Dims d;
+  if (!parse_shape(shape, &d)) return (size_t)-1;
+  if (d.kind == B200GRU_DIAGONAL) return 0;      // recompute is free for the elementwise kind
+  return (size_t)4 * d.T * d.B * d.H * sizeof(float);
+}
+
+int b200gru_scan_forward(const b200gru_shape* shape, const float* gi, const float* h0, const float* W,
+                         const float* bh, const b200gru_quant* q_in, const b200gru_quant* q_out, float* out,
+                         float* save, void* workspace, size_t workspace_bytes_, void* stream) {
+  Dims d;
+  if (!parse_shape(shape, &d)) return B200GRU_INVALID_ARGUMENT;
+  if (!gi || !h0 || !W || !bh || !out) return B200GRU_INVALID_ARGUMENT;
+  if (q_in && q_in->enabled && !(q_in->scale > 0.f)) return B200GRU_INVALID_ARGUMENT;
+  if (q_out && q_out->enabled && !(q_out->scale > 0.f)) return B200GRU_INVALID_ARGUMENT;
+  const size_t need = workspace_bytes(d, 0);
+  if (need == (size_t)-1) return B200GRU_UNSUPPORTED;
+  if (need > 0 && (workspace == nullptr || workspace_bytes_ < need)) return B200GRU_WORKSPACE_TOO_SMALL;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const Quant qi = make_quant(q_in), qo = make_quant(q_out);
+
+  switch (d.kind) {
+    case B200GRU_DIAGONAL:
+      return diag_forward(gi, h0, W, bh, out, d.T, d.B, d.H, qi, qo, st);
+    case B200GRU_DENSE:
+    case B200GRU_MONARCH: {
+      BlockScanConfig cfg;
+      if (!choose_block_config(true, d.B, d.Hb, d.nb, &cfg)) return B200GRU_UNSUPPORTED;
+      BlockScanArgs a;
+      memset(&a, 0, sizeof(a));
+      a.gi = gi; a.h0 = h0; a.W = W; a.bh = bh; a.out = out; a.save = save;
+      a.T = d.T; a.B = d.B; a.H = d.H; a.nb = d.nb; a.Hb = d.Hb;
+      a.w_gate_stride = d.gate_stride; a.w_block_stride = d.block_stride;
+      a.qin = qi; a.qout = qo;
+      if (!cfg.w_in_smem) {
+        float* Wt = static_cast<float*>(workspace);
+        int rc = launch_transpose_weights(W, Wt, d.nb, d.Hb, d.gate_stride, d.block_stride, st);
+        if (rc) return rc;
+        a.Wt = Wt;
+      }
+      return launch_block_scan(true, cfg, a, d.nb, st);
+    }
+    case B200GRU_BUTTERFLY: {
+      BflyArgs a;
+      int rc = fill_bfly(d, &a);
+      if (rc) return rc;
+      a.gi = gi; a.h0 = h0; a.h0_tail = h0; a.tw = W; a.bh = bh; a.out = out; a.save = save;
+      a.qin = qi; a.qout = qo;
+      return bfly_launch_forward(a, st);
+    }
+  }
+  return B200GRU_INVALID_ARGUMENT;
+}
+
+int b200gru_scan_backward(const b200gru_shape* shape, const float* gi, const float* h0, const float* W,
+                          const float* bh, const float* out, const float* dout, const float* save,
+                          const b200gru_quant* q_in, const b200gru_quant* q_out, float* dgi, float* dh0,
+                          float* dW, float* dbh, void* workspace, size_t workspace_bytes_, void* stream) {
+  Dims d;
+  if (!parse_shape(shape, &d)) return B200GRU_INVALID_ARGUMENT;
+  if (!gi || !h0 || !W || !bh || !out || !dout || !dgi || !dh0 || !dW || !dbh) return B200GRU_INVALID_ARGUMENT;
+  if (q_in && q_in->enabled && !(q_in->scale > 0.f)) return B200GRU_INVALID_ARGUMENT;
+  if (q_out && q_out->enabled && !(q_out->scale > 0.f)) return B200GRU_INVALID_ARGUMENT;
+  const size_t need = workspace_bytes(d, 1);
+  if (need == (size_t)-1) return B200GRU_UNSUPPORTED;
+  if (need > 0 && (workspace == nullptr || workspace_bytes_ < need)) return B200GRU_WORKSPACE_TOO_SMALL;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const Quant qi = make_quant(q_in), qo = make_quant(q_out);
+  char* ws = static_cast<char*>(workspace);
+
+  switch (d.kind) {
+    case B200GRU_DIAGONAL:
+      return diag_backward(gi, h0, W, bh, out, dout, dgi, dh0, dW, dbh, workspace, d.T, d.B, d.H, qi, qo, st);
+    case B200GRU_DENSE:
+    case B200GRU_MONARCH: {
+      float* S_ws = reinterpret_cast<float*>(ws);
+      float* scratch = reinterpret_cast<float*>(ws + s_bytes(d));
+      BlockGemmArgs g;
+      memset(&g, 0, sizeof(g));
+      g.gi = gi; g.h0 = h0; g.out = out; g.W = W; g.bh = bh; g.dgi = dgi;
+      g.dW = dW; g.dbh = dbh; g.partial = scratch;
+      g.T = d.T; g.B = d.B; g.H = d.H; g.nb = d.nb; g.Hb = d.Hb;
+      g.w_gate_stride = d.gate_stride; g.w_block_stride = d.block_stride; g.qin = qi;
+      const float* S = save;
+      if (S == nullptr) {
+        g.S = S_ws;
+        int rc = launch_recompute_gates(g, st);
+        if (rc) return rc;
+        S = S_ws;
+      }
+      BlockScanConfig cfg;
+      if (!choose_block_config(false, d.B, d.Hb, d.nb, &cfg)) return B200GRU_UNSUPPORTED;
+      BlockScanArgs a;
+      memset(&a, 0, sizeof(a));
+      a.gi = gi; a.h0 = h0; a.W = W; a.bh = bh; a.out = const_cast<float*>(out); a.S = S; a.dout = dout;
+      a.dgi = dgi; a.dh0 = dh0;
+      a.T = d.T; a.B = d.B; a.H = d.H; a.nb = d.nb; a.Hb = d.Hb;
+      a.w_gate_stride = d.gate_stride; a.w_block_stride = d.block_stride;
+      a.qin = qi; a.qout = qo;
+      int rc = launch_block_scan(false, cfg, a, d.nb, st);
+      if (rc) return rc;
+      g.S = const_cast<float*>(S);
+      return launch_weight_grads(g, st);
+    }
+    case B200GRU_BUTTERFLY: {
+      float* S_ws = reinterpret_cast<float*>(ws);
+      const size_t wg = bfly_wgrad_scratch_bytes(d.T, d.B, d.Hpad, d.nstages);
+      float* part_w = reinterpret_cast<float*>(ws + s_bytes(d));
+      float* part_b = reinterpret_cast<float*>(ws + s_bytes(d) + wg);
+      BflyArgs a;
+      int rc = fill_bfly(d, &a);
+      if (rc) return rc;
+      a.tw = W; a.bh = bh; a.qin = qi; a.qout = qo;
+      const float* S = save;
+      if (S == nullptr) {
+        // gate recompute: the forward kernel, teacher-forced over all T*B rows (T = 1)
+        BflyArgs p = a;
+        p.T = 1; p.B = d.T * d.B; p.h0_rows = d.B;
+        p.gi = gi; p.h0 = h0; p.h0_tail = out; p.out = nullptr; p.save = S_ws;
+        rc = bfly_launch_forward(p, st);
+        if (rc) return rc;
+        S = S_ws;
+      }
+      a.gi = gi; a.h0 = h0; a.S = S; a.dout = dout; a.out_c = out; a.dgi = dgi; a.dh0 = dh0;
+      rc = bfly_launch_backward(a, st);
+      if (rc) return rc;
+      a.dgi_c = dgi;
+      rc = bfly_launch_wgrad(a, part_w, dW, st);
+      if (rc) return rc;
+      return launch_bias_grads(dgi, S, part_b, dbh, d.T, d.B, d.H, st);
+    }
+  }
+  return B200GRU_INVALID_ARGUMENT;
+}
+
+// ---- per-kind conveniences ---------------------------------------------------
+
+static b200gru_shape mk_shape(int kind, int T, int B, int H, int nblocks, int log2_hpad) {
+  b200gru_shape s;
+  s.kind = kind; s.T = T; s.B = B; s.H = H; s.nblocks = nblocks; s.log2_hpad = log2_hpad;
+  return s;
+}
+
+int b200gru_dense_forward(const float* gi, const float* h0, const float* Wh_cat, const float* bh_cat, int T,
+                          int B, int H, const b200gru_quant* q_in, const b200gru_quant* q_out, float* out,
+                          float* save, void* workspace, size_t workspace_bytes_, void* stream) {
+  const b200gru_shape s = mk_shape(B200GRU_DENSE, T, B, H, 1, 0);
+  return b200gru_scan_forward(&s, gi, h0, Wh_cat, bh_cat, q_in, q_out, out, save, workspace, workspace_bytes_, stream);
+}
+
+int b200gru_dense_backward(const float* gi, const float* h0, const float* Wh_cat, const float* bh_cat,
+                           const float* out, const float* dout, const float* save, int T, int B, int H,
+                           const b200gru_quant* q_in, const b200gru_quant* q_out, float* dgi, float* dh0,
+                           float* dWh, float* dbh, void* workspace, size_t workspace_bytes_, void* stream) {
+  const b200gru_shape s = mk_shape(B200GRU_DENSE, T, B, H, 1, 0);
+  return b200gru_scan_backward(&s, gi, h0, Wh_cat, bh_cat, out, dout, save, q_in, q_out, dgi, dh0, dWh, dbh,
+                               workspace, workspace_bytes_, stream);
+}
+
+int b200gru_diagonal_forward(const float* gi, const float* h0, const float* Wh_diag, const float* bh_cat, int T,
+                             int B, int H, const b200gru_quant* q_in, const b200gru_quant* q_out, float* out,
+                             void* stream) {
+  const b200gru_shape s = mk_shape(B200GRU_DIAGONAL, T, B, H, 1, 0);
+  return b200gru_scan_forward(&s, gi, h0, Wh_diag, bh_cat, q_in, q_out, out, nullptr, nullptr, 0, stream);
+}
+
+int b200gru_diagonal_backward(const float* gi, const float* h0, const float* Wh_diag, const float* bh_cat,
+                              const float* out, const float* dout, int T, int B, int H,
+                              const b200gru_quant* q_in, const b200gru_quant* q_out, float* dgi, float* dh0,
+                              float* dWh_diag, float* dbh, void* workspace, size_t workspace_bytes_,
+                              void* stream) {
+  const b200gru_shape s = mk_shape(B200GRU_DIAGONAL, T, B, H, 1, 0);
+  return b200gru_scan_backward(&s, gi, h0, Wh_diag, bh_cat, out, dout, nullptr, q_in, q_out, dgi, dh0, dWh_diag,
+                               dbh, workspace, workspace_bytes_, stream);
+}
+
+int b200gru_monarch_forward(const float* gi, const float* h0, const float* Wh_struct, const float* bh_cat, int T,
+                            int B, int H, int nblocks, const b200gru_quant* q_in, const b200gru_quant* q_out,
+                            float* out, float* save, void* workspace, size_t workspace_bytes_, void* stream) {
+  const b200gru_shape s = mk_shape(B200GRU_MONARCH, T, B, H, nblocks, 0);
+  return b200gru_scan_forward(&s, gi, h0, Wh_struct, bh_cat, q_in, q_out, out, save, workspace, workspace_bytes_,
+                              stream);
+}
+
+int b200gru_monarch_backward(const float* gi, const float* h0, const float* Wh_struct, const float* bh_cat,
+                             const float* out, const float* dout, const float* save, int T, int B, int H,
+                             int nblocks, const b200gru_quant* q_in, const b200gru_quant* q_out, float* dgi,
+                             float* dh0, float* dWh_struct, float* dbh, void* workspace, size_t workspace_bytes_,
+                             void* stream) {
+  const b200gru_shape s = mk_shape(B200GRU_MONARCH, T, B, H, nblocks, 0);
+  return b200gru_scan_backward(&s, gi, h0, Wh_struct, bh_cat, out, dout, save, q_in, q_out, dgi, dh0, dWh_struct,
+                               dbh, workspace, workspace_bytes_, stream);
+}
+
+int b200gru_butterfly_forward(const float* gi, const float* h0, const float* twiddles, const float* bh_cat, int T,
+                              int B, int H, int nblocks, int log2_hpad, const b200gru_quant* q_in,
+                              const b200gru_quant* q_out, float* out, float* save, void* workspace,
+                              size_t workspace_bytes_, void* stream) {
+  const b200gru_shape s = mk_shape(B200GRU_BUTTERFLY, T, B, H, nblocks, log2_hpad);
+  return b200gru_scan_forward(&s, gi, h0, twiddles, bh_cat, q_in, q_out, out, save, workspace, workspace_bytes_,
+                              stream);
+}
+
+int b200gru_butterfly_backward(const float* gi, const float* h0, const float* twiddles, const float* bh_cat,
+                               const float* out, const float* dout, const float* save, int T, int B, int H,
+                               int nblocks, int log2_hpad, const b200gru_quant* q_in, const b200gru_quant* q_out,
+                               float* dgi, float* dh0, float* dtwiddles, float* dbh, void* workspace,
+                               size_t workspace_bytes_, void* stream) {
+  const b200gru_shape s = mk_shape(B200GRU_BUTTERFLY, T, B, H, nblocks, log2_hpad);
+  return b200gru_scan_backward(&s, gi, h0, twiddles, bh_cat, out, dout, save, q_in, q_out, dgi, dh0, dtwiddles,
+                               dbh, workspace, workspace_bytes_, stream);
+}
+
+unsigned long long b200gru_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+const char* b200gru_strerror(int status) {
+  switch (status) {
+    case B200GRU_OK: return "ok";
+    case B200GRU_INVALID_ARGUMENT: return "invalid argument";
+    case B200GRU_UNSUPPORTED: return "shape not supported by this build or device";
+    case B200GRU_LAUNCH_FAILURE: return "kernel launch failed";
+    case B200GRU_WORKSPACE_TOO_SMALL: return "workspace too small";
+    default: return "unknown status";
+  }
+}
+
+const char* b200gru_last_cuda_error(void) { return g_last_error; }
+
+int b200gru_version(void) { return 100; }
+
+}  // extern "C"

@@ -1,0 +1,331 @@
+// Off-chain (fully parallel) parts of the dense / block-diagonal scan.
+//
+// In the backward pass every h_t is already known, so two of the three matrix
+// products do not sit on the serial dependence chain and run as ordinary tiled
+// FP32 GEMMs over all T*B rows at once:
+//
+//   recompute_gates : gh = fq_in(h_{t-1}) @ W^T (+ bias) for every (t, b), fused with
+//                     the gate nonlinearities -> S = {r, z, n, gh_n}
+//                     (reference: in-kernel recompute, scan.py:389-432)
+//   weight_grads    : dW = dgh^T @ fq_in(h_{t-1}) summed over all (t, b), dbh = sum dgh
+//                     (reference: per-step load-add-store of a dWh partial, scan.py:573-616,
+//                      then partial.sum(0), scan.py:750-751)
+//
+// FP32 FMA keeps the 1e-5 / 1e-4 parity budget; reductions are split over row
+// ranges into partial buffers and summed in a fixed order (bitwise reproducible).
+
+#include "block_scan.cuh"
+#include "butterfly_scan.cuh"
+
+namespace b200gru {
+
+namespace {
+
+// previous hidden state of flattened row tb = t*B + b, column c
+__device__ __forceinline__ float h_prev_at(const float* __restrict__ h0, const float* __restrict__ out,
+                                           int tb, int B, int H, int c) {
+  return (tb < B) ? h0[(size_t)tb * H + c] : out[(size_t)(tb - B) * H + c];
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------------------
+// W(g,n,o,k) -> Wt[((n*Hb + k)*3 + g)*Hb + o]
+// ---------------------------------------------------------------------------
+__global__ void transpose_weights_kernel(const float* __restrict__ W, float* __restrict__ Wt, int nb,
+                                         int Hb, long long gs, long long bs) {
+  __shared__ float tile[32][33];
+  const int gn = blockIdx.z;                 // g * nb + n
+  const int g = gn / nb, n = gn - g * nb;
+  const int o0 = blockIdx.y * 32, k0 = blockIdx.x * 32;
+  const float* src = W + (size_t)g * gs + (size_t)n * bs;
+  for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+    const int o = o0 + r, k = k0 + threadIdx.x;
+    tile[r][threadIdx.x] = (o < Hb && k < Hb) ? src[(size_t)o * Hb + k] : 0.f;
+  }
+  __syncthreads();
+  for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+    const int k = k0 + r, o = o0 + threadIdx.x;
+    if (k < Hb && o < Hb) Wt[(((size_t)n * Hb + k) * 3 + g) * Hb + o] = tile[threadIdx.x][r];
+  }
+}
+
+int launch_transpose_weights(const float* W, float* Wt, int nb, int Hb, long long gs, long long bs,
+                             cudaStream_t st) {
+  dim3 grid(cdiv(Hb, 32), cdiv(Hb, 32), 3 * nb), block(32, 8);
+  transpose_weights_kernel<<<grid, block, 0, st>>>(W, Wt, nb, Hb, gs, bs);
+  note_launch();
+  return check_launch("transpose_weights_kernel");
+}
+
+// ---------------------------------------------------------------------------
+// recompute_gates
+// ---------------------------------------------------------------------------
+constexpr int RG_ROWS = 64;    // rows (t,b) per CTA
+constexpr int RG_KT = 32;      // k chunk
+
+__global__ void __launch_bounds__(256)
+recompute_gates_kernel(const BlockGemmArgs a) {
+  __shared__ float As[RG_ROWS][RG_KT + 1];     // fq_in(h_prev)[row][k]
+  __shared__ float Bs[RG_KT][96 + 1];          // W[k][g*32 + j]
+  const int Hb = a.Hb, H = a.H, B = a.B;
+  const int TB = a.T * B;
+  const int ntile_u = cdiv(Hb, 32);
+  const int n = blockIdx.x / ntile_u;
+  const int ut = blockIdx.x - n * ntile_u;
+  const int row0 = blockIdx.y * RG_ROWS;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const float* Wn = a.W + (size_t)n * a.w_block_stride;
+
+  float acc[3][8];
+#pragma unroll
+  for (int g = 0; g < 3; ++g)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[g][i] = 0.f;
+
+  for (int k0 = 0; k0 < Hb; k0 += RG_KT) {
+    for (int idx = tid; idx < RG_ROWS * RG_KT; idx += 256) {
+      const int r = idx / RG_KT, k = idx - r * RG_KT;
+      const int tb = row0 + r;
+      float v = 0.f;
+      if (tb < TB && k0 + k < Hb) {
+        v = h_prev_at(a.h0, a.out, tb, B, H, n * Hb + k0 + k);
+        if (a.qin.enabled) v = fake_quant<true>(v, a.qin);
+      }
+      As[r][k] = v;
+    }
+    for (int idx = tid; idx < 96 * RG_KT; idx += 256) {
+      const int k = idx % RG_KT, gj = idx / RG_KT;
+      const int g = gj / 32, j = gj - g * 32;
+      const int o = ut * 32 + j;
+      float v = 0.f;
+      if (o < Hb && k0 + k < Hb) v = Wn[(size_t)g * a.w_gate_stride + (size_t)o * Hb + k0 + k];
+      Bs[k][gj] = v;
+    }
+    __syncthreads();
+#pragma unroll 4
+    for (int k = 0; k < RG_KT; ++k) {
+      const float w0 = Bs[k][lane], w1 = Bs[k][32 + lane], w2 = Bs[k][64 + lane];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float h = As[warp * 8 + i][k];
+        acc[0][i] = fmaf(w0, h, acc[0][i]);
+        acc[1][i] = fmaf(w1, h, acc[1][i]);
+        acc[2][i] = fmaf(w2, h, acc[2][i]);
+      }
+    }
+    __syncthreads();
+  }
+
+  const int o = ut * 32 + lane;
+  if (o >= Hb) return;
+  const int u = n * Hb + o;
+  const float br = a.bh[u], bz = a.bh[H + u], bn = a.bh[2 * H + u];
+  const size_t comp = (size_t)TB * H;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int tb = row0 + warp * 8 + i;
+    if (tb >= TB) continue;
+    const float* g = a.gi + (size_t)tb * 3 * H + u;
+    const float ghn = acc[2][i] + bn;
+    const float r = sigmoidf_acc(g[0] + (acc[0][i] + br));
+    const float z = sigmoidf_acc(g[H] + (acc[1][i] + bz));
+    const float nn = tanhf(g[2 * H] + r * ghn);
+    const size_t off = (size_t)tb * H + u;
+    a.S[off] = r;
+    a.S[comp + off] = z;
+    a.S[2 * comp + off] = nn;
+    a.S[3 * comp + off] = ghn;
+  }
+}
+
+int launch_recompute_gates(const BlockGemmArgs& a, cudaStream_t st) {
+  dim3 grid(cdiv(a.Hb, 32) * a.nb, cdiv(a.T * a.B, RG_ROWS));
+  recompute_gates_kernel<<<grid, 256, 0, st>>>(a);
+  note_launch();
+  return check_launch("recompute_gates_kernel");
+}
+
+// ---------------------------------------------------------------------------
+// weight_grads
+// ---------------------------------------------------------------------------
+constexpr int WG_O = 64;       // output units per CTA (x 3 gates)
+constexpr int WG_K = 32;       // input units per CTA
+constexpr int WG_R = 32;       // rows (t,b) per smem chunk
+
+__global__ void __launch_bounds__(256)
+weight_grads_kernel(const BlockGemmArgs a, float* __restrict__ dst, int rows_per_split) {
+  __shared__ __align__(16) float Ds[WG_R][3 * WG_O];     // dgh[row][g*64 + o]
+  __shared__ float Hs[WG_R][WG_K];                       // fq_in(h_prev)[row][k]
+  const int Hb = a.Hb, H = a.H, B = a.B;
+  const int TB = a.T * B;
+  const int nkt = cdiv(Hb, WG_K), not_ = cdiv(Hb, WG_O);
+  int bx = blockIdx.x;
+  const int kt = bx % nkt; bx /= nkt;
+  const int ot = bx % not_;
+  const int n = bx / not_;
+  const int split = blockIdx.y;
+  const int r_begin = split * rows_per_split;
+  const int r_end = min(TB, r_begin + rows_per_split);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const size_t comp = (size_t)TB * H;
+
+  float acc[3][8];
+#pragma unroll
+  for (int g = 0; g < 3; ++g)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[g][i] = 0.f;
+
+  for (int r0 = r_begin; r0 < r_end; r0 += WG_R) {
+    for (int idx = tid; idx < WG_R * 3 * WG_O; idx += 256) {
+      const int r = idx / (3 * WG_O), go = idx - r * (3 * WG_O);
+      const int g = go / WG_O, o = go - g * WG_O;
+      const int tb = r0 + r, uo = ot * WG_O + o;
+      float v = 0.f;
+      if (tb < r_end && uo < Hb) {
+        const int u = n * Hb + uo;
+        v = a.dgi[(size_t)tb * 3 * H + (size_t)g * H + u];
+        if (g == 2) v = v * a.S[(size_t)tb * H + u];          // dgh_n = dgi_n * r
+      }
+      Ds[r][go] = v;
+    }
+    for (int idx = tid; idx < WG_R * WG_K; idx += 256) {
+      const int r = idx / WG_K, k = idx - r * WG_K;
+      const int tb = r0 + r, uk = kt * WG_K + k;
+      float v = 0.f;
+      if (tb < r_end && uk < Hb) {
+        v = h_prev_at(a.h0, a.out, tb, B, H, n * Hb + uk);
+        if (a.qin.enabled) v = fake_quant<true>(v, a.qin);
+      }
+      Hs[r][k] = v;
+    }
+    __syncthreads();
+#pragma unroll 2
+    for (int r = 0; r < WG_R; ++r) {
+      const float h = Hs[r][lane];
+#pragma unroll
+      for (int g = 0; g < 3; ++g) {
+        const float4 d0 = *reinterpret_cast<const float4*>(&Ds[r][g * WG_O + warp * 8]);
+        const float4 d1 = *reinterpret_cast<const float4*>(&Ds[r][g * WG_O + warp * 8 + 4]);
+        acc[g][0] = fmaf(d0.x, h, acc[g][0]); acc[g][1] = fmaf(d0.y, h, acc[g][1]);
+        acc[g][2] = fmaf(d0.z, h, acc[g][2]); acc[g][3] = fmaf(d0.w, h, acc[g][3]);
+        acc[g][4] = fmaf(d1.x, h, acc[g][4]); acc[g][5] = fmaf(d1.y, h, acc[g][5]);
+        acc[g][6] = fmaf(d1.z, h, acc[g][6]); acc[g][7] = fmaf(d1.w, h, acc[g][7]);
+      }
+    }
+    __syncthreads();
+  }
+  (void)comp;
+
+  const int k = kt * WG_K + lane;
+  if (k >= Hb) return;
+  const size_t dw_elems = (size_t)3 * a.nb * Hb * Hb;      // dense: 3*H*H as well
+  float* base = dst + (size_t)split * dw_elems + (size_t)n * a.w_block_stride;
+#pragma unroll
+  for (int g = 0; g < 3; ++g)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int o = ot * WG_O + warp * 8 + i;
+      if (o < Hb) base[(size_t)g * a.w_gate_stride + (size_t)o * Hb + k] = acc[g][i];
+    }
+}
+
+// dbh: column sums of dgh over a range of rows; partial[split][3H]
+__global__ void __launch_bounds__(256)
+bias_grads_kernel(const float* __restrict__ dgi, const float* __restrict__ S, float* __restrict__ dst,
+                  int TB, int H, int rows_per_split) {
+  __shared__ float red[8][32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int col = blockIdx.x * 32 + lane;                  // in [0, 3H)
+  const int r_begin = blockIdx.y * rows_per_split;
+  const int r_end = min(TB, r_begin + rows_per_split);
+  float s = 0.f;
+  if (col < 3 * H) {
+    const bool is_n = col >= 2 * H;
+    for (int tb = r_begin + warp; tb < r_end; tb += 8) {
+      float v = dgi[(size_t)tb * 3 * H + col];
+      if (is_n) v = v * S[(size_t)tb * H + (col - 2 * H)];
+      s += v;
+    }
+  }
+  red[warp][lane] = s;
+  __syncthreads();
+  if (warp == 0 && col < 3 * H) {
+    float t = red[0][lane];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) t += red[w][lane];
+    dst[(size_t)blockIdx.y * 3 * H + col] = t;
+  }
+}
+
+static void wg_splits(int T, int B, int nb, int Hb, int* nsplit, int* rows_per_split) {
+  const int TB = T * B;
+  const long long tiles = (long long)nb * cdiv(Hb, WG_O) * cdiv(Hb, WG_K);
+  long long s = (2 * 148 + tiles - 1) / tiles;
+  const long long max_by_rows = (TB + 4 * WG_R - 1) / (4 * WG_R);
+  if (s > max_by_rows) s = max_by_rows;
+  if (s > 32) s = 32;
+  if (s < 1) s = 1;
+  int rps = cdiv(cdiv(TB, (int)s), WG_R) * WG_R;
+  *nsplit = cdiv(TB, rps);
+  *rows_per_split = rps;
+}
+
+static void bg_splits(int T, int B, int* nsplit, int* rows_per_split) {
+  const int TB = T * B;
+  int s = cdiv(TB, 256);
+  if (s > 64) s = 64;
+  if (s < 1) s = 1;
+  const int rps = cdiv(TB, s);
+  *nsplit = cdiv(TB, rps);
+  *rows_per_split = rps;
+}
+
+size_t bias_grads_scratch_bytes(int T, int B, int H) {
+  int nsb, rpsb;
+  bg_splits(T, B, &nsb, &rpsb);
+  return align_up((size_t)nsb * 3 * H * sizeof(float), 256);
+}
+
+int launch_bias_grads(const float* dgi, const float* S, float* partial, float* dbh, int T, int B, int H,
+                      cudaStream_t st) {
+  int nsb, rpsb;
+  bg_splits(T, B, &nsb, &rpsb);
+  dim3 gridb(cdiv(3 * H, 32), nsb);
+  bias_grads_kernel<<<gridb, 256, 0, st>>>(dgi, S, partial, T * B, H, rpsb);
+  note_launch();
+  int rc = check_launch("bias_grads_kernel");
+  if (rc) return rc;
+  launch_reduce_partials(partial, nsb, (size_t)3 * H, (size_t)3 * H, dbh, st);
+  return check_launch("reduce_partials");
+}
+
+size_t weight_grads_scratch_bytes(int T, int B, int H, int nb, int Hb) {
+  int ns, rps, nsb, rpsb;
+  wg_splits(T, B, nb, Hb, &ns, &rps);
+  bg_splits(T, B, &nsb, &rpsb);
+  size_t f = 0;
+  if (ns > 1) f += (size_t)ns * 3 * nb * Hb * Hb;
+  f += (size_t)nsb * 3 * H;
+  return align_up(f * sizeof(float), 256);
+}
+
+int launch_weight_grads(const BlockGemmArgs& a, cudaStream_t st) {
+  int ns, rps, nsb, rpsb;
+  wg_splits(a.T, a.B, a.nb, a.Hb, &ns, &rps);
+  bg_splits(a.T, a.B, &nsb, &rpsb);
+  const size_t dw_elems = (size_t)3 * a.nb * a.Hb * a.Hb;
+  float* part_w = a.partial;
+  float* part_b = a.partial + (ns > 1 ? (size_t)ns * dw_elems : 0);
+
+  dim3 grid(cdiv(a.Hb, WG_K) * cdiv(a.Hb, WG_O) * a.nb, ns);
+  weight_grads_kernel<<<grid, 256, 0, st>>>(a, ns > 1 ? part_w : a.dW, rps);
+  note_launch();
+  int rc = check_launch("weight_grads_kernel");
+  if (rc) return rc;
+  if (ns > 1) launch_reduce_partials(part_w, ns, dw_elems, dw_elems, a.dW, st);
+
+  return launch_bias_grads(a.dgi, a.S, part_b, a.dbh, a.T, a.B, a.H, st);
+}
+
+}  // namespace b200gru

@@ -1,0 +1,338 @@
+// Diagonal hidden weights: gh_g = w_g * fq_in(h) + b_g  (elementwise over H).
+//
+// Every (batch row, hidden unit) pair is an independent length-T recurrence, so
+// the scan is a pure streaming kernel: one thread owns VEC adjacent hidden units
+// of one row, carries h (forward) or dh plus six weight/bias gradient sums
+// (backward) in registers for all T steps, and touches HBM exactly once per
+// algorithmic byte: 16*H bytes per sequence-step forward (gi read, out write),
+// 32*H backward (gi, h_prev, dout read; dgi write).  gi[t] does not depend on the
+// recurrence, so loads run PF steps ahead of the arithmetic in a register ring
+// that keeps PF*3*VEC*4 bytes per thread in flight.
+//
+// Follows the step arithmetic of src/gru_qat/triton_kernels/scan_diagonal.py
+// (forward :79-124, backward :564-647).
+
+#include "common.cuh"
+
+namespace b200gru {
+
+template <int VEC> struct VecT;
+template <> struct VecT<1> { using type = float; };
+template <> struct VecT<2> { using type = float2; };
+template <> struct VecT<4> { using type = float4; };
+
+template <int VEC>
+__device__ __forceinline__ void ld_stream(const float* p, float (&v)[VEC]) {
+  using V = typename VecT<VEC>::type;
+  V x = __ldcs(reinterpret_cast<const V*>(p));
+  const float* f = reinterpret_cast<const float*>(&x);
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) v[i] = f[i];
+}
+
+template <int VEC>
+__device__ __forceinline__ void ld_plain(const float* p, float (&v)[VEC]) {
+  using V = typename VecT<VEC>::type;
+  V x = *reinterpret_cast<const V*>(p);
+  const float* f = reinterpret_cast<const float*>(&x);
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) v[i] = f[i];
+}
+
+template <int VEC>
+__device__ __forceinline__ void st_vec(float* p, const float (&v)[VEC]) {
+  using V = typename VecT<VEC>::type;
+  V x;
+  float* f = reinterpret_cast<float*>(&x);
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) f[i] = v[i];
+  *reinterpret_cast<V*>(p) = x;
+}
+
+template <int VEC>
+__device__ __forceinline__ void st_stream(float* p, const float (&v)[VEC]) {
+  using V = typename VecT<VEC>::type;
+  V x;
+  float* f = reinterpret_cast<float*>(&x);
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) f[i] = v[i];
+  __stcs(reinterpret_cast<V*>(p), x);
+}
+
+// ---------------------------------------------------------------------------
+// forward
+// ---------------------------------------------------------------------------
+template <int VEC, int PF, bool QIN, bool QOUT>
+__global__ void __launch_bounds__(128)
+diag_fwd_kernel(const float* __restrict__ gi, const float* __restrict__ h0,
+                const float* __restrict__ W, const float* __restrict__ bh,
+                float* __restrict__ out, int T, int B, int H, Quant qin, Quant qout) {
+  const int hv = H / VEC;                                   // vectors per row
+  const long long chain = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (chain >= (long long)B * hv) return;
+  const int b = (int)(chain / hv);
+  const int i = (int)(chain % hv) * VEC;
+
+  float wr[VEC], wz[VEC], wn[VEC], br[VEC], bz[VEC], bn[VEC], h[VEC];
+  ld_plain<VEC>(W + i, wr);
+  ld_plain<VEC>(W + H + i, wz);
+  ld_plain<VEC>(W + 2 * H + i, wn);
+  ld_plain<VEC>(bh + i, br);
+  ld_plain<VEC>(bh + H + i, bz);
+  ld_plain<VEC>(bh + 2 * H + i, bn);
+  ld_plain<VEC>(h0 + (size_t)b * H + i, h);
+
+  const size_t gi_step = (size_t)B * 3 * H;
+  const size_t out_step = (size_t)B * H;
+  const float* gp = gi + (size_t)b * 3 * H + i;
+  float* op = out + (size_t)b * H + i;
+
+  float gr[PF][VEC], gz[PF][VEC], gn[PF][VEC];
+#pragma unroll
+  for (int p = 0; p < PF; ++p) {
+    if (p < T) {
+      ld_stream<VEC>(gp + p * gi_step, gr[p]);
+      ld_stream<VEC>(gp + p * gi_step + H, gz[p]);
+      ld_stream<VEC>(gp + p * gi_step + 2 * H, gn[p]);
+    }
+  }
+
+  for (int t0 = 0; t0 < T; t0 += PF) {
+#pragma unroll
+    for (int p = 0; p < PF; ++p) {
+      const int t = t0 + p;
+      if (t < T) {
+        float o[VEC];
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) {
+          const float hq = fake_quant<QIN>(h[v], qin);
+          const float ghr = wr[v] * hq + br[v];
+          const float ghz = wz[v] * hq + bz[v];
+          const float ghn = wn[v] * hq + bn[v];
+          const GateOut g = gru_gates(gr[p][v], gz[p][v], gn[p][v], ghr, ghz, ghn, h[v]);
+          h[v] = fake_quant<QOUT>(g.h_raw, qout);
+          o[v] = h[v];
+        }
+        st_vec<VEC>(op + (size_t)t * out_step, o);
+        const int tn = t + PF;
+        if (tn < T) {
+          ld_stream<VEC>(gp + tn * gi_step, gr[p]);
+          ld_stream<VEC>(gp + tn * gi_step + H, gz[p]);
+          ld_stream<VEC>(gp + tn * gi_step + 2 * H, gn[p]);
+        }
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// backward
+// ---------------------------------------------------------------------------
+// Block = (32 hidden vectors) x (BY batch rows).  Each thread walks t = T-1..0 for
+// its chain; the six per-unit sums (dW r,z,n and dbh r,z,n) are reduced over the
+// BY rows of the block in shared memory and written as one partial row per block
+// row-group: partial[part][6][H].  A second kernel sums the partial rows in a
+// fixed order, which keeps the result bit-reproducible run to run.
+constexpr int DIAG_BY = 4;
+
+template <int VEC, int PF, bool QIN, bool QOUT>
+__global__ void __launch_bounds__(32 * DIAG_BY)
+diag_bwd_kernel(const float* __restrict__ gi, const float* __restrict__ h0,
+                const float* __restrict__ W, const float* __restrict__ bh,
+                const float* __restrict__ out, const float* __restrict__ dout,
+                float* __restrict__ dgi, float* __restrict__ dh0,
+                float* __restrict__ partial, int T, int B, int H, Quant qin, Quant qout) {
+  const int hv = H / VEC;
+  const int iv = blockIdx.x * 32 + threadIdx.x;
+  const int b = blockIdx.y * DIAG_BY + threadIdx.y;
+  const bool active = (iv < hv) && (b < B);
+  const int i = iv * VEC;
+
+  float acc[6][VEC];
+#pragma unroll
+  for (int k = 0; k < 6; ++k)
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) acc[k][v] = 0.f;
+
+  if (active) {
+    float wr[VEC], wz[VEC], wn[VEC], br[VEC], bz[VEC], bn[VEC], dh_acc[VEC];
+    ld_plain<VEC>(W + i, wr);
+    ld_plain<VEC>(W + H + i, wz);
+    ld_plain<VEC>(W + 2 * H + i, wn);
+    ld_plain<VEC>(bh + i, br);
+    ld_plain<VEC>(bh + H + i, bz);
+    ld_plain<VEC>(bh + 2 * H + i, bn);
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) dh_acc[v] = 0.f;
+
+    const size_t gi_step = (size_t)B * 3 * H;
+    const size_t out_step = (size_t)B * H;
+    const float* gp = gi + (size_t)b * 3 * H + i;
+    float* dgp = dgi + (size_t)b * 3 * H + i;
+    const float* op = out + (size_t)b * H + i;
+    const float* dop = dout + (size_t)b * H + i;
+    const float* h0p = h0 + (size_t)b * H + i;
+
+    // ring slot p holds step t = T-1-(k*PF+p)
+    float gr[PF][VEC], gz[PF][VEC], gn[PF][VEC], hp[PF][VEC], dd[PF][VEC];
+#pragma unroll
+    for (int p = 0; p < PF; ++p) {
+      const int t = T - 1 - p;
+      if (t >= 0) {
+        ld_stream<VEC>(gp + t * gi_step, gr[p]);
+        ld_stream<VEC>(gp + t * gi_step + H, gz[p]);
+        ld_stream<VEC>(gp + t * gi_step + 2 * H, gn[p]);
+        ld_stream<VEC>(dop + t * out_step, dd[p]);
+        if (t > 0) ld_stream<VEC>(op + (size_t)(t - 1) * out_step, hp[p]);
+        else ld_plain<VEC>(h0p, hp[p]);
+      }
+    }
+
+    for (int s0 = 0; s0 < T; s0 += PF) {
+#pragma unroll
+      for (int p = 0; p < PF; ++p) {
+        const int t = T - 1 - (s0 + p);
+        if (t >= 0) {
+          float o_r[VEC], o_z[VEC], o_n[VEC];
+#pragma unroll
+          for (int v = 0; v < VEC; ++v) {
+            const float h_prev = hp[p][v];
+            const float hq = fake_quant<QIN>(h_prev, qin);
+            const float ghr = wr[v] * hq + br[v];
+            const float ghz = wz[v] * hq + bz[v];
+            const float ghn = wn[v] * hq + bn[v];
+            const GateOut g = gru_gates(gr[p][v], gz[p][v], gn[p][v], ghr, ghz, ghn, h_prev);
+            float dh = dd[p][v] + dh_acc[v];
+            dh = dh * ste_mask<QOUT>(g.h_raw, qout);
+            const GateGrad q = gru_gate_grads(dh, g.r, g.z, g.n, ghn, h_prev);
+            o_r[v] = q.dgr; o_z[v] = q.dgz; o_n[v] = q.dgn;
+            acc[0][v] += q.dgr * hq;
+            acc[1][v] += q.dgz * hq;
+            acc[2][v] += q.dghn * hq;
+            acc[3][v] += q.dgr;
+            acc[4][v] += q.dgz;
+            acc[5][v] += q.dghn;
+            float via = q.dgr * wr[v] + q.dgz * wz[v] + q.dghn * wn[v];
+            via = via * ste_mask<QIN>(h_prev, qin);
+            dh_acc[v] = via + q.dh_direct;
+          }
+          st_stream<VEC>(dgp + t * gi_step, o_r);
+          st_stream<VEC>(dgp + t * gi_step + H, o_z);
+          st_stream<VEC>(dgp + t * gi_step + 2 * H, o_n);
+          const int tn = t - PF;
+          if (tn >= 0) {
+            ld_stream<VEC>(gp + tn * gi_step, gr[p]);
+            ld_stream<VEC>(gp + tn * gi_step + H, gz[p]);
+            ld_stream<VEC>(gp + tn * gi_step + 2 * H, gn[p]);
+            ld_stream<VEC>(dop + tn * out_step, dd[p]);
+            if (tn > 0) ld_stream<VEC>(op + (size_t)(tn - 1) * out_step, hp[p]);
+            else ld_plain<VEC>(h0p, hp[p]);
+          }
+        }
+      }
+    }
+    st_vec<VEC>(dh0 + (size_t)b * H + i, dh_acc);
+  }
+
+  // reduce the six sums over the BY rows of this block (fixed order), one partial row out
+  __shared__ float red[DIAG_BY][6][32 * VEC];
+#pragma unroll
+  for (int k = 0; k < 6; ++k)
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) red[threadIdx.y][k][threadIdx.x * VEC + v] = acc[k][v];
+  __syncthreads();
+  if (threadIdx.y == 0 && iv < hv) {
+#pragma unroll
+    for (int k = 0; k < 6; ++k) {
+      float s[VEC];
+#pragma unroll
+      for (int v = 0; v < VEC; ++v) {
+        float a = red[0][k][threadIdx.x * VEC + v];
+#pragma unroll
+        for (int y = 1; y < DIAG_BY; ++y) a += red[y][k][threadIdx.x * VEC + v];
+        s[v] = a;
+      }
+      st_vec<VEC>(partial + ((size_t)blockIdx.y * 6 + k) * H + i, s);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+static int pick_vec(int B, int H, bool ptr_ok) {
+  // Prefer the widest vector that still leaves enough threads to fill the machine.
+  const long long chains = (long long)B * H;
+  const long long want_threads = 148LL * 512;
+  if (ptr_ok && H % 4 == 0 && chains / 4 >= want_threads) return 4;
+  if (ptr_ok && H % 2 == 0 && chains / 2 >= want_threads) return 2;
+  return 1;
+}
+
+size_t diag_bwd_workspace_bytes(int T, int B, int H) {
+  (void)T;
+  return align_up((size_t)cdiv(B, DIAG_BY) * 6 * H * sizeof(float), 256);
+}
+
+template <int VEC, int PF>
+static void launch_fwd(const float* gi, const float* h0, const float* W, const float* bh, float* out,
+                       int T, int B, int H, Quant qi, Quant qo, cudaStream_t st) {
+  const long long threads = (long long)B * (H / VEC);
+  const int block = 128;
+  const unsigned grid = (unsigned)((threads + block - 1) / block);
+#define DIAG_FWD(QI, QO) \
+  diag_fwd_kernel<VEC, PF, QI, QO><<<grid, block, 0, st>>>(gi, h0, W, bh, out, T, B, H, qi, qo)
+  if (qi.enabled) { if (qo.enabled) DIAG_FWD(true, true); else DIAG_FWD(true, false); }
+  else            { if (qo.enabled) DIAG_FWD(false, true); else DIAG_FWD(false, false); }
+#undef DIAG_FWD
+  note_launch();
+}
+
+int diag_forward(const float* gi, const float* h0, const float* W, const float* bh, float* out,
+                 int T, int B, int H, Quant qi, Quant qo, cudaStream_t st) {
+  const bool ok = aligned16(gi) && aligned16(h0) && aligned16(W) && aligned16(bh) && aligned16(out);
+  const int vec = pick_vec(B, H, ok);
+  if (vec == 4) launch_fwd<4, 4>(gi, h0, W, bh, out, T, B, H, qi, qo, st);
+  else if (vec == 2) launch_fwd<2, 6>(gi, h0, W, bh, out, T, B, H, qi, qo, st);
+  else launch_fwd<1, 8>(gi, h0, W, bh, out, T, B, H, qi, qo, st);
+  return check_launch("diag_fwd_kernel");
+}
+
+template <int VEC, int PF>
+static void launch_bwd(const float* gi, const float* h0, const float* W, const float* bh,
+                       const float* out, const float* dout, float* dgi, float* dh0, float* partial,
+                       int T, int B, int H, Quant qi, Quant qo, cudaStream_t st) {
+  dim3 block(32, DIAG_BY);
+  dim3 grid(cdiv(H / VEC, 32), cdiv(B, DIAG_BY));
+#define DIAG_BWD(QI, QO)                                                                     \
+  diag_bwd_kernel<VEC, PF, QI, QO><<<grid, block, 0, st>>>(gi, h0, W, bh, out, dout, dgi, dh0, \
+                                                           partial, T, B, H, qi, qo)
+  if (qi.enabled) { if (qo.enabled) DIAG_BWD(true, true); else DIAG_BWD(true, false); }
+  else            { if (qo.enabled) DIAG_BWD(false, true); else DIAG_BWD(false, false); }
+#undef DIAG_BWD
+  note_launch();
+}
+
+int diag_backward(const float* gi, const float* h0, const float* W, const float* bh,
+                  const float* out, const float* dout, float* dgi, float* dh0, float* dW, float* dbh,
+                  void* workspace, int T, int B, int H, Quant qi, Quant qo, cudaStream_t st) {
+  float* partial = static_cast<float*>(workspace);
+  const bool ok = aligned16(gi) && aligned16(h0) && aligned16(W) && aligned16(bh) && aligned16(out) &&
+                  aligned16(dout) && aligned16(dgi) && aligned16(dh0) && aligned16(partial);
+  const int vec = pick_vec(B, H, ok);
+  if (vec == 4) launch_bwd<4, 2>(gi, h0, W, bh, out, dout, dgi, dh0, partial, T, B, H, qi, qo, st);
+  else if (vec == 2) launch_bwd<2, 3>(gi, h0, W, bh, out, dout, dgi, dh0, partial, T, B, H, qi, qo, st);
+  else launch_bwd<1, 4>(gi, h0, W, bh, out, dout, dgi, dh0, partial, T, B, H, qi, qo, st);
+  int rc = check_launch("diag_bwd_kernel");
+  if (rc) return rc;
+  // partial[part][0..2][H] -> dW[3][H];  partial[part][3..5][H] -> dbh[3H]
+  const int nparts = cdiv(B, DIAG_BY);
+  launch_reduce_partials(partial, nparts, (size_t)6 * H, (size_t)3 * H, dW, st);
+  launch_reduce_partials(partial + (size_t)3 * H, nparts, (size_t)6 * H, (size_t)3 * H, dbh, st);
+  return check_launch("reduce_partials");
+}
+
+}  // namespace b200gru

@@ -1,0 +1,140 @@
+"""Sequence driver over ``GRUCellQuant``.
+
+Interface of ``gru_qat.gru_layer.GRULayer`` (src/gru_qat/gru_layer.py:52-342):
+same constructor keywords, ``forward(x, h0=None) -> (out, h_T)``,
+``calibrate()`` / ``freeze()``.  With ``use_triton`` in effect (the keyword keeps
+the reference's name; there is no Triton here) a CUDA input takes the fast path:
+one GEMM for the input projection of the whole sequence, then ONE persistent
+CUDA scan over all T steps (diagonal / monarch / butterfly hidden side).  CPU
+tensors, ineligible layers and ``calibrate()`` run the per-step loop.
+"""
+
+from __future__ import annotations
+
+from typing import Iterable, Optional
+
+import torch
+import torch.nn as nn
+
+from .gru_cell import GateLayout, GRUCellQuant
+from .quantizers import FakeQuantize, FakeQuantizePerTensor, QuantRecipe
+from .structure import StructureConfig
+
+_FAST_KINDS = ("diagonal", "monarch", "butterfly")
+
+
+def _extract_h_quant_params(quantizer: FakeQuantize):
+    """``(scale, qmin, qmax)`` if the quantizer is frozen, per-tensor and symmetric --
+    the only form the scan kernels apply -- else None (gru_layer.py:30-48)."""
+    cfg = quantizer.config
+    if cfg.mode != "frozen" or not isinstance(quantizer, FakeQuantizePerTensor) or not cfg.symmetric:
+        return None
+    return float(quantizer.scale.item()), int(quantizer.qmin), int(quantizer.qmax)
+
+
+class GRULayer(nn.Module):
+    def __init__(self, input_size: int, hidden_size: int, recipe: QuantRecipe, *,
+                 batch_first: bool = False, gate_layout: GateLayout = "split",
+                 compile_step: bool = False, pre_batch_input: bool = False,
+                 structure_input: Optional[StructureConfig] = None,
+                 structure_hidden: Optional[StructureConfig] = None,
+                 use_triton="auto") -> None:
+        super().__init__()
+        if pre_batch_input and gate_layout != "fused":
+            raise ValueError("pre_batch_input=True requires gate_layout='fused'")
+        self.cell = GRUCellQuant(input_size, hidden_size, recipe, gate_layout=gate_layout,
+                                 structure_input=structure_input, structure_hidden=structure_hidden)
+        if self.cell.is_structured and pre_batch_input:
+            raise ValueError("pre_batch_input is not supported in structured mode "
+                             "(no dense Wi_cat to pre-project).")
+        self.hidden_size, self.batch_first, self.pre_batch_input = hidden_size, batch_first, pre_batch_input
+
+        kind = structure_hidden.kind if structure_hidden is not None else None
+        self._fast_dispatch_eligible = kind in _FAST_KINDS and gate_layout == "fused"
+        self._dispatch_kind = kind if self._fast_dispatch_eligible else None
+        if use_triton == "auto":
+            self.use_triton = self._fast_dispatch_eligible
+        else:
+            self.use_triton = bool(use_triton)
+            if self.use_triton and not self._fast_dispatch_eligible:
+                raise ValueError("use_triton=True requires structure_hidden.kind in "
+                                 "{'diagonal', 'monarch', 'butterfly'} and gate_layout='fused'.")
+
+        if self.cell.is_structured:
+            body = self.cell.step_structured
+        elif pre_batch_input:
+            body = self.cell.step_with_gi
+        else:
+            body = self.cell.step
+        self._compiled_step = torch.compile(body, mode="default", dynamic=False) if compile_step else body
+
+    # ------------------------------------------------------------------
+    def forward(self, x: torch.Tensor, h0: Optional[torch.Tensor] = None):
+        if self.batch_first:
+            x = x.transpose(0, 1)
+        T, B, _ = x.shape
+        if T == 0:
+            raise ValueError(f"seq length T must be > 0; got T={T}")
+        if B == 0:
+            raise ValueError(f"batch size B must be > 0; got B={B}")
+        if h0 is None:
+            h0 = x.new_zeros(B, self.hidden_size)
+
+        if self.use_triton and x.is_cuda:
+            return self._forward_fast_dispatch(x, h0)
+
+        step, h, outs = self._compiled_step, h0, []
+        if self.cell.is_structured:
+            for t in range(T):
+                h = step(x[t], h)
+                outs.append(h)
+        else:
+            w = self.cell.quantize_weights()
+            seq = self.cell.input_projection(x, w) if self.pre_batch_input else x
+            for t in range(T):
+                h = step(seq[t], h, w)
+                outs.append(h)
+        out = torch.stack(outs, dim=0)
+        return (out.transpose(0, 1) if self.batch_first else out), h
+
+    def _forward_fast_dispatch(self, x, h0):
+        """Input projection hoisted to one GEMM, then the persistent CUDA scan
+        (gru_layer.py:234-302)."""
+        cell = self.cell
+        if cell._input_dense:
+            Wi_cat, bi_cat = cell.quantize_input_weights()
+            gi = nn.functional.linear(cell.quant_x(x), Wi_cat, bi_cat)
+        else:
+            gi = cell.structured_input_projection(x)
+        quant = dict(h_in_quant=_extract_h_quant_params(cell.quant_h_in),
+                     h_out_quant=_extract_h_quant_params(cell.quant_h_out))
+
+        if self._dispatch_kind == "diagonal":
+            from .scan_diagonal import extract_diagonal_factors, gru_scan_diagonal
+            out = gru_scan_diagonal(gi, h0, *extract_diagonal_factors(cell), **quant)
+        elif self._dispatch_kind == "monarch":
+            from .scan_monarch import extract_monarch_factors, gru_scan_monarch
+            out = gru_scan_monarch(gi, h0, *extract_monarch_factors(cell), **quant)
+        elif self._dispatch_kind == "butterfly":
+            from .scan_butterfly import extract_butterfly_twiddles, gru_scan_butterfly_cuda
+            out = gru_scan_butterfly_cuda(gi, h0, *extract_butterfly_twiddles(cell), **quant)
+        else:
+            raise RuntimeError(f"unexpected dispatch kind {self._dispatch_kind!r}")
+        h_T = out[-1]
+        return (out.transpose(0, 1) if self.batch_first else out), h_T
+
+    # ------------------------------------------------------------------
+    @torch.no_grad()
+    def calibrate(self, loader: Iterable[object], n_batches: int = 64, *, only_activations: bool = True):
+        """Observe activation ranges over ``n_batches`` forwards on the per-step path
+        (the fast path reads scales but never runs the hidden quantizers, so it is
+        switched off for the duration).  Call :meth:`freeze` afterwards."""
+        from .calibration import calibrate as _calibrate
+        saved, self.use_triton = self.use_triton, False
+        try:
+            return _calibrate(self, loader, n_batches=n_batches, only_activations=only_activations)
+        finally:
+            self.use_triton = saved
+
+    def freeze(self) -> None:
+        self.cell.freeze_quantizers()

@@ -1,0 +1,168 @@
+/*
+ * b200gru -- C ABI of the B200 (sm_100a) persistent GRU scan library.
+ *
+ * One shared library, plain pointers and sizes, no framework types.  Every
+ * entry point replaces one Python wrapper of LarocheC/gru-triton (package
+ * gru_qat); the citation beside each declaration names the file:line of the
+ * reference interface it stands in for.
+ *
+ * Conventions shared by all entry points
+ *  - all tensors are fp32 device pointers, row-major, last dimension contiguous
+ *    and tightly packed: gi[T,B,3H] (gates r,z,n stacked along the last axis,
+ *    input bias already added), h0[B,H], bh[3H], out[T,B,H];
+ *  - q_in / q_out describe the frozen per-tensor symmetric fake-quant of the
+ *    hidden state (NULL or enabled == 0 -> off);
+ *  - `stream` is a cudaStream_t passed as void*; all work is enqueued on it, the
+ *    library never synchronises and never allocates: scratch memory comes from
+ *    the caller (`workspace`, size from b200gru_workspace_bytes, 256-byte aligned);
+ *  - return value 0 = success, otherwise a b200gru_status (see b200gru_strerror).
+ */
+#ifndef B200GRU_H
+#define B200GRU_H
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+  B200GRU_OK = 0,
+  B200GRU_INVALID_ARGUMENT = 1,   /* NULL pointer, non-positive size, bad shape relation   */
+  B200GRU_UNSUPPORTED = 2,        /* shape outside what this build can run                  */
+  B200GRU_LAUNCH_FAILURE = 3,     /* cudaGetLastError() != cudaSuccess after a launch       */
+  B200GRU_WORKSPACE_TOO_SMALL = 4 /* workspace_bytes < b200gru_workspace_bytes(...)         */
+} b200gru_status;
+
+typedef enum {
+  B200GRU_DENSE = 0,
+  B200GRU_DIAGONAL = 1,
+  B200GRU_MONARCH = 2,    /* one block-diagonal factor per gate */
+  B200GRU_BUTTERFLY = 3
+} b200gru_kind;
+
+/* (scale, qmin, qmax) of gru_qat's h_in_quant / h_out_quant tuples
+ * (src/gru_qat/gru_layer.py:30-48; semantics src/gru_qat/triton_kernels/scan.py:1450-1457):
+ * fq(x) = clamp(rint(x / scale), qmin, qmax) * scale, round-half-to-even. */
+typedef struct {
+  float scale;
+  int qmin;
+  int qmax;
+  int enabled;
+} b200gru_quant;
+
+/* Problem shape.  nblocks: MONARCH = number of diagonal blocks (block size H/nblocks);
+ * BUTTERFLY = number of stacked butterfly factors.  log2_hpad: BUTTERFLY only, twiddles
+ * are [3, nblocks, log2_hpad, hpad/2, 2, 2] with hpad = 1 << log2_hpad >= H. */
+typedef struct {
+  int kind;
+  int T, B, H;
+  int nblocks;
+  int log2_hpad;
+} b200gru_shape;
+
+/* Bytes of caller-provided scratch needed by the forward (backward == 0) or the
+ * backward (backward == 1) of `shape`.  0 is a valid answer.  Returns (size_t)-1
+ * for an invalid shape.  Replaces the torch.zeros/torch.empty scratch allocations
+ * of the reference wrappers (scan.py:710-717, scan_monarch.py:848-856,
+ * scan_butterfly.py:429-432, 1033-1040). */
+size_t b200gru_workspace_bytes(const b200gru_shape* shape, int backward);
+
+/* Bytes of the optional `save` buffer (gate activations r, z, n and the n-gate
+ * hidden pre-activation, [4,T,B,H] fp32) that the forward can emit and the backward
+ * can consume to skip its recompute pass.  No reference counterpart: the reference
+ * recomputes the gates inside its backward kernels (scan.py:389-432). */
+size_t b200gru_save_bytes(const b200gru_shape* shape);
+
+/* Generic forward: out[T,B,H] from gi, h0, W, bh.  `save` may be NULL.
+ * Replaces gru_scan_forward_persistent (scan.py:213-293), gru_scan_forward
+ * (scan.py:1688-1765), gru_scan_diagonal_forward_triton (scan_diagonal.py:226-282),
+ * gru_scan_monarch_forward_triton (scan_monarch.py:320-406) and
+ * gru_scan_butterfly_forward_triton (scan_butterfly.py:369-459). */
+int b200gru_scan_forward(const b200gru_shape* shape,
+                         const float* gi, const float* h0, const float* W, const float* bh,
+                         const b200gru_quant* q_in, const b200gru_quant* q_out,
+                         float* out, float* save,
+                         void* workspace, size_t workspace_bytes, void* stream);
+
+/* Generic backward: (dgi[T,B,3H], dh0[B,H], dW like W, dbh[3H]) from the forward's
+ * inputs, its `out`, and dout[T,B,H].  Every output element is written (no
+ * pre-zeroing needed).  `save` is the forward's save buffer or NULL (then the
+ * gates are recomputed).  Replaces gru_scan_backward_persistent (scan.py:646-752),
+ * gru_scan_backward_triton (scan.py:1355-1447), gru_scan_diagonal_backward_triton
+ * (scan_diagonal.py:490-561), gru_scan_monarch_backward_triton
+ * (scan_monarch.py:776-884) and gru_scan_butterfly_backward_triton
+ * (scan_butterfly.py:971-1075), including their trailing partial.sum(0). */
+int b200gru_scan_backward(const b200gru_shape* shape,
+                          const float* gi, const float* h0, const float* W, const float* bh,
+                          const float* out, const float* dout, const float* save,
+                          const b200gru_quant* q_in, const b200gru_quant* q_out,
+                          float* dgi, float* dh0, float* dW, float* dbh,
+                          void* workspace, size_t workspace_bytes, void* stream);
+
+/* Per-kind conveniences with the argument order of the reference functions.
+ * W is Wh_cat[3H,H] (dense), Wh_diag[3,H], Wh_struct[3,nblocks,H/nblocks,H/nblocks]
+ * or twiddles[3,nblocks,log2_hpad,hpad/2,2,2]. */
+
+/* gru_scan_forward_persistent, scan.py:213 */
+int b200gru_dense_forward(const float* gi, const float* h0, const float* Wh_cat, const float* bh_cat,
+                          int T, int B, int H, const b200gru_quant* q_in, const b200gru_quant* q_out,
+                          float* out, float* save, void* workspace, size_t workspace_bytes, void* stream);
+/* gru_scan_backward_persistent, scan.py:646 */
+int b200gru_dense_backward(const float* gi, const float* h0, const float* Wh_cat, const float* bh_cat,
+                           const float* out, const float* dout, const float* save,
+                           int T, int B, int H, const b200gru_quant* q_in, const b200gru_quant* q_out,
+                           float* dgi, float* dh0, float* dWh, float* dbh,
+                           void* workspace, size_t workspace_bytes, void* stream);
+/* gru_scan_diagonal_forward_triton, scan_diagonal.py:226 */
+int b200gru_diagonal_forward(const float* gi, const float* h0, const float* Wh_diag, const float* bh_cat,
+                             int T, int B, int H, const b200gru_quant* q_in, const b200gru_quant* q_out,
+                             float* out, void* stream);
+/* gru_scan_diagonal_backward_triton, scan_diagonal.py:490 */
+int b200gru_diagonal_backward(const float* gi, const float* h0, const float* Wh_diag, const float* bh_cat,
+                              const float* out, const float* dout,
+                              int T, int B, int H, const b200gru_quant* q_in, const b200gru_quant* q_out,
+                              float* dgi, float* dh0, float* dWh_diag, float* dbh,
+                              void* workspace, size_t workspace_bytes, void* stream);
+/* gru_scan_monarch_forward_triton, scan_monarch.py:320 */
+int b200gru_monarch_forward(const float* gi, const float* h0, const float* Wh_struct, const float* bh_cat,
+                            int T, int B, int H, int nblocks,
+                            const b200gru_quant* q_in, const b200gru_quant* q_out,
+                            float* out, float* save, void* workspace, size_t workspace_bytes, void* stream);
+/* gru_scan_monarch_backward_triton, scan_monarch.py:776 */
+int b200gru_monarch_backward(const float* gi, const float* h0, const float* Wh_struct, const float* bh_cat,
+                             const float* out, const float* dout, const float* save,
+                             int T, int B, int H, int nblocks,
+                             const b200gru_quant* q_in, const b200gru_quant* q_out,
+                             float* dgi, float* dh0, float* dWh_struct, float* dbh,
+                             void* workspace, size_t workspace_bytes, void* stream);
+/* gru_scan_butterfly_forward_triton, scan_butterfly.py:369 */
+int b200gru_butterfly_forward(const float* gi, const float* h0, const float* twiddles, const float* bh_cat,
+                              int T, int B, int H, int nblocks, int log2_hpad,
+                              const b200gru_quant* q_in, const b200gru_quant* q_out,
+                              float* out, float* save, void* workspace, size_t workspace_bytes, void* stream);
+/* gru_scan_butterfly_backward_triton, scan_butterfly.py:971 */
+int b200gru_butterfly_backward(const float* gi, const float* h0, const float* twiddles, const float* bh_cat,
+                               const float* out, const float* dout, const float* save,
+                               int T, int B, int H, int nblocks, int log2_hpad,
+                               const b200gru_quant* q_in, const b200gru_quant* q_out,
+                               float* dgi, float* dh0, float* dtwiddles, float* dbh,
+                               void* workspace, size_t workspace_bytes, void* stream);
+
+/* Number of kernels the library has launched in this process since it was loaded
+ * (all streams).  Used by the benchmark to report its launch count; no reference
+ * counterpart. */
+unsigned long long b200gru_launch_count(void);
+
+/* Human-readable text for a b200gru_status; plus the text of the last CUDA error
+ * seen by a launch in this thread (empty string if none). */
+const char* b200gru_strerror(int status);
+const char* b200gru_last_cuda_error(void);
+
+/* Library version: major*10000 + minor*100 + patch. */
+int b200gru_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200GRU_H */

@@ -1,0 +1,298 @@
+"""GPU parity: the CUDA scan (through the C ABI) against the CPU oracle.
+
+Tolerances (the ones the build is held to):
+  fp32 forward            |gpu - ref| <= 1e-5 + 1e-5 * |ref|            (FWD_TOL)
+  fp32 gradients          max|gpu - ref| / max|ref| <= 1e-4             (GRAD_TOL)
+  int8 codes of h         bit-exact, except where the oracle's h_raw / s lies within
+                          TIE_WINDOW code units of a half-way point; then +-1 code.
+The code comparison is teacher-forced: the oracle advances ONE step from the
+device's own h_{t-1}, so a rounding tie cannot cascade into later steps.
+"""
+
+from __future__ import annotations
+
+import pytest
+import torch
+
+from conftest import SCAN_GOLDEN_FLAT, load_golden, rel_err
+from oracle import gru_scan_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+FWD_TOL = 1e-5
+GRAD_TOL = 1e-4
+TIE_WINDOW = {"diagonal": 1e-4, "dense": 1e-3, "monarch": 1e-3, "butterfly": 1e-3}
+Q8 = ((0.02, -127, 127), (0.02, -127, 127))
+Q8_ASYM = ((0.02, -127, 127), (0.013, -127, 127))
+
+
+def _mods():
+    from gru_triton_b200 import scan, scan_butterfly, scan_diagonal, scan_monarch
+    return {
+        "dense": (scan.gru_scan_forward_persistent, scan.gru_scan_backward_persistent, scan.gru_scan_persistent),
+        "diagonal": (scan_diagonal.gru_scan_diagonal_forward_triton,
+                     scan_diagonal.gru_scan_diagonal_backward_triton, scan_diagonal.gru_scan_diagonal),
+        "monarch": (scan_monarch.gru_scan_monarch_forward_triton,
+                    scan_monarch.gru_scan_monarch_backward_triton, scan_monarch.gru_scan_monarch),
+        "butterfly": (scan_butterfly.gru_scan_butterfly_forward_triton,
+                      scan_butterfly.gru_scan_butterfly_backward_triton,
+                      scan_butterfly.gru_scan_butterfly_triton),
+    }
+
+
+def _cuda(*ts):
+    return tuple(t.cuda() for t in ts)
+
+
+def check_forward(kind, out_gpu, gi, h0, W, bh, quant):
+    """Assert forward parity; returns (max abs err | None, #tie mismatches)."""
+    out_gpu = out_gpu.cpu()
+    qi, qo = quant if quant else (None, None)
+    if qo is None:
+        ref = orc.scan_forward(kind, gi, h0, W, bh, qi, qo)
+        err = (out_gpu - ref).abs()
+        assert bool((err <= FWD_TOL + FWD_TOL * ref.abs()).all()), f"max abs err {err.max().item():.3e}"
+        return err.max().item(), 0
+    h_prev = torch.cat([h0[None], out_gpu[:-1]], dim=0)
+    raw = orc.scan_forward_teacher_forced(kind, gi, h_prev, W, bh, qi)
+    codes_ref = orc.quant_codes(raw, qo)
+    codes_gpu = torch.round(out_gpu / qo[0])
+    assert bool((codes_gpu * qo[0] == out_gpu).all()), "device output is not on the quantisation grid"
+    bad = codes_ref != codes_gpu
+    nbad = int(bad.sum())
+    if nbad:
+        dist = orc.tie_distance(raw, qo)[bad]
+        step = (codes_ref - codes_gpu)[bad].abs()
+        assert float(dist.max()) <= TIE_WINDOW[kind], f"code mismatch {float(dist.max()):.2e} from a tie"
+        assert float(step.max()) <= 1.0
+    return None, nbad
+
+
+def check_backward(kind, grads_gpu, gi, h0, W, bh, out_gpu, dout, quant, tol=GRAD_TOL):
+    qi, qo = quant if quant else (None, None)
+    ref = orc.scan_backward(kind, gi, h0, W, bh, out_gpu.cpu(), dout, qi, qo)
+    errs = {}
+    for nm, a, b in zip(("dgi", "dh0", "dW", "dbh"), grads_gpu, ref):
+        errs[nm] = rel_err(a.cpu(), b)
+        assert errs[nm] <= tol, f"{nm}: rel err {errs[nm]:.3e}"
+    return errs
+
+
+GRID = [(1, 1, 32), (8, 4, 32), (8, 32, 128), (64, 4, 128), (64, 32, 512), (5, 3, 96)]
+
+
+def _kwargs(kind, H):
+    if kind == "monarch":
+        return {"nblocks": 4}
+    return {}
+
+
+@pytest.mark.parametrize("quant", [None, Q8, Q8_ASYM], ids=["fp32", "q8", "q8asym"])
+@pytest.mark.parametrize("T,B,H", GRID)
+@pytest.mark.parametrize("kind", ["dense", "diagonal", "monarch", "butterfly"])
+def test_scan_parity(kind, T, B, H, quant):
+    if kind == "butterfly" and H & (H - 1):
+        H = 128                                 # covered separately by the padding test
+    fwd, bwd, _ = _mods()[kind]
+    gi, h0, W, bh, dout = orc.make_problem(kind, T, B, H, seed=T * 1000 + B * 10 + H, **_kwargs(kind, H))
+    kw = dict(h_in_quant=quant[0], h_out_quant=quant[1]) if quant else {}
+    d = _cuda(gi, h0, W, bh, dout)
+    out = fwd(*d[:4], **kw)
+    check_forward(kind, out, gi, h0, W, bh, quant)
+    grads = bwd(*d[:4], out, d[4], **kw)
+    check_backward(kind, grads, gi, h0, W, bh, out, dout, quant)
+
+
+@pytest.mark.parametrize("kind,name", SCAN_GOLDEN_FLAT)
+def test_golden_vectors_through_the_cuda_path(kind, name):
+    g = load_golden(name)
+    fwd, bwd, _ = _mods()[kind]
+    kw = dict(h_in_quant=g["q_in"], h_out_quant=g["q_out"]) if g["q_in"] else {}
+    d = _cuda(g["gi"], g["h0"], g["W"], g["bh"], g["dout"], g["out"])
+    out = fwd(*d[:4], **kw).cpu()
+    if g["q_out"] is None:
+        assert bool(((out - g["out"]).abs() <= FWD_TOL + FWD_TOL * g["out"].abs()).all())
+    else:
+        check_forward(kind, out, g["gi"], g["h0"], g["W"], g["bh"], (g["q_in"], g["q_out"]))
+    grads = bwd(*d[:4], d[5], d[4], **kw)        # backward from the REFERENCE's out
+    for nm, a in zip(("dgi", "dh0", "dW", "dbh"), grads):
+        assert rel_err(a.cpu(), g[nm]) <= GRAD_TOL, nm
+
+
+@pytest.mark.parametrize("kind,T,B,H,extra", [
+    ("diagonal", 1, 1, 1, {}), ("diagonal", 9, 3, 2, {}), ("diagonal", 9, 5, 8, {}), ("diagonal", 7, 2, 1023, {}),
+    ("dense", 1, 1, 1, {}), ("dense", 6, 3, 2, {}), ("dense", 6, 5, 8, {}), ("dense", 4, 3, 100, {}),
+    ("dense", 3, 2, 1024, {}),
+    ("monarch", 6, 3, 8, {"nblocks": 8}), ("monarch", 6, 3, 24, {"nblocks": 2}), ("monarch", 5, 9, 96, {"nblocks": 4}),
+    ("monarch", 4, 2, 512, {"nblocks": 2}),
+    ("butterfly", 5, 3, 2, {}), ("butterfly", 5, 3, 12, {}), ("butterfly", 4, 2, 8, {"butterfly_nblocks": 2}),
+    ("butterfly", 3, 5, 48, {"butterfly_nblocks": 3}), ("butterfly", 3, 2, 1024, {}),
+])
+@pytest.mark.parametrize("quant", [None, Q8], ids=["fp32", "q8"])
+def test_edge_shapes(kind, T, B, H, extra, quant):
+    fwd, bwd, _ = _mods()[kind]
+    gi, h0, W, bh, dout = orc.make_problem(kind, T, B, H, seed=7 + H, **extra)
+    kw = dict(h_in_quant=quant[0], h_out_quant=quant[1]) if quant else {}
+    d = _cuda(gi, h0, W, bh, dout)
+    out = fwd(*d[:4], **kw)
+    check_forward(kind, out, gi, h0, W, bh, quant)
+    grads = bwd(*d[:4], out, d[4], **kw)
+    check_backward(kind, grads, gi, h0, W, bh, out, dout, quant)
+
+
+@pytest.mark.parametrize("kind", ["dense", "diagonal", "monarch", "butterfly"])
+def test_batch_invariance_and_determinism(kind):
+    """A row's result does not depend on the batch it rides in, and repeated runs are bit-identical."""
+    fwd, bwd, _ = _mods()[kind]
+    H = 128
+    gi, h0, W, bh, dout = orc.make_problem(kind, 12, 33, H, seed=99, nblocks=4)
+    d = _cuda(gi, h0, W, bh, dout)
+    full = fwd(*d[:4], h_in_quant=Q8[0], h_out_quant=Q8[1])
+    for B in (1, 3, 5, 7, 9, 17):
+        part = fwd(d[0][:, :B].contiguous(), d[1][:B].contiguous(), d[2], d[3], h_in_quant=Q8[0], h_out_quant=Q8[1])
+        assert torch.equal(part, full[:, :B]), B
+    g0 = bwd(*d[:4], full, d[4], h_in_quant=Q8[0], h_out_quant=Q8[1])
+    for _ in range(5):
+        assert torch.equal(fwd(*d[:4], h_in_quant=Q8[0], h_out_quant=Q8[1]), full)
+        g1 = bwd(*d[:4], full, d[4], h_in_quant=Q8[0], h_out_quant=Q8[1])
+        for a, b in zip(g0, g1):
+            assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("kind", ["dense", "diagonal", "monarch", "butterfly"])
+@pytest.mark.parametrize("quant", [None, Q8], ids=["fp32", "q8"])
+def test_autograd_matches_explicit_backward(kind, quant):
+    """autograd (forward saves the gate activations) vs the explicit backward (recomputes them)."""
+    fwd, bwd, fn = _mods()[kind]
+    gi, h0, W, bh, dout = orc.make_problem(kind, 16, 8, 64, seed=5, nblocks=4)
+    kw = dict(h_in_quant=quant[0], h_out_quant=quant[1]) if quant else {}
+    leaves = [t.cuda().requires_grad_(True) for t in (gi, h0, W, bh)]
+    out = fn(*leaves, **kw)
+    out.backward(dout.cuda())
+    explicit = bwd(*[l.detach() for l in leaves], out.detach(), dout.cuda(), **kw)
+    assert torch.equal(out.detach(), fwd(*[l.detach() for l in leaves], **kw))
+    for leaf, e in zip(leaves, explicit):
+        assert rel_err(leaf.grad, e) <= GRAD_TOL
+    check_backward(kind, [l.grad for l in leaves], gi, h0, W, bh, out.detach(), dout, quant)
+
+
+@pytest.mark.parametrize("cls", ["near-saturation", "large-magnitude"])
+@pytest.mark.parametrize("kind", ["dense", "diagonal", "monarch", "butterfly"])
+def test_adversarial_quant_inputs(kind, cls):
+    """Inputs that sit at the int8 clip boundary or far beyond it clip the same way as the oracle."""
+    fwd, bwd, _ = _mods()[kind]
+    T, B, H = 8, 4, 128
+    gi, h0, W, bh, dout = orc.make_problem(kind, T, B, H, seed=3, nblocks=4)
+    if cls == "near-saturation":
+        gi = torch.linspace(-0.99, 0.99, gi.numel()).reshape(gi.shape) * 2.54 * 3
+        h0 = torch.linspace(-0.99, 0.99, h0.numel()).reshape(h0.shape) * 2.54
+    else:
+        gi, h0 = gi * 5.0, torch.randn(B, H, generator=torch.Generator().manual_seed(1)) * 5.0
+    d = _cuda(gi, h0, W, bh, dout)
+    out = fwd(*d[:4], h_in_quant=Q8[0], h_out_quant=Q8[1])
+    check_forward(kind, out, gi, h0, W, bh, Q8)
+    grads = bwd(*d[:4], out, d[4], h_in_quant=Q8[0], h_out_quant=Q8[1])
+    check_backward(kind, grads, gi, h0, W, bh, out, dout, Q8)
+
+
+def test_wrapper_validation_on_cuda():
+    from gru_triton_b200 import scan, scan_butterfly, scan_diagonal, scan_monarch
+    T, B, H = 4, 2, 8
+    dev = "cuda"
+    gi, h0, bh = torch.randn(T, B, 3 * H, device=dev), torch.zeros(B, H, device=dev), torch.zeros(3 * H, device=dev)
+    Wd = torch.randn(3 * H, H, device=dev)
+    bad = [
+        lambda: scan.gru_scan(gi.double(), h0.double(), Wd.double(), bh.double()),
+        lambda: scan.gru_scan(gi, torch.zeros(B + 1, H, device=dev), Wd, bh),
+        lambda: scan.gru_scan(gi, h0, torch.randn(3 * H, H + 1, device=dev), bh),
+        lambda: scan.gru_scan_persistent(gi, torch.zeros(B + 1, H, device=dev), Wd, bh),
+        lambda: scan_diagonal.gru_scan_diagonal(gi, h0, torch.randn(3, H + 1, device=dev), bh),
+        lambda: scan_monarch.gru_scan_monarch(gi, h0, torch.randn(3, 2, 5, 5, device=dev), bh),
+        lambda: scan_butterfly.gru_scan_butterfly_triton(gi, torch.zeros(B + 1, H, device=dev),
+                                                         torch.randn(3, 1, 3, 4, 2, 2, device=dev), bh),
+        lambda: scan.gru_scan(gi, h0, Wd, bh, h_in_quant=(0.0, -127, 127)),
+    ]
+    for f in bad:
+        with pytest.raises((ValueError, RuntimeError)) as e:
+            f()
+        assert not isinstance(e.value, AssertionError)
+
+
+def _recipe(hidden_bits=32, mode="frozen"):
+    from gru_triton_b200 import QuantizerConfig, QuantRecipe
+    return QuantRecipe(weight=QuantizerConfig(bits=32, axis=0, name="W"),
+                       input_act=QuantizerConfig(bits=32, name="x_id"),
+                       hidden=QuantizerConfig(bits=hidden_bits, mode=mode, name="h"))
+
+
+@pytest.mark.parametrize("kind", ["diagonal", "monarch", "butterfly"])
+def test_layer_fast_dispatch_matches_per_step_path(kind):
+    """GRULayer on CUDA (one GEMM + one scan launch) against the same layer stepping on CPU."""
+    import copy
+    from gru_triton_b200 import GRULayer, StructureConfig
+    torch.manual_seed(11)
+    T, B, H = 12, 5, 64
+    lay = GRULayer(H, H, _recipe(), gate_layout="fused", structure_hidden=StructureConfig(kind=kind, nblocks=4))
+    x, h0 = torch.randn(T, B, H), torch.randn(B, H) * 0.3
+    ref, ref_hT = lay(x, h0)
+    ref.sum().backward()
+    gl = copy.deepcopy(lay).cuda()
+    gl.zero_grad()
+    assert gl.use_triton
+    out, hT = gl(x.cuda(), h0.cuda())
+    out.sum().backward()
+    assert bool(((out.cpu() - ref).abs() <= FWD_TOL + FWD_TOL * ref.abs()).all())
+    assert torch.equal(hT, out[-1])
+    for (n, p), (_, q) in zip(lay.named_parameters(), gl.named_parameters()):
+        assert rel_err(q.grad.cpu(), p.grad) <= GRAD_TOL, n
+    # batch_first plumbing
+    from gru_triton_b200 import GRULayer as GL
+    bf = GL(H, H, _recipe(), batch_first=True, gate_layout="fused",
+            structure_hidden=StructureConfig(kind=kind, nblocks=4)).cuda()
+    bf.load_state_dict(gl.state_dict())
+    ob, _ = bf(x.cuda().transpose(0, 1).contiguous(), h0.cuda())
+    assert torch.equal(ob.transpose(0, 1), out)
+
+
+def test_calibrate_freeze_then_cuda_scan():
+    """calibrate() (per-step path) -> freeze() -> CUDA scan with the frozen int8 scales."""
+    import copy
+    from gru_triton_b200 import GRULayer, StructureConfig
+    torch.manual_seed(3)
+    T, B, H = 16, 6, 64
+    lay = GRULayer(H, H, _recipe(8, mode="dynamic"), gate_layout="fused",
+                   structure_hidden=StructureConfig(kind="diagonal")).cuda()
+    stats = lay.calibrate([torch.randn(T, B, H, device="cuda") for _ in range(3)], n_batches=3)
+    assert stats["cell.quant_h_in"]["initialized"] and lay.use_triton
+    lay.freeze()
+    x = torch.randn(T, B, H, device="cuda")
+    out, _ = lay(x)
+    cpu = copy.deepcopy(lay).cpu()
+    q_in = (float(cpu.cell.quant_h_in.scale), -127, 127)
+    q_out = (float(cpu.cell.quant_h_out.scale), -127, 127)
+    from gru_triton_b200.scan_diagonal import extract_diagonal_factors
+    Wi, bi = cpu.cell.quantize_input_weights()
+    gi = torch.nn.functional.linear(x, Wi.cuda(), bi.cuda()).cpu()
+    W, bh = extract_diagonal_factors(cpu.cell)
+    check_forward("diagonal", out.detach(), gi, torch.zeros(B, H), W.detach(), bh.detach(), (q_in, q_out))
+
+
+def test_baseline_config_shapes_forward_backward():
+    """The benchmark shapes themselves: C1 dense (full), C3 monarch (full), C4 butterfly and
+    C2 diagonal (full launch on the device, oracle on a slice of the independent batch rows)."""
+    cases = [("dense", 64, 32, 512, {}, None, 32), ("monarch", 64, 32, 512, {"nblocks": 8}, Q8, 32),
+             ("butterfly", 128, 64, 1024, {}, None, 4), ("diagonal", 1024, 256, 1024, {}, Q8, 2)]
+    for kind, T, B, H, extra, quant, bsub in cases:
+        fwd, bwd, _ = _mods()[kind]
+        gi, h0, W, bh, dout = orc.make_problem(kind, T, B, H, seed=1, h0_scale=0.1, **extra)
+        kw = dict(h_in_quant=quant[0], h_out_quant=quant[1]) if quant else {}
+        d = _cuda(gi, h0, W, bh, dout)
+        out = fwd(*d[:4], **kw)
+        check_forward(kind, out[:, :bsub], gi[:, :bsub], h0[:bsub], W, bh, quant)
+        if kind == "diagonal":
+            continue                                    # C2 is forward only
+        grads = bwd(*d[:4], out, d[4], **kw)
+        sub = bwd(d[0][:, :bsub].contiguous(), d[1][:bsub].contiguous(), d[2], d[3], out[:, :bsub].contiguous(),
+                  d[4][:, :bsub].contiguous(), **kw)
+        assert torch.equal(sub[0], grads[0][:, :bsub]) and torch.equal(sub[1], grads[1][:bsub])
+        check_backward(kind, sub, gi[:, :bsub], h0[:bsub], W, bh, out[:, :bsub], dout[:, :bsub], quant)
