@@ -1,0 +1,454 @@
+#!/usr/bin/env python
+"""Benchmark of the persistent GRU scan on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--config c1|c2|c3|c4|c5] [--impl reference]
+
+Default workload (every N): BASELINE config 1 -- dense fp32 train step at T=64, B=32 per
+GPU, I=H=512: input projection (cuBLAS, as the reference does), the CUDA scan forward,
+loss = out.sum(), scan backward + weight-gradient GEMMs, input-side gradients.  With N > 1
+each rank runs its own batch (weak scaling) and the weight gradients are all-reduced once
+per step over NCCL.  Metric: sequence-steps/s = T*B*N / step time.
+
+One JSON line on stdout (rank 0).  `--impl reference` times the CPU port of the reference's
+per-step path (oracle/) on the host cores instead.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+import torch
+
+REPO = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, REPO)
+
+Q8 = 0.02   # placeholder scale replaced by calibration where a config asks for int8 hidden state
+
+CONFIGS = {
+    # name: kind, T, B (per GPU for c1-c4; TOTAL for c5), H, quant, train, extras
+    "c1": dict(kind="dense", T=64, B=32, H=512, quant=False, train=True, wbits=32, h0_scale=0.0,
+               desc="dense fp32 train step T=64 B=32/GPU I=H=512"),
+    "c2": dict(kind="diagonal", T=1024, B=256, H=1024, quant=True, train=False, wbits=32, h0_scale=0.0,
+               desc="diagonal int8-hidden forward T=1024 B=256 I=H=1024"),
+    "c3": dict(kind="monarch", T=64, B=32, H=512, quant=True, train=True, wbits=32, h0_scale=0.1, nblocks=8,
+               desc="block-diagonal (monarch, 8x64x64 per gate) int8-hidden train step T=64 B=32 I=H=512"),
+    "c4": dict(kind="butterfly", T=128, B=64, H=1024, quant=False, train=True, wbits=32, h0_scale=0.0,
+               desc="butterfly fp32 train step T=128 B=64 I=H=1024"),
+    "c5": dict(kind="dense", T=512, B=4096, H=1024, quant=True, train=True, wbits=8, h0_scale=0.0,
+               desc="dense int8-weight int8-hidden train step T=512 B=4096 total I=H=1024, batch-sharded"),
+}
+
+
+# ---------------------------------------------------------------------------
+# synthetic problem (same generator on every rank, rank-specific data seed)
+# ---------------------------------------------------------------------------
+
+def make_params(cfg, seed=0):
+    from oracle import gru_scan_oracle as orc      # generator only (shapes/distributions), not on the timed path
+    gen = torch.Generator().manual_seed(seed)
+    H = cfg["H"]
+    kind = cfg["kind"]
+    k = H ** -0.5
+
+    def U(*shape, a):
+        return (torch.rand(*shape, generator=gen) * 2 - 1) * a
+
+    if cfg is CONFIGS["c2"]:
+        W, bh = U(3, H, a=1.0), torch.zeros(3 * H)
+        Wi, bi = U(3 * H, H, a=1 / 32), torch.zeros(3 * H)
+    elif cfg is CONFIGS["c3"]:
+        W = torch.randn(3, 8, 64, 64, generator=gen) * 64 ** -0.5
+        bh, Wi, bi = U(3 * H, a=k), U(3 * H, H, a=k), U(3 * H, a=k)
+    elif cfg is CONFIGS["c4"]:
+        W = U(3, 1, 10, 512, 2, 2, a=2 ** -0.5)
+        bh, Wi, bi = U(3 * H, a=k), U(3 * H, H, a=k), U(3 * H, a=k)
+    elif cfg is CONFIGS["c5"]:
+        W, bh, Wi, bi = U(3 * H, H, a=1 / 32), U(3 * H, a=1 / 32), U(3 * H, H, a=1 / 32), U(3 * H, a=1 / 32)
+    else:
+        W, _ = orc.make_weights(kind, H, gen, nblocks=cfg.get("nblocks", 4))
+        bh, Wi, bi = U(3 * H, a=k), U(3 * H, H, a=k), U(3 * H, a=k)
+    return dict(W=W, bh=bh, Wi=Wi, bi=bi)
+
+
+def calibrated_scale(cfg, params):
+    """s = max|h| / 127 from an fp32 forward on a separate seeded batch of 8 sequences
+    (a short prefix of T keeps this cheap; h is bounded by 1 anyway)."""
+    from oracle import gru_scan_oracle as orc
+    gen = torch.Generator().manual_seed(1234)
+    T = min(cfg["T"], 32)
+    x = torch.randn(T, 8, cfg["H"], generator=gen)
+    gi = torch.nn.functional.linear(x, params["Wi"], params["bi"])
+    out = orc.scan_forward(cfg["kind"], gi, torch.zeros(8, cfg["H"]), params["W"], params["bh"])
+    return float(out.abs().max()) / 127.0
+
+
+def per_row_fake_quant(Wm, bits=8):
+    qmax = 2 ** (bits - 1) - 1
+    s = Wm.abs().amax(dim=1, keepdim=True).clamp(min=1e-8) / qmax
+    return torch.round(Wm / s).clamp(-qmax, qmax) * s
+
+
+# ---------------------------------------------------------------------------
+# device arm
+# ---------------------------------------------------------------------------
+
+class DeviceWorkload:
+    def __init__(self, name, cfg, rank, world, dev):
+        from gru_triton_b200 import scan, scan_butterfly, scan_diagonal, scan_monarch
+        self.cfg, self.name, self.rank, self.world, self.dev = cfg, name, rank, world, dev
+        kind = cfg["kind"]
+        self.T, self.H = cfg["T"], cfg["H"]
+        self.B = cfg["B"] // world if name == "c5" else cfg["B"]
+        self.fn = {"dense": scan.gru_scan_persistent, "diagonal": scan_diagonal.gru_scan_diagonal,
+                   "monarch": scan_monarch.gru_scan_monarch,
+                   "butterfly": scan_butterfly.gru_scan_butterfly_triton}[kind]
+        self.fwd_only = {"dense": scan.gru_scan_forward_persistent,
+                         "diagonal": scan_diagonal.gru_scan_diagonal_forward_triton,
+                         "monarch": scan_monarch.gru_scan_monarch_forward_triton,
+                         "butterfly": scan_butterfly.gru_scan_butterfly_forward_triton}[kind]
+        p = make_params(cfg)
+        self.quant = None
+        if cfg["quant"]:
+            s = calibrated_scale(cfg, p)
+            self.quant = ((s, -127, 127), (s, -127, 127))
+        self.P = {k: v.to(dev).requires_grad_(cfg["train"]) for k, v in p.items()}
+        gen = torch.Generator().manual_seed(100 + rank)
+        self.x_host = torch.randn(self.T, self.B, self.H, generator=gen).pin_memory()
+        self.h0_host = (torch.randn(self.B, self.H, generator=gen) * cfg["h0_scale"]).pin_memory()
+        self.x = self.x_host.to(dev)
+        self.h0 = self.h0_host.to(dev)
+        self.bucket = None
+
+    # -- one pass of the hot path ------------------------------------------
+    def _weights(self):
+        P = self.P
+        Wi, W = P["Wi"], P["W"]
+        if self.cfg["wbits"] < 32:
+            # dynamic per-output-row int8 weight fake-quant; straight-through gradient
+            Wi = Wi + (per_row_fake_quant(Wi.detach()) - Wi.detach())
+            W = W + (per_row_fake_quant(W.detach()) - W.detach())
+        return Wi, W
+
+    def step(self, x, h0):
+        P = self.P
+        kw = dict(h_in_quant=self.quant[0], h_out_quant=self.quant[1]) if self.quant else {}
+        if not self.cfg["train"]:
+            with torch.no_grad():
+                gi = torch.nn.functional.linear(x, P["Wi"], P["bi"])
+                return self.fn(gi, h0, P["W"], P["bh"], **kw)
+        for v in P.values():
+            v.grad = None
+        Wi, W = self._weights()
+        gi = torch.nn.functional.linear(x, Wi, P["bi"])
+        out = self.fn(gi, h0, W, P["bh"], **kw)
+        loss = out.sum()
+        loss.backward()
+        if self.world > 1:
+            import torch.distributed as dist
+            grads = [P[k].grad for k in ("W", "Wi", "bh", "bi")]
+            flat = torch.cat([g.reshape(-1) for g in grads])
+            dist.all_reduce(flat)
+        return loss
+
+    def scan_only_forward(self):
+        """The dominant kernel in isolation (one launch): forward scan on resident gi."""
+        P = self.P
+        kw = dict(h_in_quant=self.quant[0], h_out_quant=self.quant[1]) if self.quant else {}
+        with torch.no_grad():
+            if not hasattr(self, "_gi"):
+                self._gi = torch.nn.functional.linear(self.x, P["Wi"], P["bi"])
+            return self.fwd_only(self._gi, self.h0, P["W"], P["bh"], **kw)
+
+    def units(self):
+        return self.T * self.B
+
+    def scan_fwd_bytes(self):
+        return 16 * self.H * self.T * self.B      # gi read 12H + out write 4H per sequence-step
+
+
+class ClockSampler:
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.path = tempfile.mktemp(suffix=".csv")
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-i", str(gpu_index), "-lms", "100"],
+                stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in open(self.path):
+            f = [c.strip() for c in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for nm, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(nm)
+        os.unlink(self.path)
+        # samples under load = the upper half of the observed clocks
+        sm_sorted = sorted(sm)
+        load = sm_sorted[len(sm_sorted) // 2:] if sm_sorted else []
+        return {"sm_mhz": statistics.median(load) if load else None,
+                "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def timed_loop(fn, steps, warmup, flush, sync_all):
+    """W untimed + K timed calls; each timed call has its own CUDA-event pair on the
+    current stream and is preceded by an (untimed) L2 flush.  Returns per-step ms list."""
+    for _ in range(warmup):
+        flush()
+        fn()
+    sync_all()
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    for a, b in evs:
+        flush()
+        a.record()
+        fn()
+        b.record()
+    sync_all()
+    return [a.elapsed_time(b) for a, b in evs]
+
+
+def run_device(args):
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.gpus != world:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("launch multi-GPU runs with torch.distributed.run (one process per GPU)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    from gru_triton_b200 import _lib
+    cfg = CONFIGS[args.config]
+    wl = DeviceWorkload(args.config, cfg, rank, world, dev)
+    flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def flush():
+        flush_buf.zero_()
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def max_over_ranks(ms):
+        if world == 1:
+            return ms
+        t = torch.tensor(ms, device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.tolist()
+
+    sampler = ClockSampler(local) if rank == 0 else None
+
+    # ---- (1) kernel-resident: inputs already in HBM ---------------------------------
+    n0 = _lib.launch_count()
+    ms = timed_loop(lambda: wl.step(wl.x, wl.h0), args.steps, args.warmup, flush, sync_all)
+    launches_per_step = (_lib.launch_count() - n0) / (args.steps + args.warmup)
+    ms = max_over_ranks(ms)
+    ms_per_step = sum(ms) / len(ms)
+
+    # ---- (2) end to end: pinned host -> device copy in, loss (or last h) read back -----
+    def e2e_step():
+        x = wl.x_host.to(dev, non_blocking=True)
+        h0 = wl.h0_host.to(dev, non_blocking=True)
+        r = wl.step(x, h0)
+        return (r if r.dim() == 0 else r[-1, 0, 0]).item()
+
+    ms_e2e = timed_loop(e2e_step, args.steps, args.warmup, flush, sync_all)
+    ms_e2e = max_over_ranks(ms_e2e)
+    e2e_ms = sum(ms_e2e) / len(ms_e2e)
+
+    # ---- (3) the dominant kernel alone (forward scan), for the roofline --------------
+    n1 = _lib.launch_count()
+    ks = timed_loop(wl.scan_only_forward, max(args.steps, 10), 3, flush, sync_all)
+    scan_launches = (_lib.launch_count() - n1) / (max(args.steps, 10) + 3)
+    k_ms = statistics.median(ks)
+    clocks = sampler.stop() if sampler else None
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peaks = {}
+    ppath = os.path.join(REPO, "MEASURED_PEAKS.json")
+    if os.path.exists(ppath):
+        peaks = json.load(open(ppath))
+    peak_gbs = float(peaks.get("hbm_gbs", 6650.0))
+    achieved = wl.scan_fwd_bytes() / (k_ms * 1e-3) / 1e9
+
+    units = wl.units() * world
+    line = {
+        "metric": "sequence-steps/sec (T*B/s)", "value": units / (ms_per_step * 1e-3), "unit": "seq-steps/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
+        "higher_is_better": True, "scaling": "strong" if args.config == "c5" else "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"{args.config}: {cfg['desc']}", "T": wl.T, "B_per_gpu": wl.B, "H": wl.H,
+                   "hidden_kind": cfg["kind"], "int8_hidden": bool(cfg["quant"]), "weight_bits": cfg["wbits"],
+                   "train_step": bool(cfg["train"]), "parallelism": f"batch-shard x{world}" if world > 1 else "1 GPU",
+                   "l2": "256 MiB buffer written between timed steps (outside the timed events)"},
+        "e2e": {"value": units / (e2e_ms * 1e-3), "unit": "seq-steps/s", "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": wl.x_host.numel() * 4 + wl.h0_host.numel() * 4,
+                "d2h_bytes_per_step": 4},
+        "gpu_launches": int(round(launches_per_step * args.steps)),
+        "gpu_launches_per_step": launches_per_step,
+        "clocks": clocks,
+        "roofline": {"kernel": {"dense": "block_fwd_kernel", "monarch": "block_fwd_kernel",
+                                "diagonal": "diag_fwd_kernel", "butterfly": "bfly_fwd_kernel"}[cfg["kind"]],
+                     "bound": "hbm", "achieved": achieved, "peak": peak_gbs, "unit": "GB/s",
+                     "frac": achieved / peak_gbs, "peak_source": "measured" if peaks else "fallback",
+                     "traffic": None, "launch_ms": k_ms, "per_step_us": k_ms * 1e3 / wl.T,
+                     "launches_per_call": scan_launches,
+                     "algorithmic_bytes_per_launch": wl.scan_fwd_bytes()},
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_baseline(args.config, budget_s=15.0)
+    if args.kinds and world == 1 and args.config == "c1":
+        line["kinds"] = kinds_table(dev, flush, sync_all)
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def kinds_table(dev, flush, sync_all):
+    """ms/iter of a train step at the headline shape (T=64, B=32, H=512) per hidden kind."""
+    out = {}
+    for name, cfgname in (("dense", "c1"), ("monarch_nb8_int8h", "c3")):
+        wl = DeviceWorkload(cfgname, CONFIGS[cfgname], 0, 1, dev)
+        ms = timed_loop(lambda: wl.step(wl.x, wl.h0), 20, 3, flush, sync_all)
+        out[name] = {"ms_per_iter": statistics.median(ms), "seq_steps_per_s": wl.units() / (statistics.median(ms) * 1e-3)}
+    for name, kind in (("diagonal", "diagonal"), ("butterfly", "butterfly")):
+        cfg = dict(CONFIGS["c1"], kind=kind)
+        wl = DeviceWorkload("c1", cfg, 0, 1, dev)
+        ms = timed_loop(lambda: wl.step(wl.x, wl.h0), 20, 3, flush, sync_all)
+        out[name] = {"ms_per_iter": statistics.median(ms), "seq_steps_per_s": wl.units() / (statistics.median(ms) * 1e-3)}
+    return out
+
+
+# ---------------------------------------------------------------------------
+# CPU arm: the oracle's port of the reference's per-step PyTorch path
+# ---------------------------------------------------------------------------
+
+def cpu_problem(name):
+    """Bounded sample of the workload for the CPU: full C1/C3; a batch slice of the others."""
+    cfg = CONFIGS[name]
+    B = {"c1": 32, "c2": 8, "c3": 32, "c4": 8, "c5": 4}[name]
+    T = {"c1": 64, "c2": 256, "c3": 64, "c4": 32, "c5": 64}[name]
+    sample = (f"T={T}, B={B} of T={cfg['T']}, B={cfg['B']} (sequences and steps are independent units; "
+              "throughput per sequence-step)") if (T, B) != (cfg["T"], cfg["B"]) else "the full workload"
+    return cfg, T, B, sample
+
+
+def cpu_step_fn(name):
+    from oracle import gru_scan_oracle as orc
+    cfg, T, B, sample = cpu_problem(name)
+    p = make_params(cfg)
+    quant = None
+    if cfg["quant"]:
+        s = calibrated_scale(cfg, p)
+        quant = ((s, -127, 127), (s, -127, 127))
+    gen = torch.Generator().manual_seed(100)
+    x = torch.randn(T, B, cfg["H"], generator=gen)
+    h0 = torch.randn(B, cfg["H"], generator=gen) * cfg["h0_scale"]
+    qi, qo = quant if quant else (None, None)
+
+    def step():
+        orc.layer_train_step(cfg["kind"], x, h0, p["Wi"], p["bi"], p["W"], p["bh"], qi, qo,
+                             weight_bits=cfg["wbits"], backward=cfg["train"])
+    return step, T * B, sample
+
+
+def cpu_baseline(name, budget_s):
+    torch.set_num_threads(os.cpu_count() or 1)
+    step, units, sample = cpu_step_fn(name)
+    step()
+    t0 = time.perf_counter()
+    n = 0
+    while True:
+        step()
+        n += 1
+        if time.perf_counter() - t0 > budget_s or n >= 50:
+            break
+    dt = (time.perf_counter() - t0) / n
+    return {"value": units / dt, "unit": "seq-steps/s", "cores": torch.get_num_threads(), "kind": "port",
+            "ms_per_step": dt * 1e3, "sample": f"{sample}; {n} timed passes of oracle.layer_train_step"}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cfg = CONFIGS[args.config]
+    torch.set_num_threads(os.cpu_count() or 1)
+    step, units, sample = cpu_step_fn(args.config)
+    for _ in range(args.warmup):
+        step()
+    times = []
+    for _ in range(args.steps):
+        t0 = time.perf_counter()
+        step()
+        times.append(time.perf_counter() - t0)
+    dt = sum(times) / len(times)
+    v = units / dt
+    print(json.dumps({
+        "impl": "reference", "metric": "sequence-steps/sec (T*B/s)", "value": v, "unit": "seq-steps/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
+        "higher_is_better": True, "scaling": "strong" if args.config == "c5" else "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"{args.config}: {cfg['desc']}", "hidden_kind": cfg["kind"]},
+        "cpu_baseline": {"value": v, "unit": "seq-steps/s", "cores": torch.get_num_threads(), "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": v, "unit": "seq-steps/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--config", default="c1", choices=sorted(CONFIGS))
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-kinds", dest="kinds", action="store_false")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_device(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -493,6 +493,28 @@ static DeviceInfo device_info() {
   return d;
 }
 
+// Once per (device, kernel): allow the full opt-in shared memory and 16-CTA clusters.  The
+// attributes are per function, so they are set to the maximum any configuration may need
+// instead of per launch (a smaller later value would otherwise undo a larger earlier one).
+static cudaError_t prepare_kernel(KernelFn fn) {
+  static std::mutex mu;
+  static std::map<std::pair<int, const void*>, cudaError_t> done;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  std::lock_guard<std::mutex> lk(mu);
+  auto key = std::make_pair(dev, (const void*)fn);
+  auto it = done.find(key);
+  if (it != done.end()) return it->second;
+  const DeviceInfo di = device_info();
+  cudaError_t e = cudaFuncSetAttribute((const void*)fn, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)di.smem_optin);
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute((const void*)fn, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+  if (e != cudaSuccess) cudaGetLastError();
+  done[key] = e;
+  return e;
+}
+
 // How many clusters of this shape the device can hold at once (0 = cannot launch).
 static int max_active_clusters(KernelFn fn, int C, size_t smem) {
   static std::mutex mu;
@@ -506,9 +528,7 @@ static int max_active_clusters(KernelFn fn, int C, size_t smem) {
     if (it != cache.end()) return it->second;
   }
   int n = 0;
-  cudaError_t e = cudaFuncSetAttribute((const void*)fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  if (e == cudaSuccess && C > 8)
-    e = cudaFuncSetAttribute((const void*)fn, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+  cudaError_t e = prepare_kernel(fn);
   if (e == cudaSuccess) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(C, 1, 1);
