@@ -348,6 +348,8 @@ const char* b200gru_strerror(int status) {
     case B200GRU_UNSUPPORTED: return "shape not supported by this build or device";
     case B200GRU_LAUNCH_FAILURE: return "kernel launch failed";
     case B200GRU_WORKSPACE_TOO_SMALL: return "workspace too small";
+    case B200GRU_SCRATCH_EXCEEDED:
+      return "problem needs more scratch than the library's built-in buffer (B200GRU_NOALLOC_SCRATCH_BYTES)";
     default: return "unknown status";
   }
 }

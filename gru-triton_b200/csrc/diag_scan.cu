@@ -12,6 +12,8 @@
 // Follows the step arithmetic of src/gru_qat/triton_kernels/scan_diagonal.py
 // (forward :79-124, backward :564-647).
 
+#include <mutex>
+
 #include "common.cuh"
 
 namespace b200gru {
@@ -335,4 +337,54 @@ int diag_backward(const float* gi, const float* h0, const float* W, const float*
   return check_launch("reduce_partials");
 }
 
+// ---------------------------------------------------------------------------
+// backward without caller scratch
+// ---------------------------------------------------------------------------
+// Some hosts of this library may not allocate device memory at all: a plugin that runs
+// inside another runtime's memory budget, or a caller on a path where cudaMalloc is
+// off limits (it synchronises the device and can fail under memory pressure).  For them
+// the partial-sum scratch of the diagonal backward lives in this fixed array.  Every
+// process that loads the library pays for it on each GPU it touches, until exit.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[B200GRU_NOALLOC_SCRATCH_BYTES];
+
+// The array's name is only a host-side handle; kernels need its device address, which
+// differs per GPU.  Looked up once per device (with that device current) and cached in a
+// fixed table -- no allocation anywhere on this path.
+static int noalloc_scratch_address(float** out) {
+  constexpr int MAX_DEV = 64;
+  static std::mutex mu;
+  static float* table[MAX_DEV] = {nullptr};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEV) return B200GRU_LAUNCH_FAILURE;
+  std::lock_guard<std::mutex> lk(mu);
+  if (table[dev] == nullptr) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_noalloc_scratch) != cudaSuccess || p == nullptr) return check_launch("cudaGetSymbolAddress");
+    table[dev] = static_cast<float*>(p);
+  }
+  *out = table[dev];
+  return B200GRU_OK;
+}
+
 }  // namespace b200gru
+
+extern "C" int b200gru_diagonal_backward_noalloc(const float* gi, const float* h0, const float* Wh_diag,
+                                                 const float* bh_cat, const float* out, const float* dout,
+                                                 int T, int B, int H, const b200gru_quant* q_in,
+                                                 const b200gru_quant* q_out, float* dgi, float* dh0,
+                                                 float* dWh_diag, float* dbh, void* stream) {
+  using namespace b200gru;
+  if (!gi || !h0 || !Wh_diag || !bh_cat || !out || !dout || !dgi || !dh0 || !dWh_diag || !dbh)
+    return B200GRU_INVALID_ARGUMENT;
+  if (T <= 0 || B <= 0 || H <= 0) return B200GRU_INVALID_ARGUMENT;
+  if (q_in && q_in->enabled && !(q_in->scale > 0.f)) return B200GRU_INVALID_ARGUMENT;
+  if (q_out && q_out->enabled && !(q_out->scale > 0.f)) return B200GRU_INVALID_ARGUMENT;
+  if (diag_bwd_workspace_bytes(T, B, H) > (size_t)B200GRU_NOALLOC_SCRATCH_BYTES) return B200GRU_SCRATCH_EXCEEDED;
+  float* scratch = nullptr;
+  const int rc = noalloc_scratch_address(&scratch);
+  if (rc) return rc;
+  // Every element of the scratch that the reduction reads is first written by this call's
+  // backward kernel, so nothing has to be cleared; what an earlier call left is ignored.
+  return diag_backward(gi, h0, Wh_diag, bh_cat, out, dout, dgi, dh0, dWh_diag, dbh, scratch, T, B, H,
+                       make_quant(q_in), make_quant(q_out), static_cast<cudaStream_t>(stream));
+}

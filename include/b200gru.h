@@ -31,7 +31,8 @@ typedef enum {
   B200GRU_INVALID_ARGUMENT = 1,   /* NULL pointer, non-positive size, bad shape relation   */
   B200GRU_UNSUPPORTED = 2,        /* shape outside what this build can run                  */
   B200GRU_LAUNCH_FAILURE = 3,     /* cudaGetLastError() != cudaSuccess after a launch       */
-  B200GRU_WORKSPACE_TOO_SMALL = 4 /* workspace_bytes < b200gru_workspace_bytes(...)         */
+  B200GRU_WORKSPACE_TOO_SMALL = 4, /* workspace_bytes < b200gru_workspace_bytes(...)        */
+  B200GRU_SCRATCH_EXCEEDED = 5    /* problem too large for the built-in scratch of a _noalloc call */
 } b200gru_status;
 
 typedef enum {
@@ -148,6 +149,25 @@ int b200gru_butterfly_backward(const float* gi, const float* h0, const float* tw
                                const b200gru_quant* q_in, const b200gru_quant* q_out,
                                float* dgi, float* dh0, float* dtwiddles, float* dbh,
                                void* workspace, size_t workspace_bytes, void* stream);
+
+/* Diagonal backward for callers that cannot allocate device memory.  It has no counterpart in
+ * the reference (whose wrappers always allocate their scratch with torch).  Same inputs, outputs
+ * and results as b200gru_diagonal_backward, but no workspace argument: the partial sums go into a
+ * buffer of B200GRU_NOALLOC_SCRATCH_BYTES built into the library (held on every GPU the process
+ * uses, for the life of the process).  Meant for hosts that run under someone else's memory
+ * budget or on a path where cudaMalloc is forbidden; the call itself performs no allocation.
+ *  - Limit: ceil(B/4) * 6 * H * 4 bytes must fit the buffer (e.g. B=256, H=1024 needs 1.5 MiB);
+ *    larger problems return B200GRU_SCRATCH_EXCEEDED and launch nothing.
+ *  - The first call on each device looks up the buffer's device address; make that first call
+ *    outside any stream capture.
+ *  - All calls share the one buffer per device.  Nothing needs clearing between calls, but two
+ *    calls that overlap on the GPU (different streams) race on it: serialise them. */
+#define B200GRU_NOALLOC_SCRATCH_BYTES (4u << 20)
+int b200gru_diagonal_backward_noalloc(const float* gi, const float* h0, const float* Wh_diag,
+                                      const float* bh_cat, const float* out, const float* dout,
+                                      int T, int B, int H, const b200gru_quant* q_in,
+                                      const b200gru_quant* q_out, float* dgi, float* dh0,
+                                      float* dWh_diag, float* dbh, void* stream);
 
 /* Number of kernels the library has launched in this process since it was loaded
  * (all streams).  Used by the benchmark to report its launch count; no reference
