@@ -92,7 +92,7 @@ static size_t workspace_bytes(const Dims& d, int backward) {
   switch (d.kind) {
     case B200GRU_DENSE:
     case B200GRU_MONARCH:
-      if (!backward) return align_up(d.w_elems * sizeof(float), 256);
+      if (!backward) return align_up((size_t)3 * d.nb * d.Hb * transposed_row_bound(d.Hb) * sizeof(float), 256);
       return s_bytes(d) + weight_grads_scratch_bytes(d.T, d.B, d.H, d.nb, d.Hb);
     case B200GRU_DIAGONAL:
       return backward ? diag_bwd_workspace_bytes(d.T, d.B, d.H) : 0;
@@ -162,7 +162,7 @@ int b200gru_scan_forward(const b200gru_shape* shape, const float* gi, const floa
       a.qin = qi; a.qout = qo;
       if (!cfg.w_in_smem) {
         float* Wt = static_cast<float*>(workspace);
-        int rc = launch_transpose_weights(W, Wt, d.nb, d.Hb, d.gate_stride, d.block_stride, st);
+        int rc = launch_transpose_weights(W, Wt, d.nb, d.Hb, cfg.Hb4 + 4, d.gate_stride, d.block_stride, st);
         if (rc) return rc;
         a.Wt = Wt;
       }

@@ -30,10 +30,10 @@ __device__ __forceinline__ float h_prev_at(const float* __restrict__ h0, const f
 }  // namespace
 
 // ---------------------------------------------------------------------------
-// W(g,n,o,k) -> Wt[((n*Hb + k)*3 + g)*Hb + o]
+// W(g,n,o,k) -> Wt[((n*Hb + k)*3 + g)*WtR + o], zero for o in [Hb, WtR)
 // ---------------------------------------------------------------------------
 __global__ void transpose_weights_kernel(const float* __restrict__ W, float* __restrict__ Wt, int nb,
-                                         int Hb, long long gs, long long bs) {
+                                         int Hb, int WtR, long long gs, long long bs) {
   __shared__ float tile[32][33];
   const int gn = blockIdx.z;                 // g * nb + n
   const int g = gn / nb, n = gn - g * nb;
@@ -46,14 +46,14 @@ __global__ void transpose_weights_kernel(const float* __restrict__ W, float* __r
   __syncthreads();
   for (int r = threadIdx.y; r < 32; r += blockDim.y) {
     const int k = k0 + r, o = o0 + threadIdx.x;
-    if (k < Hb && o < Hb) Wt[(((size_t)n * Hb + k) * 3 + g) * Hb + o] = tile[threadIdx.x][r];
+    if (k < Hb && o < WtR) Wt[(((size_t)n * Hb + k) * 3 + g) * WtR + o] = tile[threadIdx.x][r];
   }
 }
 
-int launch_transpose_weights(const float* W, float* Wt, int nb, int Hb, long long gs, long long bs,
+int launch_transpose_weights(const float* W, float* Wt, int nb, int Hb, int WtR, long long gs, long long bs,
                              cudaStream_t st) {
-  dim3 grid(cdiv(Hb, 32), cdiv(Hb, 32), 3 * nb), block(32, 8);
-  transpose_weights_kernel<<<grid, block, 0, st>>>(W, Wt, nb, Hb, gs, bs);
+  dim3 grid(cdiv(Hb, 32), cdiv(WtR, 32), 3 * nb), block(32, 8);
+  transpose_weights_kernel<<<grid, block, 0, st>>>(W, Wt, nb, Hb, WtR, gs, bs);
   note_launch();
   return check_launch("transpose_weights_kernel");
 }

@@ -3,25 +3,30 @@
 // Both kinds are `nb` independent GRUs of width Hb (dense: nb = 1, Hb = H) sharing
 // gi / out.  Sequences are independent too, so the work splits into
 // (hidden block n) x (batch tile of BT rows) problems with no traffic between
-// them.  One thread-block CLUSTER of C CTAs owns one such problem for all T steps:
+// them.  One thread-block CLUSTER of C CTAs owns one such problem for all T steps.
+// CTA `rank` owns hidden units [rank*Hc, (rank+1)*Hc) of the block and keeps the rows
+// W(g, own unit, all k) of the weights resident in shared memory for the whole launch
+// (when that slice exceeds shared memory the same loops read a copy through L1/L2).
+// The recurrence never round-trips through HBM or L2; `out[t]` / `dgi[t]` are written
+// once, for the caller.  All arithmetic is FP32 FMA; every cross-thread sum has a fixed
+// order (bitwise reproducible run to run).
 //
-//   * CTA `rank` owns hidden units [rank*Hc, (rank+1)*Hc) of the block and keeps
-//     its slice of the weights resident in shared memory for the whole launch
-//     (forward: W[g, o in slice, all k], k-major;  backward: W[g, all o, k in slice]).
-//     When the slice does not fit (large H) the same loops read it through L1/L2.
-//   * every step the CTA needs the whole h_{t-1} (forward) or dgh_t (backward)
-//     vector of the block: each CTA publishes its own slice into the shared memory
-//     of all C peers (DSMEM stores), then one hardware cluster barrier ends the step.
-//     The recurrence never round-trips through HBM or L2; `out[t]` / `dgi[t]` are
-//     written once, for the caller.
-//   * the contraction itself is FP32 FMA: a warp owns 32 output columns x a K slice,
-//     partial sums meet in shared memory and are added in a fixed order (bitwise
-//     reproducible run to run).  At batch tiles this narrow the step is latency
-//     bound, not FLOP bound.
+// Forward step ("all-gather"):
+//   a warp owns 4 output units x 3 gates; its lanes split the contraction index k, each
+//   lane reading one float4 of weights per gate and the BT hidden values of its k; a
+//   halving shuffle reduction leaves lane (b, unit) with the three gate sums of its
+//   element, which then does the gate math in place.  Each CTA publishes its slice of
+//   fq_in(h_t) into the shared memory of all C peers (DSMEM float4 stores); one hardware
+//   cluster barrier ends the step.
 //
-// Only the matrix-vector products that sit ON the dependence chain run here.  The
-// gate recompute for the backward (one big GEMM over all t, since every h_t is
-// known) and the weight-gradient GEMM live in block_gemm.cu.
+// Backward step ("reduce-scatter"), only dh_via = dgh . W is on the dependence chain:
+//   gate gradients of the owned elements -> local partial products against the SAME
+//   weight rows, for all Hb input positions -> each CTA sends the part that belongs to
+//   peer r into r's receive buffer (DSMEM) -> cluster barrier -> the owner adds the C
+//   partials in rank order.
+//
+// The gate recompute for the backward (one big GEMM over all t, since every h_t is
+// known) and the weight-gradient GEMM are off the chain and live in block_gemm.cu.
 //
 // Step arithmetic follows src/gru_qat/triton_kernels/scan.py:1491-1550 and
 // scan_monarch.py:74-127, 955-1053.
@@ -45,26 +50,69 @@ namespace {
 constexpr int NT = BLOCK_SCAN_THREADS;   // threads per CTA
 constexpr int NW = NT / 32;
 
-template <int BT> struct HVec { float v[BT]; };
+__host__ __device__ constexpr int next_pow2(int x) { return x <= 1 ? 1 : (x <= 2 ? 2 : (x <= 4 ? 4 : 8)); }
 
+// BT consecutive floats (the batch rows of one k) from shared memory.
 template <int BT>
 __device__ __forceinline__ void load_rows(const float* p, float (&v)[BT]) {
-  if constexpr (BT == 1) {
-    v[0] = p[0];
-  } else if constexpr (BT == 2) {
-    float2 x = *reinterpret_cast<const float2*>(p);
-    v[0] = x.x; v[1] = x.y;
-  } else {
+  if constexpr (BT % 4 == 0) {
 #pragma unroll
     for (int q = 0; q < BT / 4; ++q) {
-      float4 x = *reinterpret_cast<const float4*>(p + 4 * q);
+      const float4 x = *reinterpret_cast<const float4*>(p + 4 * q);
       v[4 * q] = x.x; v[4 * q + 1] = x.y; v[4 * q + 2] = x.z; v[4 * q + 3] = x.w;
+    }
+  } else if constexpr (BT % 2 == 0) {
+#pragma unroll
+    for (int q = 0; q < BT / 2; ++q) {
+      const float2 x = *reinterpret_cast<const float2*>(p + 2 * q);
+      v[2 * q] = x.x; v[2 * q + 1] = x.y;
+    }
+  } else {
+#pragma unroll
+    for (int q = 0; q < BT; ++q) v[q] = p[q];
+  }
+}
+
+// Sum `vals` over the 32 lanes of the warp.  While more than one value is left, each
+// step hands half of them to the partner lane (lane ^ off), so the whole reduction costs
+// about N shuffles instead of 5N.  On return vals[0] holds the total of element
+// `reduced_index<N>(lane)`; lanes that end up with the same element hold the same total.
+template <int N>
+__device__ __forceinline__ void warp_reduce_scatter(float (&vals)[N], int lane) {
+  int n = N;
+#pragma unroll
+  for (int off = 16; off >= 1; off >>= 1) {
+    if (n > 1) {
+      const int half = n >> 1;
+      const bool upper = (lane & off) != 0;
+#pragma unroll
+      for (int i = 0; i < N / 2; ++i) {
+        if (i < half) {
+          const float send = upper ? vals[i] : vals[i + half];
+          const float keep = upper ? vals[i + half] : vals[i];
+          vals[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+        }
+      }
+      n = half;
+    } else {
+      vals[0] += __shfl_xor_sync(0xffffffffu, vals[0], off);
     }
   }
 }
 
-// Publish `nfloats` contiguous floats (16-byte multiple) that this CTA just wrote at
-// local shared address `src` to the same address in every peer CTA of the cluster.
+template <int N>
+__device__ __forceinline__ int reduced_index(int lane) {
+  // N = 32 -> lane, 16 -> lane >> 1, 8 -> lane >> 2, 4 -> lane >> 3
+  return N >= 32 ? lane : (N == 16 ? lane >> 1 : (N == 8 ? lane >> 2 : lane >> 3));
+}
+template <int N>
+__device__ __forceinline__ bool reduced_owner(int lane) {
+  // one lane per element: the lowest of the group that shares it
+  return N >= 32 ? true : ((lane & ((32 / N) - 1)) == 0);
+}
+
+// Copy `nfloats` contiguous floats (a multiple of 4, 16-byte aligned) that this CTA just
+// wrote at local shared address `src` to the same address in every peer CTA.
 __device__ __forceinline__ void publish_to_peers(cg::cluster_group& cluster, float* src, int nfloats,
                                                  int C, int rank) {
   const int nvec = nfloats >> 2;
@@ -83,50 +131,52 @@ __device__ __forceinline__ void publish_to_peers(cg::cluster_group& cluster, flo
 // ---------------------------------------------------------------------------
 // forward
 // ---------------------------------------------------------------------------
-template <int BT, int GPT>
+// shared memory:  hbuf [2][HbP][BT]  fq_in(h) of the whole block, k-major
+//                 wsm  [Hb][RS]      W(g, u0+j, k) at [k][g*Hc4 + j]; RS = 4 (mod 8) floats so
+//                                    that float4 reads by lanes with consecutive k hit all banks
+template <int BT, int IPW>
 __global__ void __launch_bounds__(NT, 1)
 block_fwd_kernel(const BlockScanArgs a) {
   extern __shared__ __align__(16) float smem[];
   cg::cluster_group cluster = cg::this_cluster();
+  constexpr int BTP = next_pow2(BT);
+  constexpr int NV = 4 * BTP;                          // values per gate in the warp reduction
 
-  const int C = a.C, Hb = a.Hb, Hc = a.Hc, Hcp = a.Hcp, H = a.H;
+  const int C = a.C, Hb = a.Hb, Hc = a.Hc, Hc4 = a.Hc4, H = a.H, HbP = a.HbP;
   const int rank = blockIdx.x % C;
-  const int n = blockIdx.x / C;                       // hidden block
+  const int n = blockIdx.x / C;                        // hidden block
   const int b0 = blockIdx.y * BT;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int u0 = rank * Hc;                           // first owned unit (inside the block)
-  const int nown = max(0, min(Hc, Hb - u0));          // owned units
-  const int HbP = a.HbP;                              // Hb rounded so that C*Hc*BT slices stay 16B aligned
+  const int u0 = rank * Hc;                            // first owned unit (inside the block)
+  const int nown = max(0, min(Hc, Hb - u0));           // owned units
 
-  float* hbuf = smem;                                 // [2][HbP][BT]   fq_in(h), k-major
-  float* red = hbuf + 2 * HbP * BT;                   // [KS][3][BT][Hcp]
-  float* wsm = red + a.KS * 3 * BT * Hcp;             // [Hb][3*Hcp + 1]  (only if w_in_smem)
+  float* hbuf = smem;
+  float* wsm = hbuf + ((2 * HbP * BT + 3) & ~3);        // 16-byte aligned weight rows
 
-  // ---- weights: W(g, n, u0 + j, k)  ->  wsm[k][g*Hcp + j]
   const float* wbase;
   int kstride, gstride;
   if (a.w_in_smem) {
-    kstride = 3 * Hcp + 1;
-    gstride = Hcp;
+    kstride = a.RS;
+    gstride = Hc4;
     const float* Wn = a.W + (size_t)n * a.w_block_stride;
-    const int total = 3 * Hcp * Hb;
+    const int total = 3 * Hc4 * Hb;
     for (int idx = tid; idx < total; idx += NT) {
       const int k = idx % Hb;
       const int gj = idx / Hb;
-      const int g = gj / Hcp, j = gj - g * Hcp;
+      const int g = gj / Hc4, j = gj - g * Hc4;
       float v = 0.f;
       if (j < nown) v = Wn[(size_t)g * a.w_gate_stride + (size_t)(u0 + j) * Hb + k];
-      wsm[k * kstride + g * Hcp + j] = v;
+      wsm[k * kstride + g * Hc4 + j] = v;
     }
     wbase = wsm;
   } else {
-    // transposed global copy: Wt[((n*Hb + k)*3 + g)*Hb + u]
-    kstride = 3 * Hb;
-    gstride = Hb;
-    wbase = a.Wt + (size_t)n * Hb * 3 * Hb + u0;
+    // transposed global copy, rows padded with zeros: Wt[((n*Hb + k)*3 + g)*WtR + u]
+    kstride = 3 * a.WtR;
+    gstride = a.WtR;
+    wbase = a.Wt + (size_t)n * Hb * 3 * a.WtR + u0;
   }
 
-  // ---- h_{-1}: every CTA loads the whole block row itself
+  // h_{-1}: every CTA loads the whole block row itself
   for (int idx = tid; idx < HbP * BT; idx += NT) {
     const int k = idx / BT, b = idx - k * BT;
     float v = 0.f;
@@ -135,110 +185,119 @@ block_fwd_kernel(const BlockScanArgs a) {
     hbuf[HbP * BT + idx] = 0.f;
   }
 
-  // gate-phase ownership: item q of this thread is (b, j) = divmod(tid + q*NT, Hcp)
-  float hown[GPT], gr[GPT], gz[GPT], gn[GPT], bias_r[GPT], bias_z[GPT], bias_n[GPT];
-  bool valid[GPT];
-  int ib[GPT], ij[GPT];
+  // After the reduction lane `lane` owns element (b, c) = (ridx >> 2, ridx & 3) of every
+  // item (group of 4 units) its warp processes.
+  const int ridx = reduced_index<NV>(lane);
+  const int eb = ridx >> 2, ec = ridx & 3;
+  const bool eown = reduced_owner<NV>(lane) && eb < BT && (b0 + eb) < a.B;
+  const int nitems = Hc4 >> 2;
+
+  float hown[IPW], gr[IPW], gz[IPW], gn[IPW], bias_r[IPW], bias_z[IPW], bias_n[IPW];
+  bool valid[IPW];
 #pragma unroll
-  for (int q = 0; q < GPT; ++q) {
-    const int idx = tid + q * NT;
-    ib[q] = idx / Hcp;
-    ij[q] = idx - ib[q] * Hcp;
-    valid[q] = (idx < BT * Hcp) && (ij[q] < nown) && (b0 + ib[q] < a.B);
+  for (int q = 0; q < IPW; ++q) {
+    const int item = warp + q * NW;
+    const int j = item * 4 + ec;
+    valid[q] = eown && item < nitems && j < nown;
     hown[q] = 0.f; gr[q] = gz[q] = gn[q] = 0.f; bias_r[q] = bias_z[q] = bias_n[q] = 0.f;
     if (valid[q]) {
-      const int u = n * Hb + u0 + ij[q];
-      hown[q] = a.h0[(size_t)(b0 + ib[q]) * H + u];
+      const int u = n * Hb + u0 + j;
+      hown[q] = a.h0[(size_t)(b0 + eb) * H + u];
       bias_r[q] = a.bh[u]; bias_z[q] = a.bh[H + u]; bias_n[q] = a.bh[2 * H + u];
-      const float* g = a.gi + (size_t)(b0 + ib[q]) * 3 * H + u;
+      const float* g = a.gi + (size_t)(b0 + eb) * 3 * H + u;
       gr[q] = __ldcs(g); gz[q] = __ldcs(g + H); gn[q] = __ldcs(g + 2 * H);
     }
   }
   if (C > 1) cluster.sync(); else __syncthreads();
 
-  const int nct = Hcp / 32;
-  const int nitems = nct * a.KS;
-  const int Kper = (Hb + a.KS - 1) / a.KS;
   const size_t gi_step = (size_t)a.B * 3 * H;
   const size_t out_step = (size_t)a.B * H;
+  const size_t comp = (size_t)a.T * out_step;
 
   for (int t = 0; t < a.T; ++t) {
     const float* hcur = hbuf + (t & 1) * HbP * BT;
     float* hnxt = hbuf + ((t + 1) & 1) * HbP * BT;
 
-    // ---- gh partial sums: warp = (column tile, K slice)
-    for (int item = warp; item < nitems; item += NW) {
-      const int ct = item % nct, ks = item / nct;
-      const int j = ct * 32 + lane;
-      const int jr = (j < nown) ? j : 0;
-      const int k0 = ks * Kper, k1 = min(Hb, k0 + Kper);
-      float acc[3][BT];
 #pragma unroll
-      for (int g = 0; g < 3; ++g)
-#pragma unroll
-        for (int b = 0; b < BT; ++b) acc[g][b] = 0.f;
-      const float* wp = wbase + jr;
-#pragma unroll 4
-      for (int k = k0; k < k1; ++k) {
-        const float w0 = wp[(size_t)k * kstride];
-        const float w1 = wp[(size_t)k * kstride + gstride];
-        const float w2 = wp[(size_t)k * kstride + 2 * gstride];
-        float hv[BT];
-        load_rows<BT>(hcur + k * BT, hv);
-#pragma unroll
-        for (int b = 0; b < BT; ++b) {
-          acc[0][b] = fmaf(w0, hv[b], acc[0][b]);
-          acc[1][b] = fmaf(w1, hv[b], acc[1][b]);
-          acc[2][b] = fmaf(w2, hv[b], acc[2][b]);
+    for (int q = 0; q < IPW; ++q) {
+      const int item = warp + q * NW;
+      if (item < nitems) {                              // warp-uniform
+        // next step's gi goes in flight before the contraction
+        float ngr = 0.f, ngz = 0.f, ngn = 0.f;
+        if (valid[q] && t + 1 < a.T) {
+          const float* g = a.gi + (size_t)(t + 1) * gi_step + (size_t)(b0 + eb) * 3 * H + n * Hb + u0 + item * 4 + ec;
+          ngr = __ldcs(g); ngz = __ldcs(g + H); ngn = __ldcs(g + 2 * H);
         }
-      }
-#pragma unroll
-      for (int g = 0; g < 3; ++g)
-#pragma unroll
-        for (int b = 0; b < BT; ++b) red[((ks * 3 + g) * BT + b) * Hcp + j] = acc[g][b];
-    }
-    __syncthreads();
 
-    // ---- gates for the owned (b, j) items; next step's gi goes in flight first
-    float ngr[GPT], ngz[GPT], ngn[GPT];
+        float acc[3][4][BT];
 #pragma unroll
-    for (int q = 0; q < GPT; ++q) {
-      ngr[q] = ngz[q] = ngn[q] = 0.f;
-      if (valid[q] && t + 1 < a.T) {
-        const float* g = a.gi + (size_t)(t + 1) * gi_step + (size_t)(b0 + ib[q]) * 3 * H + n * Hb + u0 + ij[q];
-        ngr[q] = __ldcs(g); ngz[q] = __ldcs(g + H); ngn[q] = __ldcs(g + 2 * H);
-      }
-    }
+        for (int g = 0; g < 3; ++g)
 #pragma unroll
-    for (int q = 0; q < GPT; ++q) {
-      const int idx = tid + q * NT;
-      if (idx < BT * Hcp) {
-        float s0 = 0.f, s1 = 0.f, s2 = 0.f;
-        for (int ks = 0; ks < a.KS; ++ks) {
-          s0 += red[((ks * 3 + 0) * BT + ib[q]) * Hcp + ij[q]];
-          s1 += red[((ks * 3 + 1) * BT + ib[q]) * Hcp + ij[q]];
-          s2 += red[((ks * 3 + 2) * BT + ib[q]) * Hcp + ij[q]];
-        }
-        float hq = 0.f;
-        if (valid[q]) {
-          const float ghn = s2 + bias_n[q];
-          const GateOut g = gru_gates(gr[q], gz[q], gn[q], s0 + bias_r[q], s1 + bias_z[q], ghn, hown[q]);
-          const float hnew = a.qout.enabled ? fake_quant<true>(g.h_raw, a.qout) : g.h_raw;
-          hown[q] = hnew;
-          const size_t o = (size_t)t * out_step + (size_t)(b0 + ib[q]) * H + n * Hb + u0 + ij[q];
-          a.out[o] = hnew;
-          if (a.save != nullptr) {
-            const size_t comp = (size_t)a.T * out_step;
-            __stcs(a.save + o, g.r);
-            __stcs(a.save + comp + o, g.z);
-            __stcs(a.save + 2 * comp + o, g.n);
-            __stcs(a.save + 3 * comp + o, ghn);
+          for (int c = 0; c < 4; ++c)
+#pragma unroll
+            for (int b = 0; b < BT; ++b) acc[g][c][b] = 0.f;
+
+        const float* wp = wbase + item * 4;
+#pragma unroll 2
+        for (int k = lane; k < Hb; k += 32) {
+          float4 w[3];
+          if (a.w_in_smem) {
+#pragma unroll
+            for (int g = 0; g < 3; ++g) w[g] = *reinterpret_cast<const float4*>(wp + k * kstride + g * gstride);
+          } else {
+#pragma unroll
+            for (int g = 0; g < 3; ++g) {
+              const float* p = wp + (size_t)k * kstride + g * gstride;
+              w[g] = make_float4(__ldg(p), __ldg(p + 1), __ldg(p + 2), __ldg(p + 3));
+            }
           }
-          hq = a.qin.enabled ? fake_quant<true>(hnew, a.qin) : hnew;
+          float hv[BT];
+          load_rows<BT>(hcur + k * BT, hv);
+#pragma unroll
+          for (int g = 0; g < 3; ++g)
+#pragma unroll
+            for (int b = 0; b < BT; ++b) {
+              acc[g][0][b] = fmaf(w[g].x, hv[b], acc[g][0][b]);
+              acc[g][1][b] = fmaf(w[g].y, hv[b], acc[g][1][b]);
+              acc[g][2][b] = fmaf(w[g].z, hv[b], acc[g][2][b]);
+              acc[g][3][b] = fmaf(w[g].w, hv[b], acc[g][3][b]);
+            }
         }
-        if (ij[q] < Hc) hnxt[(u0 + ij[q]) * BT + ib[q]] = hq;
+
+        float s[3];
+#pragma unroll
+        for (int g = 0; g < 3; ++g) {
+          float vals[NV];
+#pragma unroll
+          for (int b = 0; b < BTP; ++b)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) vals[b * 4 + c] = (b < BT) ? acc[g][c][b < BT ? b : 0] : 0.f;
+          warp_reduce_scatter<NV>(vals, lane);
+          s[g] = vals[0];
+        }
+
+        const int j = item * 4 + ec;
+        if (eown && j < Hc) {
+          float hq = 0.f;
+          if (valid[q]) {
+            const float ghn = s[2] + bias_n[q];
+            const GateOut go = gru_gates(gr[q], gz[q], gn[q], s[0] + bias_r[q], s[1] + bias_z[q], ghn, hown[q]);
+            const float hnew = a.qout.enabled ? fake_quant<true>(go.h_raw, a.qout) : go.h_raw;
+            hown[q] = hnew;
+            const size_t o = (size_t)t * out_step + (size_t)(b0 + eb) * H + n * Hb + u0 + j;
+            a.out[o] = hnew;
+            if (a.save != nullptr) {
+              __stcs(a.save + o, go.r);
+              __stcs(a.save + comp + o, go.z);
+              __stcs(a.save + 2 * comp + o, go.n);
+              __stcs(a.save + 3 * comp + o, ghn);
+            }
+            hq = a.qin.enabled ? fake_quant<true>(hnew, a.qin) : hnew;
+          }
+          hnxt[(u0 + j) * BT + eb] = hq;
+        }
+        gr[q] = ngr; gz[q] = ngz; gn[q] = ngn;
       }
-      gr[q] = ngr[q]; gz[q] = ngz[q]; gn[q] = ngn[q];
     }
     if (C > 1) {
       __syncthreads();
@@ -253,66 +312,71 @@ block_fwd_kernel(const BlockScanArgs a) {
 // ---------------------------------------------------------------------------
 // backward (serial part): dgi[t], dh chain, dh0.  Gate activations come from `S`.
 // ---------------------------------------------------------------------------
-template <int BT, int GPT>
+// shared memory:  recv [2][C][Hc][BT]   partial dh_via sent by every rank (parity = step)
+//                 xs   [3][Hc4][BT]     dgh of the owned units
+//                 wsm  [3*Hc4][Hb4]     W(g, u0+j, k) at [(g*Hc4 + j)][k]   (k contiguous)
+// The second contraction half parks its sums in the idle parity half of `recv`.
+template <int BT, int TW, int GPT>
 __global__ void __launch_bounds__(NT, 1)
 block_bwd_kernel(const BlockScanArgs a) {
   extern __shared__ __align__(16) float smem[];
   cg::cluster_group cluster = cg::this_cluster();
 
-  const int C = a.C, Hb = a.Hb, Hc = a.Hc, Hcp = a.Hcp, H = a.H;
+  const int C = a.C, Hb = a.Hb, Hc = a.Hc, Hc4 = a.Hc4, H = a.H, HbP = a.HbP, Hb4 = a.Hb4;
   const int rank = blockIdx.x % C;
   const int n = blockIdx.x / C;
   const int b0 = blockIdx.y * BT;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int u0 = rank * Hc;
   const int nown = max(0, min(Hc, Hb - u0));
-  const int HbP = a.HbP;
-  const int K3 = 3 * HbP;                              // contraction length: (gate, unit)
+  const int slice = Hc * BT;                           // floats one rank sends to one peer
 
-  float* xbuf = smem;                                  // [2][3][HbP][BT]  dgh, k-major
-  float* red = xbuf + 2 * K3 * BT;                     // [KS][BT][Hcp]
-  float* wsm = red + a.KS * BT * Hcp;                  // [3][Hb][Hcp]
+  float* recv = smem;                                  // [2][C*slice]
+  float* xs = recv + 2 * C * slice;                    // [3*Hc4][BT]
+  float* wsm = xs + 3 * Hc4 * BT;
+  wsm += (4 - ((2 * C * slice + 3 * Hc4 * BT) & 3)) & 3;   // keep the weight rows 16-byte aligned
 
-  // ---- weights: W(g, n, o, u0 + j) -> wsm[(g*Hb + o)*Hcp + j]
   const float* wbase;
   size_t gstride;      // between gates
-  int ostride;         // between output units o
+  int rstride;         // between units
   if (a.w_in_smem) {
-    gstride = (size_t)Hb * Hcp;
-    ostride = Hcp;
+    gstride = (size_t)Hc4 * Hb4;
+    rstride = Hb4;
     const float* Wn = a.W + (size_t)n * a.w_block_stride;
-    const int total = 3 * Hb * Hcp;
+    const int total = 3 * Hc4 * Hb4;
     for (int idx = tid; idx < total; idx += NT) {
-      const int j = idx % Hcp;
-      const int go = idx / Hcp;
-      const int g = go / Hb, o = go - g * Hb;
+      const int k = idx % Hb4;
+      const int gj = idx / Hb4;
+      const int g = gj / Hc4, j = gj - g * Hc4;
       float v = 0.f;
-      if (j < nown) v = Wn[(size_t)g * a.w_gate_stride + (size_t)o * Hb + u0 + j];
+      if (j < nown && k < Hb) v = Wn[(size_t)g * a.w_gate_stride + (size_t)(u0 + j) * Hb + k];
       wsm[idx] = v;
     }
     wbase = wsm;
   } else {
     gstride = (size_t)a.w_gate_stride;
-    ostride = Hb;
-    wbase = a.W + (size_t)n * a.w_block_stride + u0;
+    rstride = Hb;
+    wbase = a.W + (size_t)n * a.w_block_stride + (size_t)u0 * Hb;
   }
-  for (int idx = tid; idx < 2 * K3 * BT; idx += NT) xbuf[idx] = 0.f;
+  for (int idx = tid; idx < 2 * C * slice; idx += NT) recv[idx] = 0.f;
+  for (int idx = tid; idx < 3 * Hc4 * BT; idx += NT) xs[idx] = 0.f;
 
   const size_t gi_step = (size_t)a.B * 3 * H;
   const size_t out_step = (size_t)a.B * H;
   const size_t comp = (size_t)a.T * out_step;
 
+  // element ownership for the gate phase: idx -> (j, b), b fastest so that `recv` reads are contiguous
   float dh_acc[GPT];
   float c_do[GPT], c_r[GPT], c_z[GPT], c_n[GPT], c_ghn[GPT], c_hp[GPT];
   bool valid[GPT];
   int ib[GPT], ij[GPT];
-  size_t off[GPT];                                     // (b, u) offset inside one [B,H] slab
+  size_t off[GPT];
 #pragma unroll
   for (int q = 0; q < GPT; ++q) {
     const int idx = tid + q * NT;
-    ib[q] = idx / Hcp;
-    ij[q] = idx - ib[q] * Hcp;
-    valid[q] = (idx < BT * Hcp) && (ij[q] < nown) && (b0 + ib[q] < a.B);
+    ij[q] = idx / BT;
+    ib[q] = idx - ij[q] * BT;
+    valid[q] = (idx < Hc * BT) && (ij[q] < nown) && (b0 + ib[q] < a.B);
     off[q] = valid[q] ? (size_t)(b0 + ib[q]) * H + n * Hb + u0 + ij[q] : 0;
     dh_acc[q] = 0.f;
     c_do[q] = c_r[q] = c_z[q] = c_n[q] = c_ghn[q] = c_hp[q] = 0.f;
@@ -329,45 +393,41 @@ block_bwd_kernel(const BlockScanArgs a) {
   }
   if (C > 1) cluster.sync(); else __syncthreads();
 
-  const int nct = Hcp / 32;
-  const int nitems = nct * a.KS;
-  const int K = 3 * Hb;
-  const int Kper = (K + a.KS - 1) / a.KS;
+  // contraction geometry: k tiles of 32*TW positions, NH halves of the (gate, unit) index;
+  // ntiles * NH <= NW whenever NH > 1, so one round of warps covers both halves of a tile.
+  const int ktile = 32 * TW;
+  const int ntiles = (HbP + ktile - 1) / ktile;
+  const int NH = a.NH;
+  const int ncon = 3 * Hc4;
+  const int con_per = (ncon + NH - 1) / NH;
 
   for (int t = a.T - 1; t >= 0; --t) {
     const int par = (a.T - 1 - t) & 1;
-    float* xcur = xbuf + par * K3 * BT;
+    float* rcur = recv + par * C * slice;
+    float* park = recv + (par ^ 1) * C * slice;        // idle this step: second-half sums park here
 
-    // ---- gate gradients for the owned items; publish dgh
+    // ---- gate gradients of the owned elements
     float dh_direct[GPT], mask_in[GPT];
 #pragma unroll
     for (int q = 0; q < GPT; ++q) {
-      const int idx = tid + q * NT;
       dh_direct[q] = 0.f; mask_in[q] = 1.f;
-      if (idx < BT * Hcp) {
-        float x0 = 0.f, x1 = 0.f, x2 = 0.f;
-        if (valid[q]) {
-          float dh = c_do[q] + dh_acc[q];
-          if (a.qout.enabled) {
-            const float h_raw = (1.0f - c_z[q]) * c_n[q] + c_z[q] * c_hp[q];
-            dh = dh * ste_mask<true>(h_raw, a.qout);
-          }
-          const GateGrad gg = gru_gate_grads(dh, c_r[q], c_z[q], c_n[q], c_ghn[q], c_hp[q]);
-          dh_direct[q] = gg.dh_direct;
-          if (a.qin.enabled) mask_in[q] = ste_mask<true>(c_hp[q], a.qin);
-          float* d = a.dgi + (size_t)t * gi_step + (size_t)(b0 + ib[q]) * 3 * H + n * Hb + u0 + ij[q];
-          __stcs(d, gg.dgr); __stcs(d + H, gg.dgz); __stcs(d + 2 * H, gg.dgn);
-          x0 = gg.dgr; x1 = gg.dgz; x2 = gg.dghn;
+      if (valid[q]) {
+        float dh = c_do[q] + dh_acc[q];
+        if (a.qout.enabled) {
+          const float h_raw = (1.0f - c_z[q]) * c_n[q] + c_z[q] * c_hp[q];
+          dh = dh * ste_mask<true>(h_raw, a.qout);
         }
-        if (ij[q] < Hc) {
-          const int k = u0 + ij[q];
-          xcur[(0 * HbP + k) * BT + ib[q]] = x0;
-          xcur[(1 * HbP + k) * BT + ib[q]] = x1;
-          xcur[(2 * HbP + k) * BT + ib[q]] = x2;
-        }
+        const GateGrad gg = gru_gate_grads(dh, c_r[q], c_z[q], c_n[q], c_ghn[q], c_hp[q]);
+        dh_direct[q] = gg.dh_direct;
+        if (a.qin.enabled) mask_in[q] = ste_mask<true>(c_hp[q], a.qin);
+        float* d = a.dgi + (size_t)t * gi_step + (size_t)(b0 + ib[q]) * 3 * H + n * Hb + u0 + ij[q];
+        __stcs(d, gg.dgr); __stcs(d + H, gg.dgz); __stcs(d + 2 * H, gg.dgn);
+        xs[(0 * Hc4 + ij[q]) * BT + ib[q]] = gg.dgr;
+        xs[(1 * Hc4 + ij[q]) * BT + ib[q]] = gg.dgz;
+        xs[(2 * Hc4 + ij[q]) * BT + ib[q]] = gg.dghn;
       }
     }
-    // ---- operands of step t-1 go in flight now
+    // operands of step t-1 go in flight now
 #pragma unroll
     for (int q = 0; q < GPT; ++q) {
       if (valid[q] && t > 0) {
@@ -380,50 +440,89 @@ block_bwd_kernel(const BlockScanArgs a) {
         c_hp[q] = (t > 1) ? a.out[o - out_step] : a.h0[off[q]];
       }
     }
-    if (C > 1) {
-      __syncthreads();
-#pragma unroll
-      for (int g = 0; g < 3; ++g)
-        publish_to_peers(cluster, xcur + (g * HbP + u0) * BT, Hc * BT, C, rank);
-      cluster.sync();
-    } else {
-      __syncthreads();
-    }
-
-    // ---- dh_via[b, u0 + j] = sum_{g,o} dgh[b,g,o] * W(g, o, u0 + j)
-    for (int item = warp; item < nitems; item += NW) {
-      const int ct = item % nct, ks = item / nct;
-      const int j = ct * 32 + lane;
-      const int jr = (j < nown) ? j : 0;
-      const int k0 = ks * Kper, k1 = min(K, k0 + Kper);
-      float acc[BT];
-#pragma unroll
-      for (int b = 0; b < BT; ++b) acc[b] = 0.f;
-      int g = k0 / Hb, o = k0 - g * Hb;
-      const float* wp = wbase + jr;
-      for (int kk = k0; kk < k1; ++kk) {
-        const float w = wp[(size_t)g * gstride + (size_t)o * ostride];
-        float xv[BT];
-        load_rows<BT>(xcur + (g * HbP + o) * BT, xv);
-#pragma unroll
-        for (int b = 0; b < BT; ++b) acc[b] = fmaf(w, xv[b], acc[b]);
-        if (++o == Hb) { o = 0; ++g; }
-      }
-#pragma unroll
-      for (int b = 0; b < BT; ++b) red[(ks * BT + b) * Hcp + j] = acc[b];
-    }
     __syncthreads();
 
+    // ---- partial[k][b] = sum over own (g, j) of W(g, u0+j, k) * dgh[b, g, j]
+    for (int item0 = 0; item0 < ntiles * NH; item0 += NW) {
+      const int item = item0 + warp;
+      const bool live = item < ntiles * NH;
+      const int kt = live ? item % ntiles : 0, half = live ? item / ntiles : 0;
+      const int kbase = kt * ktile + lane * TW;
+      float acc[TW][BT];
+#pragma unroll
+      for (int i = 0; i < TW; ++i)
+#pragma unroll
+        for (int b = 0; b < BT; ++b) acc[i][b] = 0.f;
+      if (live) {
+        const int c0 = half * con_per, c1 = min(ncon, c0 + con_per);
+        int g = c0 / Hc4, j = c0 - g * Hc4;
+        const bool kin = kbase < Hb4;
+        for (int c = c0; c < c1; ++c) {
+          float w[TW];
+#pragma unroll
+          for (int i = 0; i < TW; ++i) w[i] = 0.f;
+          if (a.w_in_smem) {
+            if (kin) {
+              const float* p = wbase + (size_t)g * gstride + j * rstride + kbase;
+              if constexpr (TW == 4) {
+                const float4 x = *reinterpret_cast<const float4*>(p);
+                w[0] = x.x; w[1] = x.y; w[2] = x.z; w[3] = x.w;
+              } else {
+                w[0] = p[0];
+              }
+            }
+          } else if (j < nown) {
+#pragma unroll
+            for (int i = 0; i < TW; ++i)
+              if (kbase + i < Hb) w[i] = __ldg(wbase + (size_t)g * gstride + (size_t)j * rstride + kbase + i);
+          }
+          float xv[BT];
+          load_rows<BT>(xs + c * BT, xv);
+#pragma unroll
+          for (int i = 0; i < TW; ++i)
+#pragma unroll
+            for (int b = 0; b < BT; ++b) acc[i][b] = fmaf(w[i], xv[b], acc[i][b]);
+          if (++j == Hc4) { j = 0; ++g; }
+        }
+        if (half > 0) {
+          // park: [half-1][k][b] -- one extra half fits in the idle receive buffer
+#pragma unroll
+          for (int i = 0; i < TW; ++i)
+            if (kbase + i < HbP)
+#pragma unroll
+              for (int b = 0; b < BT; ++b) park[((half - 1) * HbP + kbase + i) * BT + b] = acc[i][b];
+        }
+      }
+      if (NH > 1) __syncthreads();
+      if (live && half == 0) {
+        // combine the halves and hand each position to the rank that owns it
+#pragma unroll
+        for (int i = 0; i < TW; ++i) {
+          const int k = kbase + i;
+          if (k < HbP) {
+            const int dst = k / Hc, jj = k - dst * Hc;
+            float* base = (dst == rank || C == 1) ? rcur : cluster.map_shared_rank(rcur, dst);
+#pragma unroll
+            for (int b = 0; b < BT; ++b) {
+              float v = acc[i][b];
+              for (int h2 = 1; h2 < NH; ++h2) v += park[((h2 - 1) * HbP + k) * BT + b];
+              base[rank * slice + jj * BT + b] = v;
+            }
+          }
+        }
+      }
+    }
+    if (C > 1) cluster.sync(); else __syncthreads();
+
+    // ---- dh for the owned elements: C partials in rank order
 #pragma unroll
     for (int q = 0; q < GPT; ++q) {
-      const int idx = tid + q * NT;
-      if (idx < BT * Hcp && valid[q]) {
+      if (valid[q]) {
         float s = 0.f;
-        for (int ks = 0; ks < a.KS; ++ks) s += red[(ks * BT + ib[q]) * Hcp + ij[q]];
+        for (int r = 0; r < C; ++r) s += rcur[r * slice + ij[q] * BT + ib[q]];
         dh_acc[q] = dh_direct[q] + s * mask_in[q];
       }
     }
-    // `red` is rewritten only after the next step's barrier, `xbuf` alternates: no extra sync.
   }
 
 #pragma unroll
@@ -438,36 +537,29 @@ block_bwd_kernel(const BlockScanArgs a) {
 using KernelFn = void (*)(const BlockScanArgs);
 
 template <int BT>
-static KernelFn pick_gpt(bool fwd, int gpt) {
-  if (fwd) {
-    if (gpt == 1) return block_fwd_kernel<BT, 1>;
-    if (gpt == 2) return block_fwd_kernel<BT, 2>;
-    return block_fwd_kernel<BT, 4>;
-  }
-  if (gpt == 1) return block_bwd_kernel<BT, 1>;
-  if (gpt == 2) return block_bwd_kernel<BT, 2>;
-  return block_bwd_kernel<BT, 4>;
+static KernelFn pick_fwd(int ipw) {
+  if (ipw <= 1) return block_fwd_kernel<BT, 1>;
+  if (ipw <= 2) return block_fwd_kernel<BT, 2>;
+  return block_fwd_kernel<BT, 8>;
+}
+template <int BT>
+static KernelFn pick_bwd(int tw, int gpt) {
+  if (tw == 4) return gpt <= 1 ? block_bwd_kernel<BT, 4, 1> : block_bwd_kernel<BT, 4, 8>;
+  return gpt <= 1 ? block_bwd_kernel<BT, 1, 1> : block_bwd_kernel<BT, 1, 8>;
 }
 
-static KernelFn pick_kernel(bool fwd, int bt, int gpt) {
-  switch (bt) {
-    case 1: return pick_gpt<1>(fwd, gpt);
-    case 2: return pick_gpt<2>(fwd, gpt);
-    case 4: return pick_gpt<4>(fwd, gpt);
-    default: return pick_gpt<8>(fwd, gpt);
+static KernelFn pick_kernel(bool fwd, const BlockScanConfig& c) {
+#define B200GRU_PICK(B) return fwd ? pick_fwd<B>(c.IPW) : pick_bwd<B>(c.TW, c.GPT)
+  switch (c.BT) {
+    case 1: B200GRU_PICK(1);
+    case 2: B200GRU_PICK(2);
+    case 3: B200GRU_PICK(3);
+    case 4: B200GRU_PICK(4);
+    case 5: B200GRU_PICK(5);
+    case 6: B200GRU_PICK(6);
+    default: B200GRU_PICK(8);
   }
-}
-
-static size_t smem_bytes(bool fwd, int BT, int Hb, int HbP, int Hcp, int KS, bool w_in_smem) {
-  size_t f;
-  if (fwd) {
-    f = (size_t)2 * HbP * BT + (size_t)KS * 3 * BT * Hcp;
-    if (w_in_smem) f += (size_t)Hb * (3 * Hcp + 1);
-  } else {
-    f = (size_t)2 * 3 * HbP * BT + (size_t)KS * BT * Hcp;
-    if (w_in_smem) f += (size_t)3 * Hb * Hcp;
-  }
-  return f * sizeof(float);
+#undef B200GRU_PICK
 }
 
 struct DeviceInfo {
@@ -546,50 +638,60 @@ static int max_active_clusters(KernelFn fn, int C, size_t smem) {
   return n;
 }
 
-// Pick (C, BT, KS, GPT, weights-in-smem) minimising a simple cost model:
-//   step = max(FMA issue, weight-slice streaming) + barrier;  total = waves * step.
+static int round_up(int x, int m) { return (x + m - 1) / m * m; }
+
+// Pick the cluster size, batch tile and weight placement that minimise a simple cost model:
+//   step = max(FMA issue, shared-memory streaming) + barrier;  total = waves * step.
 bool choose_block_config(bool fwd, int B, int Hb, int nb, BlockScanConfig* out) {
   const DeviceInfo di = device_info();
   if (!di.ok) return false;
   double best = 1e300;
   bool found = false;
-  const int bts[4] = {1, 2, 4, 8};
+  const int bts[7] = {1, 2, 3, 4, 5, 6, 8};
   const int cs[5] = {1, 2, 4, 8, 16};
   for (int ci = 0; ci < 5; ++ci) {
     const int C = cs[ci];
     if (C > 1 && Hb / C < 8) continue;                 // slices thinner than 8 units: not worth a barrier
     const int Hc = cdiv(Hb, C);
-    const int Hcp = cdiv(Hc, 32) * 32;
-    for (int bi = 0; bi < 4; ++bi) {
+    const int Hc4 = round_up(Hc, 4);
+    const int HbP = C * Hc;
+    const int Hb4 = round_up(HbP, 4);
+    const int nitems = Hc4 / 4;
+    const int ipw = cdiv(nitems, NW);
+    if (ipw > 8) continue;
+    for (int bi = 0; bi < 7; ++bi) {
       const int BT = bts[bi];
-      if (BT > 1 && BT / 2 >= B) continue;             // tile mostly empty
+      if (bi > 0 && bts[bi - 1] >= B) continue;        // a smaller tile already covers the batch
       if (C > 1 && (Hc * BT) % 4 != 0) continue;       // published slices move as float4
-      const int HbP = C * Hc;                          // padded block width (>= Hb)
-      if (BT * Hcp > 4 * NT) continue;
-      const int gpt = (BT * Hcp <= NT) ? 1 : (BT * Hcp <= 2 * NT ? 2 : 4);
-      const int nct = Hcp / 32;
-      int KS = nct >= NW ? 1 : NW / nct;
-      const int Kfull = fwd ? Hb : 3 * Hb;
-      while (KS > 1 && Kfull / KS < 4) KS >>= 1;
+      if (Hc * BT > 8 * NT) continue;
+      BlockScanConfig c;
+      c.C = C; c.BT = BT; c.Hc = Hc; c.Hc4 = Hc4; c.HbP = HbP; c.Hb4 = Hb4;
+      c.IPW = ipw <= 1 ? 1 : (ipw <= 2 ? 2 : 8);
+      int rs = 3 * Hc4;
+      while (rs % 8 != 4) ++rs;
+      c.RS = rs;
+      c.TW = (HbP >= 64 * NW) ? 4 : 1;
+      const int ntiles = cdiv(HbP, 32 * c.TW);
+      c.NH = (2 * ntiles <= NW) ? 2 : 1;
+      c.GPT = (Hc * BT <= NT) ? 1 : 8;
       for (int ws = 1; ws >= 0; --ws) {
-        const size_t smem = smem_bytes(fwd, BT, Hb, HbP, Hcp, KS, ws != 0);
+        size_t fl;
+        if (fwd) fl = (size_t)((2 * HbP * BT + 3) & ~3) + (ws ? (size_t)Hb * c.RS : 0);
+        else fl = (size_t)2 * C * Hc * BT + (size_t)3 * Hc4 * BT + 4 + (ws ? (size_t)3 * Hc4 * Hb4 : 0);
+        const size_t smem = fl * sizeof(float);
         if (smem > di.smem_optin) continue;
-        KernelFn fn = pick_kernel(fwd, BT, gpt);
+        c.w_in_smem = ws; c.smem = smem;
+        KernelFn fn = pick_kernel(fwd, c);
         const int active = max_active_clusters(fn, C, smem);
         if (active <= 0) continue;
         const long long nclusters = (long long)nb * cdiv(B, BT);
         const double waves = (double)((nclusters + active - 1) / active);
-        const double fma = 3.0 * Hcp * Hb * BT / 128.0;
-        const double stream = 3.0 * Hcp * Hb * 4.0 / (ws ? 128.0 : 24.0);
-        const double barrier = C > 1 ? 1400.0 + 40.0 * C : 250.0;
-        const double cost = waves * ((fma > stream ? fma : stream) + barrier + 300.0);
-        if (cost < best) {
-          best = cost;
-          found = true;
-          out->C = C; out->BT = BT; out->Hc = Hc; out->Hcp = Hcp; out->HbP = HbP; out->KS = KS;
-          out->GPT = gpt; out->w_in_smem = ws; out->smem = smem;
-        }
-        break;                                          // weights in smem fits: do not also try global
+        const double fma = 3.0 * Hc4 * Hb * BT / 128.0;
+        const double stream = 3.0 * Hc4 * Hb * 4.0 / (ws ? 128.0 : 24.0) + (double)Hb * BT * 4.0 * NW / 128.0;
+        const double barrier = C > 1 ? 1200.0 + 40.0 * C : 200.0;
+        const double cost = waves * ((fma > stream ? fma : stream) + barrier + 400.0);
+        if (cost < best) { best = cost; found = true; *out = c; }
+        break;                                          // weights in smem fit: do not also try global
       }
     }
   }
@@ -597,15 +699,16 @@ bool choose_block_config(bool fwd, int B, int Hb, int nb, BlockScanConfig* out) 
 }
 
 int launch_block_scan(bool fwd, const BlockScanConfig& c, BlockScanArgs args, int nb, cudaStream_t st) {
-  args.C = c.C; args.Hc = c.Hc; args.Hcp = c.Hcp; args.HbP = c.HbP; args.KS = c.KS;
-  args.w_in_smem = c.w_in_smem;
-  KernelFn fn = pick_kernel(fwd, c.BT, c.GPT);
+  args.C = c.C; args.Hc = c.Hc; args.Hc4 = c.Hc4; args.HbP = c.HbP; args.Hb4 = c.Hb4; args.RS = c.RS;
+  args.NH = c.NH; args.w_in_smem = c.w_in_smem; args.WtR = c.Hb4 + 4;
+  KernelFn fn = pick_kernel(fwd, c);
   const int active = max_active_clusters(fn, c.C, c.smem);                      // also sets the attributes
   static const bool debug = getenv("B200GRU_DEBUG") != nullptr;
   if (debug)
-    fprintf(stderr, "[b200gru] %s T=%d B=%d H=%d nb=%d Hb=%d: C=%d BT=%d Hc=%d KS=%d GPT=%d w_in_smem=%d smem=%zu "
-            "active_clusters=%d grid=(%d,%d)\n", fwd ? "block_fwd" : "block_bwd", args.T, args.B, args.H, nb, args.Hb,
-            c.C, c.BT, c.Hc, c.KS, c.GPT, c.w_in_smem, c.smem, active, c.C * nb, cdiv(args.B, c.BT));
+    fprintf(stderr, "[b200gru] %s T=%d B=%d H=%d nb=%d Hb=%d: C=%d BT=%d Hc=%d IPW=%d TW=%d NH=%d GPT=%d "
+            "w_in_smem=%d smem=%zu active_clusters=%d grid=(%d,%d)\n", fwd ? "block_fwd" : "block_bwd", args.T,
+            args.B, args.H, nb, args.Hb, c.C, c.BT, c.Hc, c.IPW, c.TW, c.NH, c.GPT, c.w_in_smem, c.smem, active,
+            c.C * nb, cdiv(args.B, c.BT));
   if (active <= 0) return B200GRU_UNSUPPORTED;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(c.C * nb, cdiv(args.B, c.BT), 1);
@@ -616,9 +719,8 @@ int launch_block_scan(bool fwd, const BlockScanConfig& c, BlockScanArgs args, in
   at[0].id = cudaLaunchAttributeClusterDimension;
   at[0].val.clusterDim.x = c.C; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
   cfg.attrs = at; cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, fn, args);
+  cudaLaunchKernelEx(&cfg, fn, args);
   note_launch();
-  if (e != cudaSuccess) return check_launch(fwd ? "block_fwd_kernel" : "block_bwd_kernel");
   return check_launch(fwd ? "block_fwd_kernel" : "block_bwd_kernel");
 }
 

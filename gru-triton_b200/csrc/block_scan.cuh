@@ -14,7 +14,7 @@ struct BlockScanArgs {
   const float* gi;
   const float* h0;
   const float* W;
-  const float* Wt;     // forward only: W transposed to [nb][Hb(k)][3][Hb(o)], used when a slice misses smem
+  const float* Wt;     // forward only: W transposed to [nb][Hb(k)][3][WtR(o), zero padded], used when a slice misses smem
   const float* bh;
   float* out;          // forward: written; backward: read (const in effect)
   float* save;         // forward: optional [4][T][B][H] (r, z, n, gh_n)
@@ -26,14 +26,22 @@ struct BlockScanArgs {
   int nb, Hb;
   long long w_gate_stride, w_block_stride;
   // launch configuration (filled by launch_block_scan)
-  int C, Hc, Hcp, HbP, KS, w_in_smem;
+  int C, Hc, Hc4, HbP, Hb4, RS, NH, WtR, w_in_smem;
   Quant qin, qout;
 };
 
+// C: cluster size; BT: batch rows per cluster; Hc: units per CTA (Hc4: rounded to 4);
+// HbP = C*Hc >= Hb (Hb4: rounded to 4); RS: forward weight row stride in shared memory;
+// IPW: forward 4-unit items per warp; TW/NH/GPT: backward vector width, contraction halves,
+// owned elements per thread.
 struct BlockScanConfig {
-  int C, BT, Hc, Hcp, HbP, KS, GPT, w_in_smem;
+  int C, BT, Hc, Hc4, HbP, Hb4, RS, IPW, TW, NH, GPT, w_in_smem;
   size_t smem;
 };
+
+// Row length of the transposed weight copy for a block of width Hb (upper bound over all
+// cluster sizes; the forward reads 4 units at a time and may run past the last owned unit).
+inline int transposed_row_bound(int Hb) { return Hb + 24; }
 
 bool choose_block_config(bool fwd, int B, int Hb, int nb, BlockScanConfig* out);
 int launch_block_scan(bool fwd, const BlockScanConfig& c, BlockScanArgs args, int nb, cudaStream_t st);
@@ -60,7 +68,7 @@ struct BlockGemmArgs {
   Quant qin;
 };
 
-int launch_transpose_weights(const float* W, float* Wt, int nb, int Hb, long long w_gate_stride,
+int launch_transpose_weights(const float* W, float* Wt, int nb, int Hb, int WtR, long long w_gate_stride,
                              long long w_block_stride, cudaStream_t st);
 int launch_recompute_gates(const BlockGemmArgs& a, cudaStream_t st);
 size_t weight_grads_scratch_bytes(int T, int B, int H, int nb, int Hb);
