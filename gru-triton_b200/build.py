@@ -43,7 +43,7 @@ def _newest_dep() -> float:
 
 
 def _compile(nvcc: str, src: str, obj: str, verbose: bool) -> str:
-    cmd = [nvcc, *NVCC_FLAGS, "-c", src, "-o", obj]
+    cmd = [nvcc, *NVCC_FLAGS, *os.environ.get("B200GRU_EXTRA_NVCC_FLAGS", "").split(), "-c", src, "-o", obj]
     if verbose:
         cmd.insert(1, "-Xptxas=-v")
     r = subprocess.run(cmd, capture_output=True, text=True)

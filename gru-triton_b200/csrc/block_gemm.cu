@@ -150,13 +150,17 @@ int launch_recompute_gates(const BlockGemmArgs& a, cudaStream_t st) {
 // weight_grads
 // ---------------------------------------------------------------------------
 constexpr int WG_O = 64;       // output units per CTA (x 3 gates)
-constexpr int WG_K = 32;       // input units per CTA
-constexpr int WG_R = 32;       // rows (t,b) per smem chunk
+constexpr int WG_K = 64;       // input units per CTA (two per lane)
+constexpr int WG_R = 16;       // rows (t,b) per shared-memory chunk
 
+// CTA tile: dW[g, 64 o, 64 k] for one row range.  Warp w owns 8 output units, lane l owns
+// input units 2l, 2l+1: 48 accumulators per thread, 7 shared loads per 48 FMAs.  The next
+// chunk's operands are fetched into registers (fake-quant / r-scaling applied) while the
+// current chunk is consumed from shared memory.
 __global__ void __launch_bounds__(256)
 weight_grads_kernel(const BlockGemmArgs a, float* __restrict__ dst, int rows_per_split) {
   __shared__ __align__(16) float Ds[WG_R][3 * WG_O];     // dgh[row][g*64 + o]
-  __shared__ float Hs[WG_R][WG_K];                       // fq_in(h_prev)[row][k]
+  __shared__ __align__(16) float Hs[WG_R][WG_K];         // fq_in(h_prev)[row][k]
   const int Hb = a.Hb, H = a.H, B = a.B;
   const int TB = a.T * B;
   const int nkt = cdiv(Hb, WG_K), not_ = cdiv(Hb, WG_O);
@@ -168,28 +172,29 @@ weight_grads_kernel(const BlockGemmArgs a, float* __restrict__ dst, int rows_per
   const int r_begin = split * rows_per_split;
   const int r_end = min(TB, r_begin + rows_per_split);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const size_t comp = (size_t)TB * H;
 
-  float acc[3][8];
-#pragma unroll
-  for (int g = 0; g < 3; ++g)
-#pragma unroll
-    for (int i = 0; i < 8; ++i) acc[g][i] = 0.f;
+  constexpr int ND = WG_R * 3 * WG_O / 256;               // 12 dgh values per thread per chunk
+  constexpr int NH_ = WG_R * WG_K / 256;                  // 4 h values per thread per chunk
+  float dreg[ND], hreg[NH_];
 
-  for (int r0 = r_begin; r0 < r_end; r0 += WG_R) {
-    for (int idx = tid; idx < WG_R * 3 * WG_O; idx += 256) {
+  auto fetch = [&](int r0) {
+#pragma unroll
+    for (int m = 0; m < ND; ++m) {
+      const int idx = tid + m * 256;
       const int r = idx / (3 * WG_O), go = idx - r * (3 * WG_O);
       const int g = go / WG_O, o = go - g * WG_O;
       const int tb = r0 + r, uo = ot * WG_O + o;
       float v = 0.f;
       if (tb < r_end && uo < Hb) {
         const int u = n * Hb + uo;
-        v = a.dgi[(size_t)tb * 3 * H + (size_t)g * H + u];
-        if (g == 2) v = v * a.S[(size_t)tb * H + u];          // dgh_n = dgi_n * r
+        v = __ldg(a.dgi + (size_t)tb * 3 * H + (size_t)g * H + u);
+        if (g == 2) v = v * __ldg(a.S + (size_t)tb * H + u);         // dgh_n = dgi_n * r
       }
-      Ds[r][go] = v;
+      dreg[m] = v;
     }
-    for (int idx = tid; idx < WG_R * WG_K; idx += 256) {
+#pragma unroll
+    for (int m = 0; m < NH_; ++m) {
+      const int idx = tid + m * 256;
       const int r = idx / WG_K, k = idx - r * WG_K;
       const int tb = r0 + r, uk = kt * WG_K + k;
       float v = 0.f;
@@ -197,27 +202,46 @@ weight_grads_kernel(const BlockGemmArgs a, float* __restrict__ dst, int rows_per
         v = h_prev_at(a.h0, a.out, tb, B, H, n * Hb + uk);
         if (a.qin.enabled) v = fake_quant<true>(v, a.qin);
       }
-      Hs[r][k] = v;
+      hreg[m] = v;
     }
+  };
+  auto stash = [&]() {
+#pragma unroll
+    for (int m = 0; m < ND; ++m) (&Ds[0][0])[tid + m * 256] = dreg[m];
+#pragma unroll
+    for (int m = 0; m < NH_; ++m) (&Hs[0][0])[tid + m * 256] = hreg[m];
+  };
+
+  float acc[3][8][2];
+#pragma unroll
+  for (int g = 0; g < 3; ++g)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[g][i][0] = acc[g][i][1] = 0.f;
+
+  fetch(r_begin);
+  for (int r0 = r_begin; r0 < r_end; r0 += WG_R) {
+    stash();
     __syncthreads();
-#pragma unroll 2
+    if (r0 + WG_R < r_end) fetch(r0 + WG_R);
+#pragma unroll 4
     for (int r = 0; r < WG_R; ++r) {
-      const float h = Hs[r][lane];
+      const float2 h = *reinterpret_cast<const float2*>(&Hs[r][2 * lane]);
 #pragma unroll
       for (int g = 0; g < 3; ++g) {
         const float4 d0 = *reinterpret_cast<const float4*>(&Ds[r][g * WG_O + warp * 8]);
         const float4 d1 = *reinterpret_cast<const float4*>(&Ds[r][g * WG_O + warp * 8 + 4]);
-        acc[g][0] = fmaf(d0.x, h, acc[g][0]); acc[g][1] = fmaf(d0.y, h, acc[g][1]);
-        acc[g][2] = fmaf(d0.z, h, acc[g][2]); acc[g][3] = fmaf(d0.w, h, acc[g][3]);
-        acc[g][4] = fmaf(d1.x, h, acc[g][4]); acc[g][5] = fmaf(d1.y, h, acc[g][5]);
-        acc[g][6] = fmaf(d1.z, h, acc[g][6]); acc[g][7] = fmaf(d1.w, h, acc[g][7]);
+        const float d[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          acc[g][i][0] = fmaf(d[i], h.x, acc[g][i][0]);
+          acc[g][i][1] = fmaf(d[i], h.y, acc[g][i][1]);
+        }
       }
     }
     __syncthreads();
   }
-  (void)comp;
 
-  const int k = kt * WG_K + lane;
+  const int k = kt * WG_K + 2 * lane;
   if (k >= Hb) return;
   const size_t dw_elems = (size_t)3 * a.nb * Hb * Hb;      // dense: 3*H*H as well
   float* base = dst + (size_t)split * dw_elems + (size_t)n * a.w_block_stride;
@@ -226,7 +250,11 @@ weight_grads_kernel(const BlockGemmArgs a, float* __restrict__ dst, int rows_per
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       const int o = ot * WG_O + warp * 8 + i;
-      if (o < Hb) base[(size_t)g * a.w_gate_stride + (size_t)o * Hb + k] = acc[g][i];
+      if (o < Hb) {
+        float* p = base + (size_t)g * a.w_gate_stride + (size_t)o * Hb + k;
+        p[0] = acc[g][i][0];
+        if (k + 1 < Hb) p[1] = acc[g][i][1];
+      }
     }
 }
 
@@ -262,7 +290,7 @@ static void wg_splits(int T, int B, int nb, int Hb, int* nsplit, int* rows_per_s
   const int TB = T * B;
   const long long tiles = (long long)nb * cdiv(Hb, WG_O) * cdiv(Hb, WG_K);
   long long s = (2 * 148 + tiles - 1) / tiles;
-  const long long max_by_rows = (TB + 4 * WG_R - 1) / (4 * WG_R);
+  const long long max_by_rows = (TB + 8 * WG_R - 1) / (8 * WG_R);
   if (s > max_by_rows) s = max_by_rows;
   if (s > 32) s = 32;
   if (s < 1) s = 1;

@@ -45,6 +45,20 @@ namespace cg = cooperative_groups;
 
 namespace b200gru {
 
+// Debug aid, compiled in only with -DB200GRU_PHASE_TIMING: thread 0 of CTA (0,0) adds the
+// clock64() distance between consecutive marks of a step to g_phase_cycles[slot].
+#ifdef B200GRU_PHASE_TIMING
+__device__ unsigned long long g_phase_cycles[16];
+#define PHASE_DECL long long ph_last = 0; const bool ph_on = (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0)
+#define PHASE_START() do { if (ph_on) ph_last = clock64(); } while (0)
+#define PHASE_MARK(slot) do { if (ph_on) { long long ph_now = clock64(); \
+    atomicAdd(&g_phase_cycles[slot], (unsigned long long)(ph_now - ph_last)); ph_last = ph_now; } } while (0)
+#else
+#define PHASE_DECL
+#define PHASE_START()
+#define PHASE_MARK(slot)
+#endif
+
 namespace {
 
 constexpr int NT = BLOCK_SCAN_THREADS;   // threads per CTA
@@ -214,9 +228,11 @@ block_fwd_kernel(const BlockScanArgs a) {
   const size_t out_step = (size_t)a.B * H;
   const size_t comp = (size_t)a.T * out_step;
 
+  PHASE_DECL;
   for (int t = 0; t < a.T; ++t) {
     const float* hcur = hbuf + (t & 1) * HbP * BT;
     float* hnxt = hbuf + ((t + 1) & 1) * HbP * BT;
+    PHASE_START();
 
 #pragma unroll
     for (int q = 0; q < IPW; ++q) {
@@ -263,6 +279,7 @@ block_fwd_kernel(const BlockScanArgs a) {
               acc[g][3][b] = fmaf(w[g].w, hv[b], acc[g][3][b]);
             }
         }
+        PHASE_MARK(0);
 
         float s[3];
 #pragma unroll
@@ -275,6 +292,7 @@ block_fwd_kernel(const BlockScanArgs a) {
           warp_reduce_scatter<NV>(vals, lane);
           s[g] = vals[0];
         }
+        PHASE_MARK(1);
 
         const int j = item * 4 + ec;
         if (eown && j < Hc) {
@@ -297,14 +315,19 @@ block_fwd_kernel(const BlockScanArgs a) {
           hnxt[(u0 + j) * BT + eb] = hq;
         }
         gr[q] = ngr; gz[q] = ngz; gn[q] = ngn;
+        PHASE_MARK(2);
       }
     }
     if (C > 1) {
       __syncthreads();
+      PHASE_MARK(3);
       publish_to_peers(cluster, hnxt + u0 * BT, Hc * BT, C, rank);
+      PHASE_MARK(4);
       cluster.sync();
+      PHASE_MARK(5);
     } else {
       __syncthreads();
+      PHASE_MARK(3);
     }
   }
 }
@@ -313,7 +336,7 @@ block_fwd_kernel(const BlockScanArgs a) {
 // backward (serial part): dgi[t], dh chain, dh0.  Gate activations come from `S`.
 // ---------------------------------------------------------------------------
 // shared memory:  recv [2][C][Hc][BT]   partial dh_via sent by every rank (parity = step)
-//                 xs   [3][Hc4][BT]     dgh of the owned units
+//                 xs   [3][Hc4][BTX]    dgh of the owned units, rows padded to a float4 multiple
 //                 wsm  [3*Hc4][Hb4]     W(g, u0+j, k) at [(g*Hc4 + j)][k]   (k contiguous)
 // The second contraction half parks its sums in the idle parity half of `recv`.
 template <int BT, int TW, int GPT>
@@ -330,11 +353,11 @@ block_bwd_kernel(const BlockScanArgs a) {
   const int u0 = rank * Hc;
   const int nown = max(0, min(Hc, Hb - u0));
   const int slice = Hc * BT;                           // floats one rank sends to one peer
+  constexpr int BTX = (BT + 3) & ~3;                   // dgh rows padded to float4
 
   float* recv = smem;                                  // [2][C*slice]
-  float* xs = recv + 2 * C * slice;                    // [3*Hc4][BT]
-  float* wsm = xs + 3 * Hc4 * BT;
-  wsm += (4 - ((2 * C * slice + 3 * Hc4 * BT) & 3)) & 3;   // keep the weight rows 16-byte aligned
+  float* xs = recv + ((2 * C * slice + 3) & ~3);       // [3*Hc4][BTX]
+  float* wsm = xs + 3 * Hc4 * BTX;
 
   const float* wbase;
   size_t gstride;      // between gates
@@ -359,7 +382,7 @@ block_bwd_kernel(const BlockScanArgs a) {
     wbase = a.W + (size_t)n * a.w_block_stride + (size_t)u0 * Hb;
   }
   for (int idx = tid; idx < 2 * C * slice; idx += NT) recv[idx] = 0.f;
-  for (int idx = tid; idx < 3 * Hc4 * BT; idx += NT) xs[idx] = 0.f;
+  for (int idx = tid; idx < 3 * Hc4 * BTX; idx += NT) xs[idx] = 0.f;
 
   const size_t gi_step = (size_t)a.B * 3 * H;
   const size_t out_step = (size_t)a.B * H;
@@ -401,7 +424,9 @@ block_bwd_kernel(const BlockScanArgs a) {
   const int ncon = 3 * Hc4;
   const int con_per = (ncon + NH - 1) / NH;
 
+  PHASE_DECL;
   for (int t = a.T - 1; t >= 0; --t) {
+    PHASE_START();
     const int par = (a.T - 1 - t) & 1;
     float* rcur = recv + par * C * slice;
     float* park = recv + (par ^ 1) * C * slice;        // idle this step: second-half sums park here
@@ -422,9 +447,9 @@ block_bwd_kernel(const BlockScanArgs a) {
         if (a.qin.enabled) mask_in[q] = ste_mask<true>(c_hp[q], a.qin);
         float* d = a.dgi + (size_t)t * gi_step + (size_t)(b0 + ib[q]) * 3 * H + n * Hb + u0 + ij[q];
         __stcs(d, gg.dgr); __stcs(d + H, gg.dgz); __stcs(d + 2 * H, gg.dgn);
-        xs[(0 * Hc4 + ij[q]) * BT + ib[q]] = gg.dgr;
-        xs[(1 * Hc4 + ij[q]) * BT + ib[q]] = gg.dgz;
-        xs[(2 * Hc4 + ij[q]) * BT + ib[q]] = gg.dghn;
+        xs[(0 * Hc4 + ij[q]) * BTX + ib[q]] = gg.dgr;
+        xs[(1 * Hc4 + ij[q]) * BTX + ib[q]] = gg.dgz;
+        xs[(2 * Hc4 + ij[q]) * BTX + ib[q]] = gg.dghn;
       }
     }
     // operands of step t-1 go in flight now
@@ -440,7 +465,9 @@ block_bwd_kernel(const BlockScanArgs a) {
         c_hp[q] = (t > 1) ? a.out[o - out_step] : a.h0[off[q]];
       }
     }
+    PHASE_MARK(8);
     __syncthreads();
+    PHASE_MARK(9);
 
     // ---- partial[k][b] = sum over own (g, j) of W(g, u0+j, k) * dgh[b, g, j]
     for (int item0 = 0; item0 < ntiles * NH; item0 += NW) {
@@ -448,71 +475,106 @@ block_bwd_kernel(const BlockScanArgs a) {
       const bool live = item < ntiles * NH;
       const int kt = live ? item % ntiles : 0, half = live ? item / ntiles : 0;
       const int kbase = kt * ktile + lane * TW;
-      float acc[TW][BT];
+      float acc[TW * BT];                               // [i][b], the layout of `recv` rows
 #pragma unroll
-      for (int i = 0; i < TW; ++i)
-#pragma unroll
-        for (int b = 0; b < BT; ++b) acc[i][b] = 0.f;
+      for (int i = 0; i < TW * BT; ++i) acc[i] = 0.f;
       if (live) {
         const int c0 = half * con_per, c1 = min(ncon, c0 + con_per);
-        int g = c0 / Hc4, j = c0 - g * Hc4;
-        const bool kin = kbase < Hb4;
-        for (int c = c0; c < c1; ++c) {
-          float w[TW];
-#pragma unroll
-          for (int i = 0; i < TW; ++i) w[i] = 0.f;
-          if (a.w_in_smem) {
-            if (kin) {
-              const float* p = wbase + (size_t)g * gstride + j * rstride + kbase;
+        if (a.w_in_smem) {
+          if (kbase < Hb4) {
+            const float* wp = wsm + (size_t)c0 * Hb4 + kbase;
+            const float* xp = xs + c0 * BTX;
+#pragma unroll 8
+            for (int c = c0; c < c1; ++c, wp += Hb4, xp += BTX) {
+              float w[TW];
               if constexpr (TW == 4) {
-                const float4 x = *reinterpret_cast<const float4*>(p);
+                const float4 x = *reinterpret_cast<const float4*>(wp);
                 w[0] = x.x; w[1] = x.y; w[2] = x.z; w[3] = x.w;
               } else {
-                w[0] = p[0];
+                w[0] = wp[0];
               }
+              float xv[BTX];
+              load_rows<BTX>(xp, xv);
+#pragma unroll
+              for (int i = 0; i < TW; ++i)
+#pragma unroll
+                for (int bb = 0; bb < BT; ++bb) acc[i * BT + bb] = fmaf(w[i], xv[bb], acc[i * BT + bb]);
             }
-          } else if (j < nown) {
+          }
+        } else {
+          int g = c0 / Hc4, j = c0 - g * Hc4;
+          for (int c = c0; c < c1; ++c) {
+            float w[TW];
 #pragma unroll
             for (int i = 0; i < TW; ++i)
-              if (kbase + i < Hb) w[i] = __ldg(wbase + (size_t)g * gstride + (size_t)j * rstride + kbase + i);
+              w[i] = (j < nown && kbase + i < Hb)
+                         ? __ldg(wbase + (size_t)g * gstride + (size_t)j * rstride + kbase + i) : 0.f;
+            float xv[BTX];
+            load_rows<BTX>(xs + c * BTX, xv);
+#pragma unroll
+            for (int i = 0; i < TW; ++i)
+#pragma unroll
+              for (int bb = 0; bb < BT; ++bb) acc[i * BT + bb] = fmaf(w[i], xv[bb], acc[i * BT + bb]);
+            if (++j == Hc4) { j = 0; ++g; }
           }
-          float xv[BT];
-          load_rows<BT>(xs + c * BT, xv);
-#pragma unroll
-          for (int i = 0; i < TW; ++i)
-#pragma unroll
-            for (int b = 0; b < BT; ++b) acc[i][b] = fmaf(w[i], xv[b], acc[i][b]);
-          if (++j == Hc4) { j = 0; ++g; }
         }
-        if (half > 0) {
-          // park: [half-1][k][b] -- one extra half fits in the idle receive buffer
+        if (half > 0 && kbase < HbP) {
+          // park: [k][b] of the second half -- it fits in the idle receive buffer
+          float* pp = park + (size_t)kbase * BT;
+          if constexpr ((TW * BT) % 4 == 0) {
 #pragma unroll
-          for (int i = 0; i < TW; ++i)
-            if (kbase + i < HbP)
+            for (int v = 0; v < TW * BT / 4; ++v)
+              *reinterpret_cast<float4*>(pp + 4 * v) = make_float4(acc[4 * v], acc[4 * v + 1], acc[4 * v + 2], acc[4 * v + 3]);
+          } else {
 #pragma unroll
-              for (int b = 0; b < BT; ++b) park[((half - 1) * HbP + kbase + i) * BT + b] = acc[i][b];
+            for (int i = 0; i < TW * BT; ++i)
+              if (kbase + i / BT < HbP) pp[i] = acc[i];
+          }
         }
       }
+      PHASE_MARK(10);
       if (NH > 1) __syncthreads();
-      if (live && half == 0) {
+      PHASE_MARK(11);
+      if (live && half == 0 && kbase < HbP) {
         // combine the halves and hand each position to the rank that owns it
+        if (NH > 1) {
+          const float* pp = park + (size_t)kbase * BT;
+          if constexpr ((TW * BT) % 4 == 0) {
 #pragma unroll
-        for (int i = 0; i < TW; ++i) {
-          const int k = kbase + i;
-          if (k < HbP) {
-            const int dst = k / Hc, jj = k - dst * Hc;
-            float* base = (dst == rank || C == 1) ? rcur : cluster.map_shared_rank(rcur, dst);
+            for (int v = 0; v < TW * BT / 4; ++v) {
+              const float4 x = *reinterpret_cast<const float4*>(pp + 4 * v);
+              acc[4 * v] += x.x; acc[4 * v + 1] += x.y; acc[4 * v + 2] += x.z; acc[4 * v + 3] += x.w;
+            }
+          } else {
 #pragma unroll
-            for (int b = 0; b < BT; ++b) {
-              float v = acc[i][b];
-              for (int h2 = 1; h2 < NH; ++h2) v += park[((h2 - 1) * HbP + k) * BT + b];
-              base[rank * slice + jj * BT + b] = v;
+            for (int i = 0; i < TW * BT; ++i)
+              if (kbase + i / BT < HbP) acc[i] += pp[i];
+          }
+        }
+        const int dst0 = kbase / Hc, jj0 = kbase - dst0 * Hc;
+        if ((TW * BT) % 4 == 0 && jj0 + TW <= Hc) {
+          // the TW positions of this lane belong to one rank and form one contiguous run there
+          float* base = ((dst0 == rank || C == 1) ? rcur : cluster.map_shared_rank(rcur, dst0)) + rank * slice + jj0 * BT;
+#pragma unroll
+          for (int v = 0; v < TW * BT / 4; ++v)
+            *reinterpret_cast<float4*>(base + 4 * v) = make_float4(acc[4 * v], acc[4 * v + 1], acc[4 * v + 2], acc[4 * v + 3]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < TW; ++i) {
+            const int k = kbase + i;
+            if (k < HbP) {
+              const int dst = k / Hc, jj = k - dst * Hc;
+              float* base = (dst == rank || C == 1) ? rcur : cluster.map_shared_rank(rcur, dst);
+#pragma unroll
+              for (int bb = 0; bb < BT; ++bb) base[rank * slice + jj * BT + bb] = acc[i * BT + bb];
             }
           }
         }
       }
     }
+    PHASE_MARK(12);
     if (C > 1) cluster.sync(); else __syncthreads();
+    PHASE_MARK(13);
 
     // ---- dh for the owned elements: C partials in rank order
 #pragma unroll
@@ -523,6 +585,7 @@ block_bwd_kernel(const BlockScanArgs a) {
         dh_acc[q] = dh_direct[q] + s * mask_in[q];
       }
     }
+    PHASE_MARK(14);
   }
 
 #pragma unroll
@@ -677,7 +740,7 @@ bool choose_block_config(bool fwd, int B, int Hb, int nb, BlockScanConfig* out) 
       for (int ws = 1; ws >= 0; --ws) {
         size_t fl;
         if (fwd) fl = (size_t)((2 * HbP * BT + 3) & ~3) + (ws ? (size_t)Hb * c.RS : 0);
-        else fl = (size_t)2 * C * Hc * BT + (size_t)3 * Hc4 * BT + 4 + (ws ? (size_t)3 * Hc4 * Hb4 : 0);
+        else fl = (size_t)((2 * C * Hc * BT + 3) & ~3) + (size_t)3 * Hc4 * ((BT + 3) & ~3) + (ws ? (size_t)3 * Hc4 * Hb4 : 0);
         const size_t smem = fl * sizeof(float);
         if (smem > di.smem_optin) continue;
         c.w_in_smem = ws; c.smem = smem;
@@ -723,5 +786,16 @@ int launch_block_scan(bool fwd, const BlockScanConfig& c, BlockScanArgs args, in
   note_launch();
   return check_launch(fwd ? "block_fwd_kernel" : "block_bwd_kernel");
 }
+
+#ifdef B200GRU_PHASE_TIMING
+extern "C" void b200gru_debug_phase_cycles(unsigned long long* out16, int reset) {
+  cudaDeviceSynchronize();
+  cudaMemcpyFromSymbol(out16, g_phase_cycles, sizeof(unsigned long long) * 16);
+  if (reset) {
+    unsigned long long z[16] = {0};
+    cudaMemcpyToSymbol(g_phase_cycles, z, sizeof(z));
+  }
+}
+#endif
 
 }  // namespace b200gru
