@@ -51,6 +51,7 @@ SIGNATURES = {
     "b200gru_butterfly_forward": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _I, _QP, _QP, _P, _P, _P, _Z, _P]),
     "b200gru_butterfly_backward": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _QP, _QP, _P, _P, _P, _P, _P, _Z, _P]),
     "b200gru_diagonal_backward_noalloc": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _QP, _QP, _P, _P, _P, _P, _P]),
+    "b200gru_device_status": (_I, [_I]),
     "b200gru_launch_count": (ctypes.c_ulonglong, []),
     "b200gru_strerror": (ctypes.c_char_p, [_I]),
     "b200gru_last_cuda_error": (ctypes.c_char_p, []),

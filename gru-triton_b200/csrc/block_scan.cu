@@ -59,6 +59,9 @@ __device__ unsigned long long g_phase_cycles[16];
 #define PHASE_MARK(slot)
 #endif
 
+// Set to 1 by a kernel whose bounded mbarrier wait gave up (a peer CTA never delivered).
+__device__ int g_scan_status;
+
 namespace {
 
 constexpr int NT = BLOCK_SCAN_THREADS;   // threads per CTA
@@ -125,19 +128,54 @@ __device__ __forceinline__ bool reduced_owner(int lane) {
   return N >= 32 ? true : ((lane & ((32 / N) - 1)) == 0);
 }
 
-// Copy `nfloats` contiguous floats (a multiple of 4, 16-byte aligned) that this CTA just
-// wrote at local shared address `src` to the same address in every peer CTA.
-__device__ __forceinline__ void publish_to_peers(cg::cluster_group& cluster, float* src, int nfloats,
-                                                 int C, int rank) {
-  const int nvec = nfloats >> 2;
-  const float4* s4 = reinterpret_cast<const float4*>(src);
-  for (int idx = threadIdx.x; idx < nvec * (C - 1); idx += NT) {
-    const int p = idx / nvec;
-    const int e = idx - p * nvec;
-    const int peer = p + (p >= rank ? 1 : 0);
-    float4* d4 = reinterpret_cast<float4*>(cluster.map_shared_rank(src, peer));
-    d4[e] = s4[e];
-  }
+// ---- asynchronous DSMEM stores signalled through mbarriers -------------------------------
+// The per-step exchange between the CTAs of a cluster is a data flow, not a barrier: every
+// producer writes its values straight into each consumer's shared memory with st.async, which
+// also counts the bytes on the CONSUMER's mbarrier; a consumer proceeds when the bytes of the
+// step have arrived.  Two buffers / two mbarriers alternate by step parity.  Re-use is safe
+// without a second ("empty") handshake: a producer can only be one step ahead, because its
+// next step needs this consumer's own output of the current step.
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_fence_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void mbar_arm(unsigned bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(unsigned bar, unsigned parity) {
+  unsigned ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded wait: gives up after WAIT_LIMIT polls (each poll already blocks for a hardware-defined
+// time slice), records the failure in *status and lets the kernel run to its end.
+constexpr int WAIT_LIMIT = 1 << 20;
+__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, bool& dead, int* status) {
+  if (dead) return false;
+  for (int i = 0; i < WAIT_LIMIT; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+  dead = true;
+  if (status != nullptr) atomicExch(status, 1);
+  return false;
+}
+__device__ __forceinline__ unsigned map_to_rank(unsigned addr, unsigned rank) {
+  unsigned r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void st_async_f32(unsigned raddr, float v, unsigned rbar) {
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];"
+               ::"r"(raddr), "r"(__float_as_uint(v)), "r"(rbar) : "memory");
+}
+__device__ __forceinline__ void st_async_f32x4(unsigned raddr, float a, float b, float c, float d, unsigned rbar) {
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.b32 [%0], {%1, %2, %3, %4}, [%5];"
+               ::"r"(raddr), "r"(__float_as_uint(a)), "r"(__float_as_uint(b)), "r"(__float_as_uint(c)),
+                 "r"(__float_as_uint(d)), "r"(rbar) : "memory");
 }
 
 }  // namespace
@@ -145,9 +183,11 @@ __device__ __forceinline__ void publish_to_peers(cg::cluster_group& cluster, flo
 // ---------------------------------------------------------------------------
 // forward
 // ---------------------------------------------------------------------------
-// shared memory:  hbuf [2][HbP][BT]  fq_in(h) of the whole block, k-major
+// shared memory:  full [2]            mbarriers, one per hbuf parity (16 bytes)
+//                 hbuf [2][HbP][BT]  fq_in(h) of the whole block, k-major
 //                 wsm  [Hb][RS]      W(g, u0+j, k) at [k][g*Hc4 + j]; RS = 4 (mod 8) floats so
 //                                    that float4 reads by lanes with consecutive k hit all banks
+// Warps run free: no CTA-wide barrier inside the time loop.
 template <int BT, int IPW>
 __global__ void __launch_bounds__(NT, 1)
 block_fwd_kernel(const BlockScanArgs a) {
@@ -164,8 +204,18 @@ block_fwd_kernel(const BlockScanArgs a) {
   const int u0 = rank * Hc;                            // first owned unit (inside the block)
   const int nown = max(0, min(Hc, Hb - u0));           // owned units
 
-  float* hbuf = smem;
+  const unsigned full0 = smem_u32(smem);               // two 8-byte mbarriers
+  float* hbuf = smem + 4;
   float* wsm = hbuf + ((2 * HbP * BT + 3) & ~3);        // 16-byte aligned weight rows
+  const unsigned step_bytes = (unsigned)(C * Hc * BT * sizeof(float));
+  if (tid == 0) {
+    mbar_init(full0, 1);
+    mbar_init(full0 + 8, 1);
+    mbar_fence_init();
+    // the sends of steps 0 and 1 land in buffers 1 and 0
+    if (a.T > 1) mbar_arm(full0 + 8, step_bytes);
+    if (a.T > 2) mbar_arm(full0, step_bytes);
+  }
 
   const float* wbase;
   int kstride, gstride;
@@ -203,7 +253,8 @@ block_fwd_kernel(const BlockScanArgs a) {
   // item (group of 4 units) its warp processes.
   const int ridx = reduced_index<NV>(lane);
   const int eb = ridx >> 2, ec = ridx & 3;
-  const bool eown = reduced_owner<NV>(lane) && eb < BT && (b0 + eb) < a.B;
+  const bool esend = reduced_owner<NV>(lane) && eb < BT;       // this lane publishes element (eb, ec)
+  const bool eown = esend && (b0 + eb) < a.B;
   const int nitems = Hc4 >> 2;
 
   float hown[IPW], gr[IPW], gz[IPW], gn[IPW], bias_r[IPW], bias_z[IPW], bias_n[IPW];
@@ -222,17 +273,29 @@ block_fwd_kernel(const BlockScanArgs a) {
       gr[q] = __ldcs(g); gz[q] = __ldcs(g + H); gn[q] = __ldcs(g + 2 * H);
     }
   }
-  if (C > 1) cluster.sync(); else __syncthreads();
+  cluster.sync();            // weights, h_{-1} and the armed mbarriers are in place everywhere
 
   const size_t gi_step = (size_t)a.B * 3 * H;
   const size_t out_step = (size_t)a.B * H;
   const size_t comp = (size_t)a.T * out_step;
+  unsigned phase0 = 0u, phase1 = 0u;      // parity of the next completion of each mbarrier
+  bool dead = false;
 
   PHASE_DECL;
   for (int t = 0; t < a.T; ++t) {
-    const float* hcur = hbuf + (t & 1) * HbP * BT;
-    float* hnxt = hbuf + ((t + 1) & 1) * HbP * BT;
+    const int p = t & 1;
+    const float* hcur = hbuf + p * HbP * BT;
+    float* hnxt = hbuf + (p ^ 1) * HbP * BT;
     PHASE_START();
+    if (t > 0) {
+      mbar_wait(full0 + 8 * p, p ? phase1 : phase0, dead, a.status);
+      if (p) phase1 ^= 1u; else phase0 ^= 1u;
+      // buffer p is filled again by the sends of step t+1
+      if (tid == 0 && t + 1 <= a.T - 2) mbar_arm(full0 + 8 * p, step_bytes);
+    }
+    const unsigned nxt_addr = smem_u32(hnxt);
+    const unsigned nxt_bar = full0 + 8 * (p ^ 1);
+    PHASE_MARK(5);
 
 #pragma unroll
     for (int q = 0; q < IPW; ++q) {
@@ -295,7 +358,7 @@ block_fwd_kernel(const BlockScanArgs a) {
         PHASE_MARK(1);
 
         const int j = item * 4 + ec;
-        if (eown && j < Hc) {
+        if (esend && j < Hc) {
           float hq = 0.f;
           if (valid[q]) {
             const float ghn = s[2] + bias_n[q];
@@ -312,31 +375,27 @@ block_fwd_kernel(const BlockScanArgs a) {
             }
             hq = a.qin.enabled ? fake_quant<true>(hnew, a.qin) : hnew;
           }
-          hnxt[(u0 + j) * BT + eb] = hq;
+          if (t + 1 < a.T) {
+            // publish fq_in(h_t) of this element to every CTA of the cluster (itself included)
+            const unsigned eoff = (unsigned)(((u0 + j) * BT + eb) * sizeof(float));
+            for (int r = 0; r < C; ++r)
+              st_async_f32(map_to_rank(nxt_addr + eoff, r), hq, map_to_rank(nxt_bar, r));
+          }
         }
         gr[q] = ngr; gz[q] = ngz; gn[q] = ngn;
         PHASE_MARK(2);
       }
     }
-    if (C > 1) {
-      __syncthreads();
-      PHASE_MARK(3);
-      publish_to_peers(cluster, hnxt + u0 * BT, Hc * BT, C, rank);
-      PHASE_MARK(4);
-      cluster.sync();
-      PHASE_MARK(5);
-    } else {
-      __syncthreads();
-      PHASE_MARK(3);
-    }
   }
+  cluster.sync();            // nobody leaves while a peer could still be reading or writing
 }
 
 // ---------------------------------------------------------------------------
 // backward (serial part): dgi[t], dh chain, dh0.  Gate activations come from `S`.
 // ---------------------------------------------------------------------------
-// shared memory:  recv [2][C][Hc][BT]   partial dh_via sent by every rank (parity = step)
-//                 xs   [3][Hc4][BTX]    dgh of the owned units, rows padded to a float4 multiple
+// shared memory:  full [2]              mbarriers, one per recv parity (16 bytes)
+//                 recv [2][C][Hc][BT]   partial dh_via sent by every rank (parity = step)
+//                 xs   [2][3][Hc4][BTX] dgh of the owned units (parity = step), rows padded to float4
 //                 wsm  [3*Hc4][Hb4]     W(g, u0+j, k) at [(g*Hc4 + j)][k]   (k contiguous)
 // The second contraction half parks its sums in the idle parity half of `recv`.
 template <int BT, int TW, int GPT>
@@ -355,9 +414,18 @@ block_bwd_kernel(const BlockScanArgs a) {
   const int slice = Hc * BT;                           // floats one rank sends to one peer
   constexpr int BTX = (BT + 3) & ~3;                   // dgh rows padded to float4
 
-  float* recv = smem;                                  // [2][C*slice]
-  float* xs = recv + ((2 * C * slice + 3) & ~3);       // [3*Hc4][BTX]
-  float* wsm = xs + 3 * Hc4 * BTX;
+  const unsigned full0 = smem_u32(smem);               // two 8-byte mbarriers
+  float* recv = smem + 4;                              // [2][C*slice]
+  float* xs2 = recv + ((2 * C * slice + 3) & ~3);      // [2][3*Hc4][BTX]
+  const unsigned step_bytes = (unsigned)(C * slice * sizeof(float));
+  if (tid == 0) {
+    mbar_init(full0, 1);
+    mbar_init(full0 + 8, 1);
+    mbar_fence_init();
+    mbar_arm(full0, step_bytes);
+    if (a.T > 1) mbar_arm(full0 + 8, step_bytes);
+  }
+  float* wsm = xs2 + 2 * 3 * Hc4 * BTX;
 
   const float* wbase;
   size_t gstride;      // between gates
@@ -382,7 +450,7 @@ block_bwd_kernel(const BlockScanArgs a) {
     wbase = a.W + (size_t)n * a.w_block_stride + (size_t)u0 * Hb;
   }
   for (int idx = tid; idx < 2 * C * slice; idx += NT) recv[idx] = 0.f;
-  for (int idx = tid; idx < 3 * Hc4 * BTX; idx += NT) xs[idx] = 0.f;
+  for (int idx = tid; idx < 2 * 3 * Hc4 * BTX; idx += NT) xs2[idx] = 0.f;
 
   const size_t gi_step = (size_t)a.B * 3 * H;
   const size_t out_step = (size_t)a.B * H;
@@ -414,7 +482,9 @@ block_bwd_kernel(const BlockScanArgs a) {
       c_hp[q] = (t > 0) ? a.out[o - out_step] : a.h0[off[q]];
     }
   }
-  if (C > 1) cluster.sync(); else __syncthreads();
+  cluster.sync();            // weights, zeroed buffers and the armed mbarriers are in place everywhere
+  unsigned phase0 = 0u, phase1 = 0u;      // parity of the next completion of each mbarrier
+  bool dead = false;
 
   // contraction geometry: k tiles of 32*TW positions, NH halves of the (gate, unit) index;
   // ntiles * NH <= NW whenever NH > 1, so one round of warps covers both halves of a tile.
@@ -429,7 +499,16 @@ block_bwd_kernel(const BlockScanArgs a) {
     PHASE_START();
     const int par = (a.T - 1 - t) & 1;
     float* rcur = recv + par * C * slice;
-    float* park = recv + (par ^ 1) * C * slice;        // idle this step: second-half sums park here
+    // The other parity buffer is idle during this step's contraction, so the second-half sums
+    // park there.  A peer one step ahead may already write its slice [r*slice, (r+1)*slice) of
+    // that buffer; this is exactly the park rows of the positions rank r owns, and r can only be
+    // ahead after it has received the combined values of those rows -- i.e. after they were read.
+    float* park = recv + (par ^ 1) * C * slice;
+    const unsigned rcur_addr = smem_u32(rcur);
+    const unsigned rcur_bar = full0 + 8 * par;
+    // dgh alternates between two buffers: a warp that already has its partials for this step may
+    // run ahead into the next step's gate phase while a slower warp still reads this step's dgh.
+    float* xs = xs2 + par * 3 * Hc4 * BTX;
 
     // ---- gate gradients of the owned elements
     float dh_direct[GPT], mask_in[GPT];
@@ -554,26 +633,30 @@ block_bwd_kernel(const BlockScanArgs a) {
         const int dst0 = kbase / Hc, jj0 = kbase - dst0 * Hc;
         if ((TW * BT) % 4 == 0 && jj0 + TW <= Hc) {
           // the TW positions of this lane belong to one rank and form one contiguous run there
-          float* base = ((dst0 == rank || C == 1) ? rcur : cluster.map_shared_rank(rcur, dst0)) + rank * slice + jj0 * BT;
+          const unsigned doff = (unsigned)((rank * slice + jj0 * BT) * sizeof(float));
+          const unsigned daddr = map_to_rank(rcur_addr + doff, dst0), dbar = map_to_rank(rcur_bar, dst0);
 #pragma unroll
           for (int v = 0; v < TW * BT / 4; ++v)
-            *reinterpret_cast<float4*>(base + 4 * v) = make_float4(acc[4 * v], acc[4 * v + 1], acc[4 * v + 2], acc[4 * v + 3]);
+            st_async_f32x4(daddr + 16 * v, acc[4 * v], acc[4 * v + 1], acc[4 * v + 2], acc[4 * v + 3], dbar);
         } else {
 #pragma unroll
           for (int i = 0; i < TW; ++i) {
             const int k = kbase + i;
             if (k < HbP) {
               const int dst = k / Hc, jj = k - dst * Hc;
-              float* base = (dst == rank || C == 1) ? rcur : cluster.map_shared_rank(rcur, dst);
+              const unsigned doff = (unsigned)((rank * slice + jj * BT) * sizeof(float));
+              const unsigned daddr = map_to_rank(rcur_addr + doff, dst), dbar = map_to_rank(rcur_bar, dst);
 #pragma unroll
-              for (int bb = 0; bb < BT; ++bb) base[rank * slice + jj * BT + bb] = acc[i * BT + bb];
+              for (int bb = 0; bb < BT; ++bb) st_async_f32(daddr + 4 * bb, acc[i * BT + bb], dbar);
             }
           }
         }
       }
     }
     PHASE_MARK(12);
-    if (C > 1) cluster.sync(); else __syncthreads();
+    mbar_wait(rcur_bar, par ? phase1 : phase0, dead, a.status);
+    if (par) phase1 ^= 1u; else phase0 ^= 1u;
+    if (tid == 0 && t >= 2) mbar_arm(rcur_bar, step_bytes);     // this buffer receives again two steps on
     PHASE_MARK(13);
 
     // ---- dh for the owned elements: C partials in rank order
@@ -591,6 +674,7 @@ block_bwd_kernel(const BlockScanArgs a) {
 #pragma unroll
   for (int q = 0; q < GPT; ++q)
     if (valid[q]) a.dh0[off[q]] = dh_acc[q];
+  cluster.sync();            // nobody leaves while a peer could still be reading or writing
 }
 
 // ---------------------------------------------------------------------------
@@ -703,6 +787,22 @@ static int max_active_clusters(KernelFn fn, int C, size_t smem) {
 
 static int round_up(int x, int m) { return (x + m - 1) / m * m; }
 
+// Device address of g_scan_status on the current device (looked up once per device).
+static int* scan_status_address() {
+  constexpr int MAX_DEV = 64;
+  static std::mutex mu;
+  static int* table[MAX_DEV] = {nullptr};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEV) return nullptr;
+  std::lock_guard<std::mutex> lk(mu);
+  if (table[dev] == nullptr) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_scan_status) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+    table[dev] = static_cast<int*>(p);
+  }
+  return table[dev];
+}
+
 // Pick the cluster size, batch tile and weight placement that minimise a simple cost model:
 //   step = max(FMA issue, shared-memory streaming) + barrier;  total = waves * step.
 bool choose_block_config(bool fwd, int B, int Hb, int nb, BlockScanConfig* out) {
@@ -739,8 +839,8 @@ bool choose_block_config(bool fwd, int B, int Hb, int nb, BlockScanConfig* out) 
       c.GPT = (Hc * BT <= NT) ? 1 : 8;
       for (int ws = 1; ws >= 0; --ws) {
         size_t fl;
-        if (fwd) fl = (size_t)((2 * HbP * BT + 3) & ~3) + (ws ? (size_t)Hb * c.RS : 0);
-        else fl = (size_t)((2 * C * Hc * BT + 3) & ~3) + (size_t)3 * Hc4 * ((BT + 3) & ~3) + (ws ? (size_t)3 * Hc4 * Hb4 : 0);
+        if (fwd) fl = 4 + (size_t)((2 * HbP * BT + 3) & ~3) + (ws ? (size_t)Hb * c.RS : 0);
+        else fl = 4 + (size_t)((2 * C * Hc * BT + 3) & ~3) + (size_t)2 * 3 * Hc4 * ((BT + 3) & ~3) + (ws ? (size_t)3 * Hc4 * Hb4 : 0);
         const size_t smem = fl * sizeof(float);
         if (smem > di.smem_optin) continue;
         c.w_in_smem = ws; c.smem = smem;
@@ -764,6 +864,7 @@ bool choose_block_config(bool fwd, int B, int Hb, int nb, BlockScanConfig* out) 
 int launch_block_scan(bool fwd, const BlockScanConfig& c, BlockScanArgs args, int nb, cudaStream_t st) {
   args.C = c.C; args.Hc = c.Hc; args.Hc4 = c.Hc4; args.HbP = c.HbP; args.Hb4 = c.Hb4; args.RS = c.RS;
   args.NH = c.NH; args.w_in_smem = c.w_in_smem; args.WtR = c.Hb4 + 4;
+  args.status = scan_status_address();
   KernelFn fn = pick_kernel(fwd, c);
   const int active = max_active_clusters(fn, c.C, c.smem);                      // also sets the attributes
   static const bool debug = getenv("B200GRU_DEBUG") != nullptr;
@@ -785,6 +886,17 @@ int launch_block_scan(bool fwd, const BlockScanConfig& c, BlockScanArgs args, in
   cudaLaunchKernelEx(&cfg, fn, args);
   note_launch();
   return check_launch(fwd ? "block_fwd_kernel" : "block_bwd_kernel");
+}
+
+extern "C" int b200gru_device_status(int reset) {
+  int v = 0;
+  if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+  if (cudaMemcpyFromSymbol(&v, g_scan_status, sizeof(int)) != cudaSuccess) return -1;
+  if (reset && v != 0) {
+    const int z = 0;
+    cudaMemcpyToSymbol(g_scan_status, &z, sizeof(int));
+  }
+  return v;
 }
 
 #ifdef B200GRU_PHASE_TIMING

@@ -22,6 +22,7 @@ struct BlockScanArgs {
   const float* dout;
   float* dgi;
   float* dh0;
+  int* status;         // device word set to 1 if a bounded wait inside a kernel gave up
   int T, B, H;
   int nb, Hb;
   long long w_gate_stride, w_block_stride;

@@ -174,6 +174,15 @@ int b200gru_diagonal_backward_noalloc(const float* gi, const float* h0, const fl
  * counterpart. */
 unsigned long long b200gru_launch_count(void);
 
+/* Health of the in-kernel waits on the current device.  The dense / block-diagonal kernels
+ * exchange data between the CTAs of a cluster and wait for it with a bounded number of polls;
+ * a wait that gives up sets a device flag and lets the kernel finish (its results are then
+ * invalid).  This call SYNCHRONISES the device and returns that flag (0 = healthy, 1 = a wait
+ * gave up, -1 = CUDA error); reset != 0 clears it.  Meant for tests and post-mortems, not for
+ * the hot path.  No reference counterpart: the reference's spin-wait is unbounded
+ * (scan.py:202-205). */
+int b200gru_device_status(int reset);
+
 /* Human-readable text for a b200gru_status; plus the text of the last CUDA error
  * seen by a launch in this thread (empty string if none). */
 const char* b200gru_strerror(int status);
