@@ -17,7 +17,7 @@ CSRC = os.path.join(PKG_DIR, "csrc")
 INCLUDE = os.path.join(os.path.dirname(PKG_DIR), "include")
 LIB_DIR = os.path.join(PKG_DIR, "lib")
 OBJ_DIR = os.path.join(PKG_DIR, "build")
-LIB_PATH = os.path.join(LIB_DIR, "libb200gru.so")
+LIB_PATH = os.path.join(LIB_DIR, os.environ.get("B200GRU_LIB_NAME", "libb200gru.so"))
 
 SOURCES = ["api.cu", "diag_scan.cu", "block_scan.cu", "block_gemm.cu", "butterfly_scan.cu"]
 

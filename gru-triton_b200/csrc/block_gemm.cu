@@ -212,11 +212,13 @@ weight_grads_kernel(const BlockGemmArgs a, float* __restrict__ dst, int rows_per
     for (int m = 0; m < NH_; ++m) (&Hs[0][0])[tid + m * 256] = hreg[m];
   };
 
-  float acc[3][8][2];
+  float2 acc[3][2][4];                                  // [gate][k of the pair][unit pair]: packed FP32 FMA
 #pragma unroll
   for (int g = 0; g < 3; ++g)
 #pragma unroll
-    for (int i = 0; i < 8; ++i) acc[g][i][0] = acc[g][i][1] = 0.f;
+    for (int kk = 0; kk < 2; ++kk)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[g][kk][i] = make_float2(0.f, 0.f);
 
   fetch(r_begin);
   for (int r0 = r_begin; r0 < r_end; r0 += WG_R) {
@@ -226,15 +228,17 @@ weight_grads_kernel(const BlockGemmArgs a, float* __restrict__ dst, int rows_per
 #pragma unroll 4
     for (int r = 0; r < WG_R; ++r) {
       const float2 h = *reinterpret_cast<const float2*>(&Hs[r][2 * lane]);
+      const float2 h0 = make_float2(h.x, h.x), h1 = make_float2(h.y, h.y);
 #pragma unroll
       for (int g = 0; g < 3; ++g) {
         const float4 d0 = *reinterpret_cast<const float4*>(&Ds[r][g * WG_O + warp * 8]);
         const float4 d1 = *reinterpret_cast<const float4*>(&Ds[r][g * WG_O + warp * 8 + 4]);
-        const float d[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
+        const float2 d[4] = {make_float2(d0.x, d0.y), make_float2(d0.z, d0.w), make_float2(d1.x, d1.y),
+                             make_float2(d1.z, d1.w)};
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          acc[g][i][0] = fmaf(d[i], h.x, acc[g][i][0]);
-          acc[g][i][1] = fmaf(d[i], h.y, acc[g][i][1]);
+        for (int i = 0; i < 4; ++i) {
+          acc[g][0][i] = __ffma2_rn(d[i], h0, acc[g][0][i]);
+          acc[g][1][i] = __ffma2_rn(d[i], h1, acc[g][1][i]);
         }
       }
     }
@@ -252,8 +256,9 @@ weight_grads_kernel(const BlockGemmArgs a, float* __restrict__ dst, int rows_per
       const int o = ot * WG_O + warp * 8 + i;
       if (o < Hb) {
         float* p = base + (size_t)g * a.w_gate_stride + (size_t)o * Hb + k;
-        p[0] = acc[g][i][0];
-        if (k + 1 < Hb) p[1] = acc[g][i][1];
+        const float2 v0 = acc[g][0][i >> 1], v1 = acc[g][1][i >> 1];
+        p[0] = (i & 1) ? v0.y : v0.x;
+        if (k + 1 < Hb) p[1] = (i & 1) ? v1.y : v1.x;
       }
     }
 }

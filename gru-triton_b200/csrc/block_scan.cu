@@ -178,6 +178,50 @@ __device__ __forceinline__ void st_async_f32x4(unsigned raddr, float a, float b,
                  "r"(__float_as_uint(d)), "r"(rbar) : "memory");
 }
 
+// Weights of 4 units x 3 gates at contraction index k, and the BT hidden values of k.
+template <int BT, bool SMEM>
+__device__ __forceinline__ void fwd_load(const float* wp, int kstride, int gstride, const float* hcur, int k,
+                                         float4 (&w)[3], float (&hv)[BT]) {
+#pragma unroll
+  for (int g = 0; g < 3; ++g) {
+    if (SMEM) {
+      w[g] = *reinterpret_cast<const float4*>(wp + k * kstride + g * gstride);
+    } else {
+      const float* p = wp + (size_t)k * kstride + g * gstride;
+      w[g] = make_float4(__ldg(p), __ldg(p + 1), __ldg(p + 2), __ldg(p + 3));
+    }
+  }
+  load_rows<BT>(hcur + k * BT, hv);
+}
+
+// Packed FP32 FMA (two IEEE fused multiply-adds per instruction on sm_100): units (0,1) and
+// (2,3) of a weight float4 share one instruction; the hidden value is duplicated once per row.
+template <int BT>
+__device__ __forceinline__ void fwd_fma(float2 (&acc)[3][2][BT], const float4 (&w)[3], const float (&hv)[BT]) {
+#pragma unroll
+  for (int b = 0; b < BT; ++b) {
+    const float2 hh = make_float2(hv[b], hv[b]);
+#pragma unroll
+    for (int g = 0; g < 3; ++g) {
+      acc[g][0][b] = __ffma2_rn(make_float2(w[g].x, w[g].y), hh, acc[g][0][b]);
+      acc[g][1][b] = __ffma2_rn(make_float2(w[g].z, w[g].w), hh, acc[g][1][b]);
+    }
+  }
+}
+
+// acc[g][c][b] += sum over this lane's k (= lane, lane+32, ...) of W(g, unit c, k) * h[k][b].
+template <int BT, bool SMEM>
+__device__ __forceinline__ void fwd_contract(float2 (&acc)[3][2][BT], const float* wp, int kstride, int gstride,
+                                             const float* hcur, int lane, int Hb) {
+#pragma unroll 2
+  for (int k = lane; k < Hb; k += 32) {
+    float4 w[3];
+    float hv[BT];
+    fwd_load<BT, SMEM>(wp, kstride, gstride, hcur, k, w, hv);
+    fwd_fma<BT>(acc, w, hv);
+  }
+}
+
 }  // namespace
 
 // ---------------------------------------------------------------------------
@@ -308,40 +352,17 @@ block_fwd_kernel(const BlockScanArgs a) {
           ngr = __ldcs(g); ngz = __ldcs(g + H); ngn = __ldcs(g + 2 * H);
         }
 
-        float acc[3][4][BT];
+        float2 acc[3][2][BT];                            // [gate][unit pair][row]
 #pragma unroll
         for (int g = 0; g < 3; ++g)
 #pragma unroll
-          for (int c = 0; c < 4; ++c)
+          for (int c = 0; c < 2; ++c)
 #pragma unroll
-            for (int b = 0; b < BT; ++b) acc[g][c][b] = 0.f;
+            for (int b = 0; b < BT; ++b) acc[g][c][b] = make_float2(0.f, 0.f);
 
         const float* wp = wbase + item * 4;
-#pragma unroll 2
-        for (int k = lane; k < Hb; k += 32) {
-          float4 w[3];
-          if (a.w_in_smem) {
-#pragma unroll
-            for (int g = 0; g < 3; ++g) w[g] = *reinterpret_cast<const float4*>(wp + k * kstride + g * gstride);
-          } else {
-#pragma unroll
-            for (int g = 0; g < 3; ++g) {
-              const float* p = wp + (size_t)k * kstride + g * gstride;
-              w[g] = make_float4(__ldg(p), __ldg(p + 1), __ldg(p + 2), __ldg(p + 3));
-            }
-          }
-          float hv[BT];
-          load_rows<BT>(hcur + k * BT, hv);
-#pragma unroll
-          for (int g = 0; g < 3; ++g)
-#pragma unroll
-            for (int b = 0; b < BT; ++b) {
-              acc[g][0][b] = fmaf(w[g].x, hv[b], acc[g][0][b]);
-              acc[g][1][b] = fmaf(w[g].y, hv[b], acc[g][1][b]);
-              acc[g][2][b] = fmaf(w[g].z, hv[b], acc[g][2][b]);
-              acc[g][3][b] = fmaf(w[g].w, hv[b], acc[g][3][b]);
-            }
-        }
+        if (a.w_in_smem) fwd_contract<BT, true>(acc, wp, kstride, gstride, hcur, lane, Hb);
+        else fwd_contract<BT, false>(acc, wp, kstride, gstride, hcur, lane, Hb);
         PHASE_MARK(0);
 
         float s[3];
@@ -351,7 +372,10 @@ block_fwd_kernel(const BlockScanArgs a) {
 #pragma unroll
           for (int b = 0; b < BTP; ++b)
 #pragma unroll
-            for (int c = 0; c < 4; ++c) vals[b * 4 + c] = (b < BT) ? acc[g][c][b < BT ? b : 0] : 0.f;
+            for (int c = 0; c < 4; ++c) {
+              const float2 pr = acc[g][c >> 1][b < BT ? b : 0];
+              vals[b * 4 + c] = (b < BT) ? ((c & 1) ? pr.y : pr.x) : 0.f;
+            }
           warp_reduce_scatter<NV>(vals, lane);
           s[g] = vals[0];
         }
@@ -574,10 +598,22 @@ block_bwd_kernel(const BlockScanArgs a) {
               }
               float xv[BTX];
               load_rows<BTX>(xp, xv);
+              if constexpr (TW == 4) {
+                // packed FP32 FMA: positions (0,1) and (2,3) of the weight float4 share an instruction
 #pragma unroll
-              for (int i = 0; i < TW; ++i)
+                for (int bb = 0; bb < BT; ++bb) {
+                  const float2 xx = make_float2(xv[bb], xv[bb]);
+                  const float2 r01 = __ffma2_rn(make_float2(w[0], w[1]), xx, make_float2(acc[0 * BT + bb], acc[1 * BT + bb]));
+                  const float2 r23 = __ffma2_rn(make_float2(w[2], w[3]), xx, make_float2(acc[2 * BT + bb], acc[3 * BT + bb]));
+                  acc[0 * BT + bb] = r01.x; acc[1 * BT + bb] = r01.y;
+                  acc[2 * BT + bb] = r23.x; acc[3 * BT + bb] = r23.y;
+                }
+              } else {
 #pragma unroll
-                for (int bb = 0; bb < BT; ++bb) acc[i * BT + bb] = fmaf(w[i], xv[bb], acc[i * BT + bb]);
+                for (int i = 0; i < TW; ++i)
+#pragma unroll
+                  for (int bb = 0; bb < BT; ++bb) acc[i * BT + bb] = fmaf(w[i], xv[bb], acc[i * BT + bb]);
+              }
             }
           }
         } else {
