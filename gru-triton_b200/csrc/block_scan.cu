@@ -45,20 +45,6 @@ namespace cg = cooperative_groups;
 
 namespace b200gru {
 
-// Debug aid, compiled in only with -DB200GRU_PHASE_TIMING: thread 0 of CTA (0,0) adds the
-// clock64() distance between consecutive marks of a step to g_phase_cycles[slot].
-#ifdef B200GRU_PHASE_TIMING
-__device__ unsigned long long g_phase_cycles[16];
-#define PHASE_DECL long long ph_last = 0; const bool ph_on = (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0)
-#define PHASE_START() do { if (ph_on) ph_last = clock64(); } while (0)
-#define PHASE_MARK(slot) do { if (ph_on) { long long ph_now = clock64(); \
-    atomicAdd(&g_phase_cycles[slot], (unsigned long long)(ph_now - ph_last)); ph_last = ph_now; } } while (0)
-#else
-#define PHASE_DECL
-#define PHASE_START()
-#define PHASE_MARK(slot)
-#endif
-
 // Set to 1 by a kernel whose bounded mbarrier wait gave up (a peer CTA never delivered).
 __device__ int g_scan_status;
 
@@ -932,18 +918,11 @@ extern "C" int b200gru_device_status(int reset) {
     const int z = 0;
     cudaMemcpyToSymbol(g_scan_status, &z, sizeof(int));
   }
-  return v;
+  const int d = diag_read_status(reset);
+  if (d < 0) return -1;
+  return (v != 0 || d != 0) ? 1 : 0;
 }
-
-#ifdef B200GRU_PHASE_TIMING
-extern "C" void b200gru_debug_phase_cycles(unsigned long long* out16, int reset) {
-  cudaDeviceSynchronize();
-  cudaMemcpyFromSymbol(out16, g_phase_cycles, sizeof(unsigned long long) * 16);
-  if (reset) {
-    unsigned long long z[16] = {0};
-    cudaMemcpyToSymbol(g_phase_cycles, z, sizeof(z));
-  }
-}
-#endif
 
 }  // namespace b200gru
+
+B200GRU_DEFINE_PHASE_READER(b200gru_debug_phase_cycles)

@@ -176,7 +176,9 @@ bfly_fwd_kernel(const BflyArgs a) {
   const size_t out_step = (size_t)a.B * H;
   const size_t comp = (size_t)a.T * out_step;
 
+  PHASE_DECL;
   for (int t = 0; t < a.T; ++t) {
+    PHASE_START();
     // gi[t] for the tile: lands while the butterflies run
     for (int idx = tid; idx < 3 * BT * H; idx += NT) {
       const int g = idx / (BT * H);
@@ -186,14 +188,18 @@ bfly_fwd_kernel(const BflyArgs a) {
       if (row < a.B) cp_async4(gbuf + idx, a.gi + (size_t)t * gi_step + (size_t)row * 3 * H + g * H + i);
     }
     cp_async_commit();
+    PHASE_MARK(0);
 
     for (int p = 0; p < a.npasses; ++p) {
       if (p == 0) run_pass<BT, false>(a.passes[0], hq, 0, st, BT * Hpad, tw, Hpad, a.logn, a.nstages);
       else run_pass<BT, false>(a.passes[p], st, BT * Hpad, st, BT * Hpad, tw, Hpad, a.logn, a.nstages);
+      PHASE_MARK(1 + (p < 4 ? p : 4));
       __syncthreads();
+      PHASE_MARK(6);
     }
     cp_async_wait_all();
     __syncthreads();
+    PHASE_MARK(7);
 
     for (int idx = tid; idx < BT * H; idx += NT) {
       const int b = idx / H, i = idx - b * H;
@@ -217,7 +223,9 @@ bfly_fwd_kernel(const BflyArgs a) {
       hraw[b * Hpad + i] = hnew;
       hq[b * Hpad + i] = a.qin.enabled ? fake_quant<true>(hnew, a.qin) : hnew;
     }
+    PHASE_MARK(8);
     __syncthreads();
+    PHASE_MARK(9);
   }
 }
 
@@ -551,3 +559,5 @@ int bfly_launch_wgrad(BflyArgs a, float* partial, float* dtw, cudaStream_t st) {
 }
 
 }  // namespace b200gru
+
+B200GRU_DEFINE_PHASE_READER(b200gru_debug_phase_cycles_bfly)

@@ -10,36 +10,91 @@
 #pragma once
 
 #include <cuda_runtime.h>
+#include <math.h>
 #include <stdint.h>
 
 #include "../../include/b200gru.h"
 
 namespace b200gru {
 
+// Debug aid, compiled in only with -DB200GRU_PHASE_TIMING: thread 0 of CTA (0,0) adds the
+// clock64() distance between consecutive marks of a step to g_phase_cycles[slot].
+#ifdef B200GRU_PHASE_TIMING
+static __device__ unsigned long long g_phase_cycles[16];   // one copy per translation unit
+#define PHASE_DECL long long ph_last = 0; const bool ph_on = (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0)
+#define PHASE_START() do { if (ph_on) ph_last = clock64(); } while (0)
+#define PHASE_MARK(slot) do { if (ph_on) { long long ph_now = clock64(); \
+    atomicAdd(&g_phase_cycles[slot], (unsigned long long)(ph_now - ph_last)); ph_last = ph_now; } } while (0)
+#define B200GRU_DEFINE_PHASE_READER(name)                                                   \
+  extern "C" void name(unsigned long long* out16, int reset) {                                \
+    cudaDeviceSynchronize();                                                                  \
+    cudaMemcpyFromSymbol(out16, b200gru::g_phase_cycles, sizeof(unsigned long long) * 16);    \
+    if (reset) {                                                                              \
+      unsigned long long z[16] = {0};                                                         \
+      cudaMemcpyToSymbol(b200gru::g_phase_cycles, z, sizeof(z));                              \
+    }                                                                                         \
+  }
+#else
+#define B200GRU_DEFINE_PHASE_READER(name)
+#define PHASE_DECL
+#define PHASE_START()
+#define PHASE_MARK(slot)
+#endif
+
 struct Quant {
   float scale;
+  float inv_scale;   // RN(1 / scale), used by the exact division below
   float qmin;
   float qmax;
   int enabled;
 };
 
+// Correctly rounded float reciprocal of s: among the double-rounded candidate and its two
+// neighbours pick the one whose product with s is closest to 1 (products of two floats are
+// exact in double).
+__host__ inline float exact_reciprocal(float s) {
+  const float y = (float)(1.0 / (double)s);
+  const float cand[3] = {y, nextafterf(y, 0.f), nextafterf(y, 2.f * y)};
+  float best = y;
+  double err = fabs(1.0 - (double)y * (double)s);
+  for (int i = 1; i < 3; ++i) {
+    const double e = fabs(1.0 - (double)cand[i] * (double)s);
+    if (e < err) { err = e; best = cand[i]; }
+  }
+  return best;
+}
+
 __host__ inline Quant make_quant(const b200gru_quant* q) {
   Quant r;
   if (q == nullptr || !q->enabled) {
-    r.scale = 1.f; r.qmin = 0.f; r.qmax = 0.f; r.enabled = 0;
+    r.scale = 1.f; r.inv_scale = 1.f; r.qmin = 0.f; r.qmax = 0.f; r.enabled = 0;
   } else {
-    r.scale = q->scale; r.qmin = (float)q->qmin; r.qmax = (float)q->qmax; r.enabled = 1;
+    r.scale = q->scale; r.inv_scale = exact_reciprocal(q->scale);
+    r.qmin = (float)q->qmin; r.qmax = (float)q->qmax; r.enabled = 1;
   }
   return r;
 }
 
+// 1 / (1 + e^-x): the reciprocal of a float is correctly rounded by rcp.rn, which is what the
+// IEEE division 1.0f / y returns.
 __device__ __forceinline__ float sigmoidf_acc(float x) {
-  return 1.0f / (1.0f + expf(-x));
+  return __frcp_rn(1.0f + expf(-x));
+}
+
+// x / s, correctly rounded (bit-identical to IEEE division), for the fixed divisor s of a
+// quantizer: one multiply by RN(1/s) and one FMA-exact residual correction (Markstein).  The
+// generic division routine costs about four times as many instructions.
+__device__ __forceinline__ float div_by_scale(float x, const Quant& q) {
+  const float q0 = x * q.inv_scale;
+  const float r = fmaf(-q0, q.scale, x);
+  const float q1 = fmaf(r, q.inv_scale, q0);
+  if (!(fabsf(q1) <= 3.0e38f)) return __fdiv_rn(x, q.scale);     // overflow / NaN: take the slow path
+  return q1;
 }
 
 // Unclamped integer code of x (as float): rint(x / s).
 __device__ __forceinline__ float fq_code(float x, const Quant& q) {
-  return rintf(__fdiv_rn(x, q.scale));
+  return rintf(div_by_scale(x, q));
 }
 
 template <bool ON>
@@ -96,6 +151,9 @@ __device__ __forceinline__ GateGrad gru_gate_grads(float dh, float r, float z, f
 
 __host__ __device__ inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 __host__ __device__ inline int cdiv(int a, int b) { return (a + b - 1) / b; }
+
+// Health flag of the diagonal kernels' bounded waits (diag_scan.cu); -1 on CUDA error.
+int diag_read_status(int reset);
 
 // Launch bookkeeping shared by all translation units (defined in api.cu).
 void note_launch(int n = 1);

@@ -12,6 +12,7 @@
 // Follows the step arithmetic of src/gru_qat/triton_kernels/scan_diagonal.py
 // (forward :79-124, backward :564-647).
 
+#include <cstdlib>
 #include <mutex>
 
 #include "common.cuh"
@@ -125,6 +126,127 @@ diag_fwd_kernel(const float* __restrict__ gi, const float* __restrict__ h0,
       }
     }
   }
+}
+
+// ---------------------------------------------------------------------------
+// forward, TMA-staged (large problems)
+// ---------------------------------------------------------------------------
+// The register ring above cannot keep more than a few loads per warp in flight: a warp has
+// only a handful of scoreboards, so waiting for an old load also waits for the youngest one.
+// Here gi is staged through shared memory instead: one elected thread issues bulk copies
+// (cp.async.bulk, the 1-D TMA path) DT_STAGES time steps ahead, completion is counted on an
+// mbarrier per stage, and the 64 threads of the CTA only ever read shared memory.  A CTA owns
+// 256 adjacent hidden units of one batch row (3 x 1 KB per step); small CTAs keep the 148 SMs
+// evenly loaded (about seven CTAs per SM at B*H = 256 Ki).
+constexpr int DT_THREADS = 64;
+constexpr int DT_COLS = DT_THREADS * 4;
+constexpr int DT_STAGES = 8;
+constexpr int DT_WAIT_LIMIT = 1 << 20;
+
+static __device__ int g_diag_status;     // set to 1 if a bounded wait gave up
+
+__device__ __forceinline__ unsigned dt_smem(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void dt_bulk_load(unsigned dst, const void* src, unsigned bytes, unsigned bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ bool dt_try_wait(unsigned bar, unsigned parity) {
+  unsigned ok;
+  asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+               "selp.u32 %0, 1, 0, p;\n\t}" : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+
+template <bool QIN, bool QOUT>
+__global__ void __launch_bounds__(DT_THREADS)
+diag_fwd_tma_kernel(const float* __restrict__ gi, const float* __restrict__ h0,
+                    const float* __restrict__ W, const float* __restrict__ bh,
+                    float* __restrict__ out, int T, int B, int H, Quant qin, Quant qout) {
+  __shared__ __align__(128) float stage[DT_STAGES][3][DT_COLS];
+  __shared__ __align__(8) unsigned long long full[DT_STAGES];
+  const int tid = threadIdx.x;
+  const int b = blockIdx.y;
+  const int i0 = blockIdx.x * DT_COLS;
+  const int ncols = min(DT_COLS, H - i0);                 // multiple of 4 (H % 4 == 0)
+  const unsigned seg_bytes = (unsigned)ncols * sizeof(float);
+  const bool active = 4 * tid < ncols;
+  const int i = i0 + 4 * tid;
+
+  const size_t gi_step = (size_t)B * 3 * H;
+  const size_t out_step = (size_t)B * H;
+  const float* grow = gi + (size_t)b * 3 * H + i0;        // + t*gi_step + g*H
+
+  auto issue = [&](int t) {                                // thread 0 only
+    const int s = t % DT_STAGES;
+    const unsigned bar = dt_smem(&full[s]);
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(3u * seg_bytes) : "memory");
+#pragma unroll
+    for (int g = 0; g < 3; ++g)
+      dt_bulk_load(dt_smem(&stage[s][g][0]), grow + (size_t)t * gi_step + (size_t)g * H, seg_bytes, bar);
+  };
+
+  if (tid == 0) {
+    for (int s = 0; s < DT_STAGES; ++s)
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(dt_smem(&full[s])) : "memory");
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    for (int t = 0; t < DT_STAGES && t < T; ++t) issue(t);
+  }
+
+  float wr[4], wz[4], wn[4], br[4], bz[4], bn[4], h[4];
+#pragma unroll
+  for (int v = 0; v < 4; ++v) { wr[v] = wz[v] = wn[v] = br[v] = bz[v] = bn[v] = h[v] = 0.f; }
+  if (active) {
+    ld_plain<4>(W + i, wr); ld_plain<4>(W + H + i, wz); ld_plain<4>(W + 2 * H + i, wn);
+    ld_plain<4>(bh + i, br); ld_plain<4>(bh + H + i, bz); ld_plain<4>(bh + 2 * H + i, bn);
+    ld_plain<4>(h0 + (size_t)b * H + i, h);
+  }
+  __syncthreads();                                         // barriers initialised before anyone polls
+
+  float* op = out + (size_t)b * H + i;
+  bool dead = false;
+  for (int t = 0; t < T; ++t) {
+    const int s = t % DT_STAGES;
+    const unsigned bar = dt_smem(&full[s]);
+    const unsigned parity = (unsigned)(t / DT_STAGES) & 1u;
+    if (!dead) {
+      int spin = 0;
+      while (!dt_try_wait(bar, parity)) {
+        if (++spin > DT_WAIT_LIMIT) { dead = true; atomicExch(&g_diag_status, 1); break; }
+      }
+    }
+    float gr[4], gz[4], gn[4];
+    if (active) {
+      ld_plain<4>(&stage[s][0][4 * tid], gr);
+      ld_plain<4>(&stage[s][1][4 * tid], gz);
+      ld_plain<4>(&stage[s][2][4 * tid], gn);
+    }
+    __syncthreads();                                       // stage s has been read by everyone
+    if (tid == 0 && t + DT_STAGES < T) issue(t + DT_STAGES);
+    if (active) {
+      float o[4];
+#pragma unroll
+      for (int v = 0; v < 4; ++v) {
+        const float hq = fake_quant<QIN>(h[v], qin);
+        const float ghr = wr[v] * hq + br[v];
+        const float ghz = wz[v] * hq + bz[v];
+        const float ghn = wn[v] * hq + bn[v];
+        const GateOut g = gru_gates(gr[v], gz[v], gn[v], ghr, ghz, ghn, h[v]);
+        h[v] = fake_quant<QOUT>(g.h_raw, qout);
+        o[v] = h[v];
+      }
+      st_vec<4>(op + (size_t)t * out_step, o);
+    }
+  }
+}
+
+int diag_read_status(int reset) {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_diag_status, sizeof(int)) != cudaSuccess) return -1;
+  if (reset && v != 0) {
+    const int z = 0;
+    cudaMemcpyToSymbol(g_diag_status, &z, sizeof(int));
+  }
+  return v;
 }
 
 // ---------------------------------------------------------------------------
@@ -266,6 +388,10 @@ diag_bwd_kernel(const float* __restrict__ gi, const float* __restrict__ h0,
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 static int pick_vec(int B, int H, bool ptr_ok) {
+  if (const char* e = getenv("B200GRU_DIAG_VEC")) {          // tuning override
+    const int v = atoi(e);
+    if ((v == 1) || (v == 2 && ptr_ok && H % 2 == 0) || (v == 4 && ptr_ok && H % 4 == 0)) return v;
+  }
   // Prefer the widest vector that still leaves enough threads to fill the machine.
   const long long chains = (long long)B * H;
   const long long want_threads = 148LL * 512;
@@ -296,6 +422,16 @@ static void launch_fwd(const float* gi, const float* h0, const float* W, const f
 int diag_forward(const float* gi, const float* h0, const float* W, const float* bh, float* out,
                  int T, int B, int H, Quant qi, Quant qo, cudaStream_t st) {
   const bool ok = aligned16(gi) && aligned16(h0) && aligned16(W) && aligned16(bh) && aligned16(out);
+  static const bool no_tma = getenv("B200GRU_DIAG_NO_TMA") != nullptr;       // tuning override
+  if (!no_tma && ok && H % 4 == 0 && T >= DT_STAGES && (long long)B * H >= 65536 && B <= 65535) {
+    dim3 grid(cdiv(H, DT_COLS), B);
+#define DIAG_TMA(QI, QO) diag_fwd_tma_kernel<QI, QO><<<grid, DT_THREADS, 0, st>>>(gi, h0, W, bh, out, T, B, H, qi, qo)
+    if (qi.enabled) { if (qo.enabled) DIAG_TMA(true, true); else DIAG_TMA(true, false); }
+    else            { if (qo.enabled) DIAG_TMA(false, true); else DIAG_TMA(false, false); }
+#undef DIAG_TMA
+    note_launch();
+    return check_launch("diag_fwd_tma_kernel");
+  }
   const int vec = pick_vec(B, H, ok);
   if (vec == 4) launch_fwd<4, 4>(gi, h0, W, bh, out, T, B, H, qi, qo, st);
   else if (vec == 2) launch_fwd<2, 6>(gi, h0, W, bh, out, T, B, H, qi, qo, st);

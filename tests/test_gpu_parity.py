@@ -121,6 +121,7 @@ def test_golden_vectors_through_the_cuda_path(kind, name):
 
 @pytest.mark.parametrize("kind,T,B,H,extra", [
     ("diagonal", 1, 1, 1, {}), ("diagonal", 9, 3, 2, {}), ("diagonal", 9, 5, 8, {}), ("diagonal", 7, 2, 1023, {}),
+    ("diagonal", 19, 70, 1000, {}), ("diagonal", 8, 64, 1024, {}), ("diagonal", 33, 300, 256, {}),
     ("dense", 1, 1, 1, {}), ("dense", 6, 3, 2, {}), ("dense", 6, 5, 8, {}), ("dense", 4, 3, 100, {}),
     ("dense", 3, 2, 1024, {}),
     ("monarch", 6, 3, 8, {"nblocks": 8}), ("monarch", 6, 3, 24, {"nblocks": 2}), ("monarch", 5, 9, 96, {"nblocks": 4}),
