@@ -150,7 +150,7 @@ def scan_backward(kind: str, gi, h0, W, bh, out, dout, save, h_in_quant: Quant, 
     dh0 = torch.empty_like(h0)
     dW = torch.empty_like(W)
     dbh = torch.empty_like(bh)
-    ws = _workspace(lib, shape, 1, gi.device)
+    ws = _workspace(lib, shape, 2 if save is not None else 1, gi.device)
     qi, qo = _cquant(h_in_quant), _cquant(h_out_quant)
     with torch.cuda.device(gi.device):
         stream = torch.cuda.current_stream().cuda_stream

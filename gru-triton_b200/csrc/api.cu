@@ -88,19 +88,21 @@ static bool parse_shape(const b200gru_shape* s, Dims* d) {
 
 static size_t s_bytes(const Dims& d) { return align_up((size_t)4 * d.T * d.B * d.H * sizeof(float), 256); }
 
+// backward: 0 forward, 1 backward that recomputes the gates, 2 backward that is given `save`
 static size_t workspace_bytes(const Dims& d, int backward) {
+  const size_t s_need = (backward == 2) ? 0 : s_bytes(d);
   switch (d.kind) {
     case B200GRU_DENSE:
     case B200GRU_MONARCH:
       if (!backward) return align_up((size_t)3 * d.nb * d.Hb * transposed_row_bound(d.Hb) * sizeof(float), 256);
-      return s_bytes(d) + weight_grads_scratch_bytes(d.T, d.B, d.H, d.nb, d.Hb);
+      return s_need + weight_grads_scratch_bytes(d.T, d.B, d.H, d.nb, d.Hb);
     case B200GRU_DIAGONAL:
       return backward ? diag_bwd_workspace_bytes(d.T, d.B, d.H) : 0;
     case B200GRU_BUTTERFLY: {
       if (!backward) return 0;
       const size_t w = bfly_wgrad_scratch_bytes(d.T, d.B, d.Hpad, d.nstages);
       if (w == (size_t)-1) return (size_t)-1;
-      return s_bytes(d) + w + bias_grads_scratch_bytes(d.T, d.B, d.H);
+      return s_need + w + bias_grads_scratch_bytes(d.T, d.B, d.H);
     }
   }
   return (size_t)-1;
@@ -189,12 +191,13 @@ int b200gru_scan_backward(const b200gru_shape* shape, const float* gi, const flo
   if (!gi || !h0 || !W || !bh || !out || !dout || !dgi || !dh0 || !dW || !dbh) return B200GRU_INVALID_ARGUMENT;
   if (q_in && q_in->enabled && !(q_in->scale > 0.f)) return B200GRU_INVALID_ARGUMENT;
   if (q_out && q_out->enabled && !(q_out->scale > 0.f)) return B200GRU_INVALID_ARGUMENT;
-  const size_t need = workspace_bytes(d, 1);
+  const size_t need = workspace_bytes(d, save != nullptr ? 2 : 1);
   if (need == (size_t)-1) return B200GRU_UNSUPPORTED;
   if (need > 0 && (workspace == nullptr || workspace_bytes_ < need)) return B200GRU_WORKSPACE_TOO_SMALL;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const Quant qi = make_quant(q_in), qo = make_quant(q_out);
   char* ws = static_cast<char*>(workspace);
+  const size_t s_off = (save != nullptr) ? 0 : s_bytes(d);     // the gate buffer leads the workspace when needed
 
   switch (d.kind) {
     case B200GRU_DIAGONAL:
@@ -202,7 +205,7 @@ int b200gru_scan_backward(const b200gru_shape* shape, const float* gi, const flo
     case B200GRU_DENSE:
     case B200GRU_MONARCH: {
       float* S_ws = reinterpret_cast<float*>(ws);
-      float* scratch = reinterpret_cast<float*>(ws + s_bytes(d));
+      float* scratch = reinterpret_cast<float*>(ws + s_off);
       BlockGemmArgs g;
       memset(&g, 0, sizeof(g));
       g.gi = gi; g.h0 = h0; g.out = out; g.W = W; g.bh = bh; g.dgi = dgi;
@@ -233,8 +236,8 @@ int b200gru_scan_backward(const b200gru_shape* shape, const float* gi, const flo
     case B200GRU_BUTTERFLY: {
       float* S_ws = reinterpret_cast<float*>(ws);
       const size_t wg = bfly_wgrad_scratch_bytes(d.T, d.B, d.Hpad, d.nstages);
-      float* part_w = reinterpret_cast<float*>(ws + s_bytes(d));
-      float* part_b = reinterpret_cast<float*>(ws + s_bytes(d) + wg);
+      float* part_w = reinterpret_cast<float*>(ws + s_off);
+      float* part_b = reinterpret_cast<float*>(ws + s_off + wg);
       BflyArgs a;
       int rc = fill_bfly(d, &a);
       if (rc) return rc;

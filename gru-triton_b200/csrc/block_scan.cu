@@ -173,8 +173,9 @@ __device__ __forceinline__ void fwd_load(const float* wp, int kstride, int gstri
     if (SMEM) {
       w[g] = *reinterpret_cast<const float4*>(wp + k * kstride + g * gstride);
     } else {
-      const float* p = wp + (size_t)k * kstride + g * gstride;
-      w[g] = make_float4(__ldg(p), __ldg(p + 1), __ldg(p + 2), __ldg(p + 3));
+      // rows of the transposed copy are WtR floats (a multiple of 4) and every slice starts on a
+      // multiple of 4 when Hc does, which the configuration requires for this mode
+      w[g] = __ldg(reinterpret_cast<const float4*>(wp + (size_t)k * kstride + g * gstride));
     }
   }
   load_rows<BT>(hcur + k * BT, hv);
@@ -860,6 +861,7 @@ bool choose_block_config(bool fwd, int B, int Hb, int nb, BlockScanConfig* out) 
       c.NH = (2 * ntiles <= NW) ? 2 : 1;
       c.GPT = (Hc * BT <= NT) ? 1 : 8;
       for (int ws = 1; ws >= 0; --ws) {
+        if (ws == 0 && fwd && C > 1 && Hc % 4 != 0) continue;   // streamed weights are read as float4
         size_t fl;
         if (fwd) fl = 4 + (size_t)((2 * HbP * BT + 3) & ~3) + (ws ? (size_t)Hb * c.RS : 0);
         else fl = 4 + (size_t)((2 * C * Hc * BT + 3) & ~3) + (size_t)2 * 3 * Hc4 * ((BT + 3) & ~3) + (ws ? (size_t)3 * Hc4 * Hb4 : 0);

@@ -62,8 +62,9 @@ typedef struct {
   int log2_hpad;
 } b200gru_shape;
 
-/* Bytes of caller-provided scratch needed by the forward (backward == 0) or the
- * backward (backward == 1) of `shape`.  0 is a valid answer.  Returns (size_t)-1
+/* Bytes of caller-provided scratch needed by the forward (backward == 0), by a backward that
+ * recomputes the gate activations (backward == 1), or by a backward that is handed the
+ * forward's `save` buffer (backward == 2) of `shape`.  0 is a valid answer.  Returns (size_t)-1
  * for an invalid shape.  Replaces the torch.zeros/torch.empty scratch allocations
  * of the reference wrappers (scan.py:710-717, scan_monarch.py:848-856,
  * scan_butterfly.py:429-432, 1033-1040). */
