@@ -135,11 +135,11 @@ diag_fwd_kernel(const float* __restrict__ gi, const float* __restrict__ h0,
 // only a handful of scoreboards, so waiting for an old load also waits for the youngest one.
 // Here gi is staged through shared memory instead: one elected thread issues bulk copies
 // (cp.async.bulk, the 1-D TMA path) DT_STAGES time steps ahead, completion is counted on an
-// mbarrier per stage, and the 64 threads of the CTA only ever read shared memory.  A CTA owns
+// mbarrier per stage, and the threads of the CTA only ever read shared memory.  A CTA owns
 // 256 adjacent hidden units of one batch row (3 x 1 KB per step); small CTAs keep the 148 SMs
-// evenly loaded (about seven CTAs per SM at B*H = 256 Ki).
-constexpr int DT_THREADS = 64;
-constexpr int DT_COLS = DT_THREADS * 4;
+// evenly loaded (about seven CTAs per SM at B*H = 256 Ki).  With gi off the critical path the
+// kernel is bound by instruction issue (two sigmoids, a tanh and two exact fake-quants cost
+// about 110 instructions per element-step), not by HBM.
 constexpr int DT_STAGES = 8;
 constexpr int DT_WAIT_LIMIT = 1 << 20;
 
@@ -157,11 +157,12 @@ __device__ __forceinline__ bool dt_try_wait(unsigned bar, unsigned parity) {
   return ok != 0;
 }
 
-template <bool QIN, bool QOUT>
+template <int DT_VEC, int DT_THREADS, bool QIN, bool QOUT>
 __global__ void __launch_bounds__(DT_THREADS)
 diag_fwd_tma_kernel(const float* __restrict__ gi, const float* __restrict__ h0,
                     const float* __restrict__ W, const float* __restrict__ bh,
                     float* __restrict__ out, int T, int B, int H, Quant qin, Quant qout) {
+  constexpr int DT_COLS = DT_THREADS * DT_VEC;
   __shared__ __align__(128) float stage[DT_STAGES][3][DT_COLS];
   __shared__ __align__(8) unsigned long long full[DT_STAGES];
   const int tid = threadIdx.x;
@@ -169,8 +170,8 @@ diag_fwd_tma_kernel(const float* __restrict__ gi, const float* __restrict__ h0,
   const int i0 = blockIdx.x * DT_COLS;
   const int ncols = min(DT_COLS, H - i0);                 // multiple of 4 (H % 4 == 0)
   const unsigned seg_bytes = (unsigned)ncols * sizeof(float);
-  const bool active = 4 * tid < ncols;
-  const int i = i0 + 4 * tid;
+  const bool active = DT_VEC * tid < ncols;
+  const int i = i0 + DT_VEC * tid;
 
   const size_t gi_step = (size_t)B * 3 * H;
   const size_t out_step = (size_t)B * H;
@@ -192,13 +193,13 @@ diag_fwd_tma_kernel(const float* __restrict__ gi, const float* __restrict__ h0,
     for (int t = 0; t < DT_STAGES && t < T; ++t) issue(t);
   }
 
-  float wr[4], wz[4], wn[4], br[4], bz[4], bn[4], h[4];
+  float wr[DT_VEC], wz[DT_VEC], wn[DT_VEC], br[DT_VEC], bz[DT_VEC], bn[DT_VEC], h[DT_VEC];
 #pragma unroll
-  for (int v = 0; v < 4; ++v) { wr[v] = wz[v] = wn[v] = br[v] = bz[v] = bn[v] = h[v] = 0.f; }
+  for (int v = 0; v < DT_VEC; ++v) { wr[v] = wz[v] = wn[v] = br[v] = bz[v] = bn[v] = h[v] = 0.f; }
   if (active) {
-    ld_plain<4>(W + i, wr); ld_plain<4>(W + H + i, wz); ld_plain<4>(W + 2 * H + i, wn);
-    ld_plain<4>(bh + i, br); ld_plain<4>(bh + H + i, bz); ld_plain<4>(bh + 2 * H + i, bn);
-    ld_plain<4>(h0 + (size_t)b * H + i, h);
+    ld_plain<DT_VEC>(W + i, wr); ld_plain<DT_VEC>(W + H + i, wz); ld_plain<DT_VEC>(W + 2 * H + i, wn);
+    ld_plain<DT_VEC>(bh + i, br); ld_plain<DT_VEC>(bh + H + i, bz); ld_plain<DT_VEC>(bh + 2 * H + i, bn);
+    ld_plain<DT_VEC>(h0 + (size_t)b * H + i, h);
   }
   __syncthreads();                                         // barriers initialised before anyone polls
 
@@ -214,18 +215,18 @@ diag_fwd_tma_kernel(const float* __restrict__ gi, const float* __restrict__ h0,
         if (++spin > DT_WAIT_LIMIT) { dead = true; atomicExch(&g_diag_status, 1); break; }
       }
     }
-    float gr[4], gz[4], gn[4];
+    float gr[DT_VEC], gz[DT_VEC], gn[DT_VEC];
     if (active) {
-      ld_plain<4>(&stage[s][0][4 * tid], gr);
-      ld_plain<4>(&stage[s][1][4 * tid], gz);
-      ld_plain<4>(&stage[s][2][4 * tid], gn);
+      ld_plain<DT_VEC>(&stage[s][0][DT_VEC * tid], gr);
+      ld_plain<DT_VEC>(&stage[s][1][DT_VEC * tid], gz);
+      ld_plain<DT_VEC>(&stage[s][2][DT_VEC * tid], gn);
     }
     __syncthreads();                                       // stage s has been read by everyone
     if (tid == 0 && t + DT_STAGES < T) issue(t + DT_STAGES);
     if (active) {
-      float o[4];
+      float o[DT_VEC];
 #pragma unroll
-      for (int v = 0; v < 4; ++v) {
+      for (int v = 0; v < DT_VEC; ++v) {
         const float hq = fake_quant<QIN>(h[v], qin);
         const float ghr = wr[v] * hq + br[v];
         const float ghz = wz[v] * hq + bz[v];
@@ -234,7 +235,7 @@ diag_fwd_tma_kernel(const float* __restrict__ gi, const float* __restrict__ h0,
         h[v] = fake_quant<QOUT>(g.h_raw, qout);
         o[v] = h[v];
       }
-      st_vec<4>(op + (size_t)t * out_step, o);
+      st_vec<DT_VEC>(op + (size_t)t * out_step, o);
     }
   }
 }
@@ -424,8 +425,10 @@ int diag_forward(const float* gi, const float* h0, const float* W, const float* 
   const bool ok = aligned16(gi) && aligned16(h0) && aligned16(W) && aligned16(bh) && aligned16(out);
   static const bool no_tma = getenv("B200GRU_DIAG_NO_TMA") != nullptr;       // tuning override
   if (!no_tma && ok && H % 4 == 0 && T >= DT_STAGES && (long long)B * H >= 65536 && B <= 65535) {
-    dim3 grid(cdiv(H, DT_COLS), B);
-#define DIAG_TMA(QI, QO) diag_fwd_tma_kernel<QI, QO><<<grid, DT_THREADS, 0, st>>>(gi, h0, W, bh, out, T, B, H, qi, qo)
+    // 128 threads x 2 units: the best of the (units per thread, threads) shapes measured on B200
+    constexpr int V = 2, N = 128;
+    const dim3 grid(cdiv(H, V * N), B);
+#define DIAG_TMA(QI, QO) diag_fwd_tma_kernel<V, N, QI, QO><<<grid, N, 0, st>>>(gi, h0, W, bh, out, T, B, H, qi, qo)
     if (qi.enabled) { if (qo.enabled) DIAG_TMA(true, true); else DIAG_TMA(true, false); }
     else            { if (qo.enabled) DIAG_TMA(false, true); else DIAG_TMA(false, false); }
 #undef DIAG_TMA
