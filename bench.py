@@ -325,7 +325,7 @@ def run_device(args):
         "gpu_launches_per_step": launches_per_step,
         "clocks": clocks,
         "roofline": {"kernel": {"dense": "block_fwd_kernel", "monarch": "block_fwd_kernel",
-                                "diagonal": "diag_fwd_kernel", "butterfly": "bfly_fwd_kernel"}[cfg["kind"]],
+                                "diagonal": "diag_fwd_tma_kernel", "butterfly": "bfly_fwd2_kernel"}[cfg["kind"]],
                      "bound": "hbm", "achieved": achieved, "peak": peak_gbs, "unit": "GB/s",
                      "frac": achieved / peak_gbs, "peak_source": "measured" if peaks else "fallback",
                      "traffic": None, "launch_ms": k_ms, "per_step_us": k_ms * 1e3 / wl.T,

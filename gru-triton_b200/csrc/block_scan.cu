@@ -921,8 +921,9 @@ extern "C" int b200gru_device_status(int reset) {
     cudaMemcpyToSymbol(g_scan_status, &z, sizeof(int));
   }
   const int d = diag_read_status(reset);
-  if (d < 0) return -1;
-  return (v != 0 || d != 0) ? 1 : 0;
+  const int f = bfly_read_status(reset);
+  if (d < 0 || f < 0) return -1;
+  return (v != 0 || d != 0 || f != 0) ? 1 : 0;
 }
 
 }  // namespace b200gru

@@ -19,6 +19,8 @@
 // only on-chain work is the TRANSPOSED butterfly of dgh; (3) twiddle gradients,
 // parallel over rows, accumulated per CTA in shared memory (bfly_wgrad_kernel).
 
+#include <cstdlib>
+
 #include "butterfly_scan.cuh"
 
 namespace b200gru {
@@ -438,6 +440,7 @@ int build_bfly_passes(int logn, int nblocks, BflyPass* passes, int max_passes) {
     }
     if (np >= max_passes) return -1;
     passes[np].l0 = (short)l; passes[np].nst = (short)n; passes[np].lb = (short)lo; passes[np].r = (short)(hi - lo + 1);
+    for (int s = 0; s < 4; ++s) passes[np].pb[s] = (short)(s < n ? ls_of(l + s) - lo : 0);
     ++np; l += n;
   }
   return np;
@@ -457,6 +460,9 @@ static int pick_bt(int B) {
   return bt;
 }
 
+// staged kernels: spread a small batch over as many SMs as possible (>= ~128 CTAs), up to 2 rows
+static int pick_bt2(int B) { return B >= 256 ? 2 : 1; }
+
 static size_t fwd_smem(int BT, int H, int Hpad, size_t tw_bytes) {
   return ((size_t)5 * BT * Hpad + (size_t)3 * BT * H) * sizeof(float) + tw_bytes;
 }
@@ -471,6 +477,12 @@ static int set_smem(K kernel, size_t bytes) {
 }
 
 int bfly_launch_forward(BflyArgs a, cudaStream_t st) {
+  // The staged variant is the faster one wherever it applies; B200GRU_BFLY_LEGACY (read at every
+  // call) selects the kernel below so that both keep parity coverage.
+  if (getenv("B200GRU_BFLY_LEGACY") == nullptr) {
+    const int rc2 = bfly2_launch_forward(a, pick_bt2(a.B), st);
+    if (rc2 >= 0) return rc2;
+  }
   const size_t lim = optin_smem();
   const size_t twb = (size_t)3 * a.nstages * (a.Hpad / 2) * 16;
   int BT = pick_bt(a.B);
@@ -491,6 +503,10 @@ int bfly_launch_forward(BflyArgs a, cudaStream_t st) {
 }
 
 int bfly_launch_backward(BflyArgs a, cudaStream_t st) {
+  if (getenv("B200GRU_BFLY_LEGACY") == nullptr) {
+    const int rc2 = bfly2_launch_backward(a, pick_bt2(a.B), st);
+    if (rc2 >= 0) return rc2;
+  }
   const size_t lim = optin_smem();
   const size_t twb = (size_t)3 * a.nstages * (a.Hpad / 2) * 16;
   int BT = pick_bt(a.B);

@@ -9,8 +9,10 @@ constexpr int BFLY_THREADS = 256;
 constexpr int BFLY_MAX_PASSES = 48;
 
 // A run of consecutive stages [l0, l0 + nst) whose strides touch only bits [lb, lb + r).
+// pb[s] = (log-stride of stage l0 + s) - lb, the stage's bit inside the pass.
 struct BflyPass {
   short l0, nst, lb, r;
+  short pb[4];
 };
 
 struct BflyArgs {
@@ -31,12 +33,18 @@ struct BflyArgs {
   int h0_rows;
   int npasses;
   int tw_in_smem;
+  int tw_mode;            // staged kernels: 0 twiddles read from global, 1 resident in smem, 2 streamed per pass
+  int RSZ;                // staged kernels: swizzled row stride of the running vectors
   BflyPass passes[BFLY_MAX_PASSES];
   Quant qin, qout;
 };
 
 int build_bfly_passes(int logn, int nblocks, BflyPass* passes, int max_passes);
 int bfly_launch_forward(BflyArgs a, cudaStream_t st);
+// butterfly_scan2.cu: staged variants; return -1 when they do not apply to the problem
+int bfly2_launch_forward(BflyArgs a, int want_bt, cudaStream_t st);
+int bfly2_launch_backward(BflyArgs a, int want_bt, cudaStream_t st);
+int bfly_read_status(int reset);
 int bfly_launch_backward(BflyArgs a, cudaStream_t st);
 size_t bfly_wgrad_scratch_bytes(int T, int B, int Hpad, int nstages);
 int bfly_launch_wgrad(BflyArgs a, float* partial, float* dtw, cudaStream_t st);

@@ -1,0 +1,710 @@
+// Butterfly scan, staged variant (aligned problems: H % 4 == 0, 16-byte aligned tensors).
+//
+// Same arithmetic and pass structure as butterfly_scan.cu, with the memory side rebuilt around
+// bulk (1-D TMA) copies and mbarriers so that nothing on the per-step chain waits for L2:
+//
+//   * twiddles: resident in shared memory when all of them fit; otherwise STREAMED -- the
+//     twiddle block of pass q+2 (three contiguous runs, one per gate) is copied while passes
+//     q and q+1 compute, two buffers alternating;
+//   * gi[t] (forward) and dout / gate activations / h_{t-1} (backward) arrive as row-sized bulk
+//     copies issued one step ahead;
+//   * the running vectors use a swizzled row layout, phys(i) = i + 8 * (i / 64), which makes the
+//     strided accesses of the middle passes bank-conflict free; the stride-1 pass and the gate
+//     phases move float4s.
+//
+// Every wait is a bounded poll of an mbarrier; a wait that gives up sets a device flag and the
+// kernel runs to its end (results invalid, flag visible through b200gru_device_status).
+
+#include "butterfly_scan.cuh"
+
+namespace b200gru {
+
+namespace {
+
+constexpr int NT = 384;                 // 12 warps: one radix-8 item per thread per pass at Hpad = 1024
+constexpr int WAIT_LIMIT = 1 << 20;
+
+static __device__ int g_bfly_status;
+
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(unsigned bar) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arm(unsigned bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_load(unsigned dst, const void* src, unsigned bytes, unsigned bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(unsigned bar, unsigned parity) {
+  unsigned ok;
+  asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+               "selp.u32 %0, 1, 0, p;\n\t}" : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ void mbar_wait(unsigned bar, unsigned parity, bool& dead) {
+  if (dead) return;
+  for (int i = 0; i < WAIT_LIMIT; ++i)
+    if (mbar_try_wait(bar, parity)) return;
+  dead = true;
+  atomicExch(&g_bfly_status, 1);
+}
+
+__device__ __forceinline__ int sw(int i) { return i + ((i >> 6) << 3); }
+
+template <int R, int P, int BT, bool TRANSPOSE>
+__device__ __forceinline__ void stage_regs(float (&v)[BT][1 << R], const float4 (&tw)[(1 << R) / 2]) {
+  int idx = 0;
+#pragma unroll
+  for (int e = 0; e < (1 << R); ++e) {
+    if (e & (1 << P)) continue;
+    const float4 t = tw[idx];
+#pragma unroll
+    for (int b = 0; b < BT; ++b) {
+      const float a0 = v[b][e], a1 = v[b][e | (1 << P)];
+      if (!TRANSPOSE) {
+        v[b][e] = fmaf(t.y, a1, t.x * a0);
+        v[b][e | (1 << P)] = fmaf(t.z, a0, t.w * a1);
+      } else {
+        v[b][e] = fmaf(t.z, a1, t.x * a0);
+        v[b][e | (1 << P)] = fmaf(t.y, a0, t.w * a1);
+      }
+    }
+    ++idx;
+  }
+}
+
+template <int R, int BT, bool TRANSPOSE>
+__device__ __forceinline__ void stage_dispatch(float (&v)[BT][1 << R], const float4 (&tw)[(1 << R) / 2], int p) {
+  if (R >= 3 && p == 2) stage_regs<R, (R >= 3 ? 2 : 0), BT, TRANSPOSE>(v, tw);
+  else if (R >= 2 && p == 1) stage_regs<R, (R >= 2 ? 1 : 0), BT, TRANSPOSE>(v, tw);
+  else stage_regs<R, 0, BT, TRANSPOSE>(v, tw);
+}
+
+// A float4 of twiddles from shared memory (by 32-bit shared address) or from global memory.
+template <bool TW_SMEM>
+__device__ __forceinline__ float4 tw_load(const float4* p) {
+  if (TW_SMEM) {
+    float4 v;
+    asm("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+        : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(smem_u32(p)));
+    return v;
+  }
+  return __ldg(p);
+}
+
+// One pass over the three gates on swizzled rows of stride RSZ.  Twiddle of (gate g, stage l,
+// pair) is twp[g * tw_gate + (l - tw_l0) * half + pair].
+template <int R, int BT, bool TRANSPOSE, bool TW_SMEM>
+__device__ __forceinline__ void run_pass2_r(const BflyPass pd, const float* src, int src_gate, float* dst,
+                                            int dst_gate, const float4* twp, int tw_gate, int tw_l0, int Hpad,
+                                            int RSZ, int logn) {
+  constexpr int E = 1 << R;
+  const int lb = pd.lb;
+  const int pb0 = pd.pb[0], pb1 = pd.pb[1], pb2 = pd.pb[2];
+  const int lgG = logn - R;                             // log2 of the groups per gate
+  const int G = 1 << lgG;
+  const int half = Hpad >> 1;
+  for (int item = threadIdx.x; item < 3 * G; item += NT) {
+    const int g = item >> lgG, q = item & (G - 1);
+    const int low = q & ((1 << lb) - 1), high = q >> lb;
+    const int base = (high << (lb + R)) | low;
+
+    // The idx-th pair of this group has the same twiddle index at every stage of the pass:
+    // removing the stage's own bit from the position leaves (high, idx, low).
+    const int pair0 = (high << (lb + R - 1)) | low;
+    float4 t[3][E / 2];
+    int pbit[3];
+#pragma unroll
+    for (int s = 0; s < 3; ++s) {
+      pbit[s] = 0;
+      if (s < pd.nst) {
+        const int so = TRANSPOSE ? (pd.nst - 1 - s) : s;          // stage offset inside the pass
+        pbit[s] = so == 0 ? pb0 : (so == 1 ? pb1 : pb2);
+        const float4* tl = twp + (g * tw_gate + (pd.l0 + so - tw_l0) * half + pair0);
+#pragma unroll
+        for (int idx = 0; idx < E / 2; ++idx) t[s][idx] = tw_load<TW_SMEM>(tl + (idx << lb));
+      }
+    }
+
+    float v[BT][E];
+    const float* sp = src + (size_t)g * src_gate;
+    float* dp = dst + (size_t)g * dst_gate;
+    const bool contiguous = (lb == 0);
+    const int pbase = sw(base);
+    // the swizzle is affine in the element number unless the pass straddles bit 6
+    const bool uniform = (lb + R <= 6) || (lb >= 6);
+    const int estride = (lb >= 6) ? ((1 << lb) + (8 << (lb - 6))) : (1 << lb);
+    if (contiguous) {
+#pragma unroll
+      for (int b = 0; b < BT; ++b) {
+        if constexpr (E == 8) {
+          const float4 x0 = *reinterpret_cast<const float4*>(sp + b * RSZ + pbase);
+          const float4 x1 = *reinterpret_cast<const float4*>(sp + b * RSZ + pbase + 4);
+          v[b][0] = x0.x; v[b][1] = x0.y; v[b][2] = x0.z; v[b][3] = x0.w;
+          v[b][4] = x1.x; v[b][5] = x1.y; v[b][6] = x1.z; v[b][7] = x1.w;
+        } else if constexpr (E == 4) {
+          const float4 x0 = *reinterpret_cast<const float4*>(sp + b * RSZ + pbase);
+          v[b][0] = x0.x; v[b][1] = x0.y; v[b][2] = x0.z; v[b][3] = x0.w;
+        } else {
+          const float2 x0 = *reinterpret_cast<const float2*>(sp + b * RSZ + pbase);
+          v[b][0] = x0.x; v[b][1] = x0.y;
+        }
+      }
+    } else if (uniform) {
+#pragma unroll
+      for (int b = 0; b < BT; ++b)
+#pragma unroll
+        for (int e = 0; e < E; ++e) v[b][e] = sp[b * RSZ + pbase + e * estride];
+    } else {
+#pragma unroll
+      for (int b = 0; b < BT; ++b)
+#pragma unroll
+        for (int e = 0; e < E; ++e) v[b][e] = sp[b * RSZ + sw(base + (e << lb))];
+    }
+
+#pragma unroll
+    for (int s = 0; s < 3; ++s)
+      if (s < pd.nst) stage_dispatch<R, BT, TRANSPOSE>(v, t[s], pbit[s]);
+
+    if (contiguous) {
+#pragma unroll
+      for (int b = 0; b < BT; ++b) {
+        if constexpr (E == 8) {
+          *reinterpret_cast<float4*>(dp + b * RSZ + pbase) = make_float4(v[b][0], v[b][1], v[b][2], v[b][3]);
+          *reinterpret_cast<float4*>(dp + b * RSZ + pbase + 4) = make_float4(v[b][4], v[b][5], v[b][6], v[b][7]);
+        } else if constexpr (E == 4) {
+          *reinterpret_cast<float4*>(dp + b * RSZ + pbase) = make_float4(v[b][0], v[b][1], v[b][2], v[b][3]);
+        } else {
+          *reinterpret_cast<float2*>(dp + b * RSZ + pbase) = make_float2(v[b][0], v[b][1]);
+        }
+      }
+    } else if (uniform) {
+#pragma unroll
+      for (int b = 0; b < BT; ++b)
+#pragma unroll
+        for (int e = 0; e < E; ++e) dp[b * RSZ + pbase + e * estride] = v[b][e];
+    } else {
+#pragma unroll
+      for (int b = 0; b < BT; ++b)
+#pragma unroll
+        for (int e = 0; e < E; ++e) dp[b * RSZ + sw(base + (e << lb))] = v[b][e];
+    }
+  }
+}
+
+// Single-stage pass at a stride of at least 4: a thread takes 4 adjacent pairs (float4 on both
+// sides of the stride), so the pass needs a quarter of the items.
+template <int BT, bool TRANSPOSE, bool TW_SMEM>
+__device__ __forceinline__ void run_pass2_r1w4(const BflyPass pd, const float* src, int src_gate, float* dst,
+                                               int dst_gate, const float4* twp, int tw_gate, int tw_l0, int Hpad,
+                                               int RSZ, int logn) {
+  const int lb = pd.lb;
+  const int lgG = logn - 3;                             // groups of 4 pairs per gate
+  const int G = 1 << lgG;
+  const int half = Hpad >> 1;
+  const int S = 1 << lb;
+  for (int item = threadIdx.x; item < 3 * G; item += NT) {
+    const int g = item >> lgG, q = item & (G - 1);
+    const int pair = q << 2;                            // first of 4 adjacent pairs
+    const int low = pair & (S - 1), high = pair >> lb;
+    const int i0 = (high << (lb + 1)) | low;
+    const float4* tl = twp + (g * tw_gate + (pd.l0 - tw_l0) * half + pair);
+    float4 t[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) t[j] = tw_load<TW_SMEM>(tl + j);
+    const int p0 = sw(i0), p1 = sw(i0 + S);
+    const float* sp = src + (size_t)g * src_gate;
+    float* dp = dst + (size_t)g * dst_gate;
+#pragma unroll
+    for (int b = 0; b < BT; ++b) {
+      const float4 x0 = *reinterpret_cast<const float4*>(sp + b * RSZ + p0);
+      const float4 x1 = *reinterpret_cast<const float4*>(sp + b * RSZ + p1);
+      const float a0[4] = {x0.x, x0.y, x0.z, x0.w}, a1[4] = {x1.x, x1.y, x1.z, x1.w};
+      float r0[4], r1[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (!TRANSPOSE) {
+          r0[j] = fmaf(t[j].y, a1[j], t[j].x * a0[j]);
+          r1[j] = fmaf(t[j].z, a0[j], t[j].w * a1[j]);
+        } else {
+          r0[j] = fmaf(t[j].z, a1[j], t[j].x * a0[j]);
+          r1[j] = fmaf(t[j].y, a0[j], t[j].w * a1[j]);
+        }
+      }
+      *reinterpret_cast<float4*>(dp + b * RSZ + p0) = make_float4(r0[0], r0[1], r0[2], r0[3]);
+      *reinterpret_cast<float4*>(dp + b * RSZ + p1) = make_float4(r1[0], r1[1], r1[2], r1[3]);
+    }
+  }
+}
+
+template <int BT, bool TRANSPOSE, bool TW_SMEM>
+__device__ __forceinline__ void run_pass2_s(const BflyPass pd, const float* src, int src_gate, float* dst,
+                                            int dst_gate, const float4* twp, int tw_gate, int tw_l0, int Hpad,
+                                            int RSZ, int logn) {
+  if (pd.r == 3) run_pass2_r<3, BT, TRANSPOSE, TW_SMEM>(pd, src, src_gate, dst, dst_gate, twp, tw_gate, tw_l0, Hpad, RSZ, logn);
+  else if (pd.r == 2) run_pass2_r<2, BT, TRANSPOSE, TW_SMEM>(pd, src, src_gate, dst, dst_gate, twp, tw_gate, tw_l0, Hpad, RSZ, logn);
+  else if (pd.nst == 1 && pd.lb >= 2 && logn >= 3)
+    run_pass2_r1w4<BT, TRANSPOSE, TW_SMEM>(pd, src, src_gate, dst, dst_gate, twp, tw_gate, tw_l0, Hpad, RSZ, logn);
+  else run_pass2_r<1, BT, TRANSPOSE, TW_SMEM>(pd, src, src_gate, dst, dst_gate, twp, tw_gate, tw_l0, Hpad, RSZ, logn);
+}
+
+// Twiddle supply shared by the forward and the backward kernel.
+struct TwiddleFeed {
+  const float4* gtw;      // global twiddles [3][nstages][half]
+  float4* buf;            // shared: resident copy, or two streaming buffers of 3 * 3 * half float4
+  unsigned bar0;          // streaming: mbarriers of the two buffers (bar0, bar0 + 8)
+  int mode;               // 0 global, 1 resident, 2 streamed
+  int half, nstages, npasses;
+};
+
+// thread 0: start the copies of launch-wide pass number q (pass p of its step) into buffer q & 1
+__device__ __forceinline__ void feed_issue(const TwiddleFeed& f, const BflyPass* passes, unsigned q, int p) {
+  const int l0 = passes[p].l0, nst = passes[p].nst;
+  const unsigned bytes = (unsigned)(nst * f.half) * 16u;
+  const unsigned par = q & 1u;
+  const unsigned bar = f.bar0 + 8u * par;
+  mbar_arm(bar, 3u * bytes);
+  const unsigned dst = smem_u32(f.buf) + par * (unsigned)(9 * f.half) * 16u;
+  const float4* src = f.gtw + l0 * f.half;
+#pragma unroll
+  for (int g = 0; g < 3; ++g)
+    bulk_load(dst + (unsigned)(g * 3 * f.half) * 16u, src + (size_t)g * f.nstages * f.half, bytes, bar);
+}
+
+}  // namespace
+
+// shared memory (floats unless noted), in this order:
+//   mbarriers      4 x 8 bytes: twiddle buffer 0 / 1, step operands, spare
+//   twiddles       resident: 3*nstages*half float4; streamed: 2*3*3*half float4; global: none
+//   st             [3][BT][RSZ]   running vectors of the gates (swizzled rows)
+//   hq             [BT][RSZ]      forward: fq_in(h), zero beyond H
+//   hraw / opnd    forward: [BT][H] raw h and [3][BT][H] gi;  backward: [6][BT][H] operands,
+//                  [BT][H] dh, [BT][H] direct term, [BT][H] mask
+//   bias           forward: [3][H]
+
+// TW_SMEM: twiddles come from shared memory (resident or streamed) rather than from global memory
+template <int BT, bool TW_SMEM>
+__global__ void __launch_bounds__(NT)
+bfly_fwd2_kernel(const BflyArgs a) {
+  extern __shared__ __align__(128) float smem[];
+  // pass table in shared memory: indexing the kernel parameter with a run-time pass number
+  // would move the whole argument block to local memory
+  __shared__ BflyPass spass[BFLY_MAX_PASSES];
+  if (threadIdx.x == 0) {
+#pragma unroll
+    for (int i = 0; i < BFLY_MAX_PASSES; ++i) spass[i] = a.passes[i];
+  }
+  __syncthreads();
+  const int H = a.H, Hpad = a.Hpad, half = Hpad >> 1, RSZ = a.RSZ, H4g = H >> 2;
+  const int row0 = blockIdx.x * BT;
+  const int tid = threadIdx.x;
+  const int nrows = min(BT, a.B - row0);
+
+  const unsigned bar0 = smem_u32(smem);
+  float4* twbuf = reinterpret_cast<float4*>(smem + 8);
+  const size_t tw_f4 = a.tw_mode == 1 ? (size_t)3 * a.nstages * half : (a.tw_mode == 2 ? (size_t)2 * 9 * half : 0);
+  float* st = smem + 8 + 4 * tw_f4;
+  float* hq = st + 3 * BT * RSZ;
+  float* hraw = hq + BT * RSZ;
+  float* gbuf = hraw + BT * H;
+  float* bias = gbuf + 3 * BT * H;
+  const unsigned gbar = bar0 + 16;
+
+  TwiddleFeed feed;
+  feed.gtw = reinterpret_cast<const float4*>(a.tw);
+  feed.buf = twbuf; feed.bar0 = bar0; feed.mode = a.tw_mode; feed.half = half; feed.nstages = a.nstages;
+  feed.npasses = a.npasses;
+  const unsigned total_passes = (unsigned)a.T * (unsigned)a.npasses;
+
+  const size_t gi_step = (size_t)a.B * 3 * H;
+  const size_t out_step = (size_t)a.B * H;
+  const size_t comp = (size_t)a.T * out_step;
+  const unsigned row_bytes = (unsigned)H * sizeof(float);
+
+  auto issue_gi = [&](int t) {          // thread 0
+    mbar_arm(gbar, 3u * nrows * row_bytes);
+    for (int g = 0; g < 3; ++g)
+      for (int b = 0; b < nrows; ++b)
+        bulk_load(smem_u32(gbuf + (g * BT + b) * H),
+                  a.gi + (size_t)t * gi_step + (size_t)(row0 + b) * 3 * H + (size_t)g * H, row_bytes, gbar);
+  };
+
+  if (tid == 0) {
+    mbar_init(bar0); mbar_init(bar0 + 8); mbar_init(gbar);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    if (feed.mode == 2) {
+      feed_issue(feed, spass, 0u, 0);
+      if (total_passes > 1) feed_issue(feed, spass, 1u, a.npasses > 1 ? 1 : 0);
+    }
+    issue_gi(0);
+  }
+  if (feed.mode == 1) {
+    const int n4 = 3 * a.nstages * half;
+    for (int i = tid; i < n4; i += NT) twbuf[i] = feed.gtw[i];
+  }
+  for (int i = tid; i < 3 * H; i += NT) bias[i] = a.bh[i];
+  for (int idx = tid; idx < BT * RSZ; idx += NT) hq[idx] = 0.f;
+  __syncthreads();
+  for (int idx = tid; idx < BT * H; idx += NT) {
+    const int b = idx / H, i = idx - b * H;
+    const int row = row0 + b;
+    float v = 0.f;
+    if (row < a.B)
+      v = (row < a.h0_rows) ? a.h0[(size_t)row * H + i] : a.h0_tail[(size_t)(row - a.h0_rows) * H + i];
+    hraw[idx] = v;
+    hq[b * RSZ + sw(i)] = a.qin.enabled ? fake_quant<true>(v, a.qin) : v;
+  }
+  __syncthreads();
+
+  const float4* twp = feed.mode == 0 ? feed.gtw : twbuf;
+  const int tw_gate_res = a.nstages * half;
+  bool dead = false;
+  unsigned q = 0;
+
+  PHASE_DECL;
+  for (int t = 0; t < a.T; ++t) {
+    PHASE_START();
+    for (int p = 0; p < a.npasses; ++p, ++q) {
+      const float4* tp = twp;
+      int tgate = tw_gate_res, tl0 = 0;
+      if (feed.mode == 2) {
+        mbar_wait(bar0 + 8u * (unsigned)(q & 1), (unsigned)(q >> 1) & 1u, dead);
+        PHASE_MARK(0);
+        tp = twbuf + (size_t)(q & 1) * 9 * half;
+        tgate = 3 * half;
+        tl0 = spass[p].l0;
+      }
+      // one call site: every inlined copy of the pass body costs registers across the whole kernel
+      run_pass2_s<BT, false, TW_SMEM>(spass[p], p == 0 ? hq : st, p == 0 ? 0 : BT * RSZ, st, BT * RSZ, tp, tgate, tl0,
+                                      Hpad, RSZ, a.logn);
+      PHASE_MARK(1 + (p < 4 ? p : 4));
+      __syncthreads();
+      PHASE_MARK(6);
+      if (feed.mode == 2 && tid == 0 && q + 2 < total_passes) {
+        int p2 = p + 2;
+        while (p2 >= a.npasses) p2 -= a.npasses;
+        feed_issue(feed, spass, q + 2, p2);
+      }
+      PHASE_MARK(7);
+    }
+    mbar_wait(gbar, (unsigned)t & 1u, dead);
+    PHASE_MARK(8);
+
+    for (int idx = tid; idx < nrows * H4g; idx += NT) {
+      const int b = idx / H4g, i = (idx - b * H4g) << 2;
+      const int row = row0 + b;
+      const int ps = b * RSZ + sw(i);
+      const float4 s0 = *reinterpret_cast<const float4*>(st + 0 * BT * RSZ + ps);
+      const float4 s1 = *reinterpret_cast<const float4*>(st + 1 * BT * RSZ + ps);
+      const float4 s2 = *reinterpret_cast<const float4*>(st + 2 * BT * RSZ + ps);
+      const float4 b0 = *reinterpret_cast<const float4*>(bias + i);
+      const float4 b1 = *reinterpret_cast<const float4*>(bias + H + i);
+      const float4 b2 = *reinterpret_cast<const float4*>(bias + 2 * H + i);
+      const float4 g0 = *reinterpret_cast<const float4*>(gbuf + (0 * BT + b) * H + i);
+      const float4 g1 = *reinterpret_cast<const float4*>(gbuf + (1 * BT + b) * H + i);
+      const float4 g2 = *reinterpret_cast<const float4*>(gbuf + (2 * BT + b) * H + i);
+      const float4 hp = *reinterpret_cast<const float4*>(hraw + b * H + i);
+      const float sr[4] = {s0.x + b0.x, s0.y + b0.y, s0.z + b0.z, s0.w + b0.w};
+      const float sz[4] = {s1.x + b1.x, s1.y + b1.y, s1.z + b1.z, s1.w + b1.w};
+      const float sn[4] = {s2.x + b2.x, s2.y + b2.y, s2.z + b2.z, s2.w + b2.w};
+      const float gr[4] = {g0.x, g0.y, g0.z, g0.w}, gz[4] = {g1.x, g1.y, g1.z, g1.w}, gn[4] = {g2.x, g2.y, g2.z, g2.w};
+      const float hv[4] = {hp.x, hp.y, hp.z, hp.w};
+      float hn[4], hqv[4], rr[4], zz[4], nn[4];
+#pragma unroll
+      for (int v = 0; v < 4; ++v) {
+        const GateOut go = gru_gates(gr[v], gz[v], gn[v], sr[v], sz[v], sn[v], hv[v]);
+        hn[v] = a.qout.enabled ? fake_quant<true>(go.h_raw, a.qout) : go.h_raw;
+        hqv[v] = a.qin.enabled ? fake_quant<true>(hn[v], a.qin) : hn[v];
+        rr[v] = go.r; zz[v] = go.z; nn[v] = go.n;
+      }
+      const size_t o = (size_t)t * out_step + (size_t)row * H + i;
+      if (a.out != nullptr) *reinterpret_cast<float4*>(a.out + o) = make_float4(hn[0], hn[1], hn[2], hn[3]);
+      if (a.save != nullptr) {
+        __stcs(reinterpret_cast<float4*>(a.save + o), make_float4(rr[0], rr[1], rr[2], rr[3]));
+        __stcs(reinterpret_cast<float4*>(a.save + comp + o), make_float4(zz[0], zz[1], zz[2], zz[3]));
+        __stcs(reinterpret_cast<float4*>(a.save + 2 * comp + o), make_float4(nn[0], nn[1], nn[2], nn[3]));
+        __stcs(reinterpret_cast<float4*>(a.save + 3 * comp + o), make_float4(sn[0], sn[1], sn[2], sn[3]));
+      }
+      *reinterpret_cast<float4*>(hraw + b * H + i) = make_float4(hn[0], hn[1], hn[2], hn[3]);
+      *reinterpret_cast<float4*>(hq + ps) = make_float4(hqv[0], hqv[1], hqv[2], hqv[3]);
+    }
+    PHASE_MARK(9);
+    __syncthreads();
+    PHASE_MARK(10);
+    if (tid == 0 && t + 1 < a.T) issue_gi(t + 1);
+    PHASE_MARK(11);
+  }
+}
+
+template <int BT, bool TW_SMEM>
+__global__ void __launch_bounds__(NT)
+bfly_bwd2_kernel(const BflyArgs a) {
+  extern __shared__ __align__(128) float smem[];
+  // pass table in shared memory: indexing the kernel parameter with a run-time pass number
+  // would move the whole argument block to local memory
+  __shared__ BflyPass spass[BFLY_MAX_PASSES];
+  if (threadIdx.x == 0) {
+#pragma unroll
+    for (int i = 0; i < BFLY_MAX_PASSES; ++i) spass[i] = a.passes[i];
+  }
+  __syncthreads();
+  const int H = a.H, Hpad = a.Hpad, half = Hpad >> 1, RSZ = a.RSZ, H4g = H >> 2, P4g = Hpad >> 2;
+  const int row0 = blockIdx.x * BT;
+  const int tid = threadIdx.x;
+  const int nrows = min(BT, a.B - row0);
+
+  const unsigned bar0 = smem_u32(smem);
+  float4* twbuf = reinterpret_cast<float4*>(smem + 8);
+  const size_t tw_f4 = a.tw_mode == 1 ? (size_t)3 * a.nstages * half : (a.tw_mode == 2 ? (size_t)2 * 9 * half : 0);
+  float* st = smem + 8 + 4 * tw_f4;
+  float* pbuf = st + 3 * BT * RSZ;       // [6][BT][H]: dout, r, z, n, gh_n, h_prev
+  float* dhacc = pbuf + 6 * BT * H;
+  float* dhdir = dhacc + BT * H;
+  float* mk = dhdir + BT * H;
+  const unsigned pbar = bar0 + 16;
+
+  TwiddleFeed feed;
+  feed.gtw = reinterpret_cast<const float4*>(a.tw);
+  feed.buf = twbuf; feed.bar0 = bar0; feed.mode = a.tw_mode; feed.half = half; feed.nstages = a.nstages;
+  feed.npasses = a.npasses;
+  const unsigned total_passes = (unsigned)a.T * (unsigned)a.npasses;
+
+  const size_t gi_step = (size_t)a.B * 3 * H;
+  const size_t out_step = (size_t)a.B * H;
+  const size_t comp = (size_t)a.T * out_step;
+  const unsigned row_bytes = (unsigned)H * sizeof(float);
+
+  auto issue_operands = [&](int t) {    // thread 0
+    mbar_arm(pbar, 6u * nrows * row_bytes);
+    for (int c = 0; c < 6; ++c)
+      for (int b = 0; b < nrows; ++b) {
+        const size_t o = (size_t)t * out_step + (size_t)(row0 + b) * H;
+        const float* src;
+        if (c == 0) src = a.dout + o;
+        else if (c <= 4) src = a.S + (size_t)(c - 1) * comp + o;
+        else src = (t > 0) ? (a.out_c + o - out_step) : (a.h0 + (size_t)(row0 + b) * H);
+        bulk_load(smem_u32(pbuf + (c * BT + b) * H), src, row_bytes, pbar);
+      }
+  };
+
+  if (tid == 0) {
+    mbar_init(bar0); mbar_init(bar0 + 8); mbar_init(pbar);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    if (feed.mode == 2) {
+      feed_issue(feed, spass, 0u, a.npasses - 1);
+      if (total_passes > 1) feed_issue(feed, spass, 1u, a.npasses > 1 ? a.npasses - 2 : 0);
+    }
+    issue_operands(a.T - 1);
+  }
+  if (feed.mode == 1) {
+    const int n4 = 3 * a.nstages * half;
+    for (int i = tid; i < n4; i += NT) twbuf[i] = feed.gtw[i];
+  }
+  for (int idx = tid; idx < BT * H; idx += NT) dhacc[idx] = 0.f;
+  for (int idx = tid; idx < 3 * BT * RSZ; idx += NT) st[idx] = 0.f;
+  __syncthreads();
+
+  const float4* twp = feed.mode == 0 ? feed.gtw : twbuf;
+  const int tw_gate_res = a.nstages * half;
+  bool dead = false;
+  unsigned q = 0;
+
+  for (int t = a.T - 1; t >= 0; --t) {
+    mbar_wait(pbar, (unsigned)(a.T - 1 - t) & 1u, dead);
+
+    // gate gradients -> st (and zero the padded tail, which the transposed passes dirty)
+    for (int idx = tid; idx < nrows * P4g; idx += NT) {
+      const int b = idx / P4g, i = (idx - b * P4g) << 2;
+      const int row = row0 + b;
+      const int ps = b * RSZ + sw(i);
+      float x0[4] = {0.f, 0.f, 0.f, 0.f}, x1[4] = {0.f, 0.f, 0.f, 0.f}, x2[4] = {0.f, 0.f, 0.f, 0.f};
+      if (i < H) {
+        const int e = b * H + i;
+        const float4 d4 = *reinterpret_cast<const float4*>(pbuf + 0 * BT * H + e);
+        const float4 r4 = *reinterpret_cast<const float4*>(pbuf + 1 * BT * H + e);
+        const float4 z4 = *reinterpret_cast<const float4*>(pbuf + 2 * BT * H + e);
+        const float4 n4 = *reinterpret_cast<const float4*>(pbuf + 3 * BT * H + e);
+        const float4 g4 = *reinterpret_cast<const float4*>(pbuf + 4 * BT * H + e);
+        const float4 h4 = *reinterpret_cast<const float4*>(pbuf + 5 * BT * H + e);
+        const float4 a4 = *reinterpret_cast<const float4*>(dhacc + e);
+        const float dd[4] = {d4.x, d4.y, d4.z, d4.w}, rr[4] = {r4.x, r4.y, r4.z, r4.w};
+        const float zz[4] = {z4.x, z4.y, z4.z, z4.w}, nn[4] = {n4.x, n4.y, n4.z, n4.w};
+        const float gg[4] = {g4.x, g4.y, g4.z, g4.w}, hh[4] = {h4.x, h4.y, h4.z, h4.w};
+        const float aa[4] = {a4.x, a4.y, a4.z, a4.w};
+        float dir[4], msk[4], dgn[4];
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          float dh = dd[v] + aa[v];
+          if (a.qout.enabled) {
+            const float h_raw = (1.0f - zz[v]) * nn[v] + zz[v] * hh[v];
+            dh = dh * ste_mask<true>(h_raw, a.qout);
+          }
+          const GateGrad q4 = gru_gate_grads(dh, rr[v], zz[v], nn[v], gg[v], hh[v]);
+          dir[v] = q4.dh_direct;
+          msk[v] = a.qin.enabled ? ste_mask<true>(hh[v], a.qin) : 1.0f;
+          x0[v] = q4.dgr; x1[v] = q4.dgz; x2[v] = q4.dghn; dgn[v] = q4.dgn;
+        }
+        *reinterpret_cast<float4*>(dhdir + e) = make_float4(dir[0], dir[1], dir[2], dir[3]);
+        *reinterpret_cast<float4*>(mk + e) = make_float4(msk[0], msk[1], msk[2], msk[3]);
+        float* d = a.dgi + (size_t)t * gi_step + (size_t)row * 3 * H + i;
+        __stcs(reinterpret_cast<float4*>(d), make_float4(x0[0], x0[1], x0[2], x0[3]));
+        __stcs(reinterpret_cast<float4*>(d + H), make_float4(x1[0], x1[1], x1[2], x1[3]));
+        __stcs(reinterpret_cast<float4*>(d + 2 * H), make_float4(dgn[0], dgn[1], dgn[2], dgn[3]));
+      }
+      *reinterpret_cast<float4*>(st + 0 * BT * RSZ + ps) = make_float4(x0[0], x0[1], x0[2], x0[3]);
+      *reinterpret_cast<float4*>(st + 1 * BT * RSZ + ps) = make_float4(x1[0], x1[1], x1[2], x1[3]);
+      *reinterpret_cast<float4*>(st + 2 * BT * RSZ + ps) = make_float4(x2[0], x2[1], x2[2], x2[3]);
+    }
+    __syncthreads();
+    if (tid == 0 && t > 0) issue_operands(t - 1);
+
+    for (int p = a.npasses - 1; p >= 0; --p, ++q) {
+      const float4* tp = twp;
+      int tgate = tw_gate_res, tl0 = 0;
+      if (feed.mode == 2) {
+        mbar_wait(bar0 + 8u * (unsigned)(q & 1), (unsigned)(q >> 1) & 1u, dead);
+        tp = twbuf + (size_t)(q & 1) * 9 * half;
+        tgate = 3 * half;
+        tl0 = spass[p].l0;
+      }
+      run_pass2_s<BT, true, TW_SMEM>(spass[p], st, BT * RSZ, st, BT * RSZ, tp, tgate, tl0, Hpad, RSZ, a.logn);
+      __syncthreads();
+      if (feed.mode == 2 && tid == 0 && q + 2 < total_passes) {
+        int p2 = p - 2;
+        while (p2 < 0) p2 += a.npasses;
+        feed_issue(feed, spass, q + 2, p2);
+      }
+    }
+
+    for (int idx = tid; idx < nrows * H4g; idx += NT) {
+      const int b = idx / H4g, i = (idx - b * H4g) << 2;
+      const int ps = b * RSZ + sw(i);
+      const int e = b * H + i;
+      const float4 s0 = *reinterpret_cast<const float4*>(st + 0 * BT * RSZ + ps);
+      const float4 s1 = *reinterpret_cast<const float4*>(st + 1 * BT * RSZ + ps);
+      const float4 s2 = *reinterpret_cast<const float4*>(st + 2 * BT * RSZ + ps);
+      const float4 dr = *reinterpret_cast<const float4*>(dhdir + e);
+      const float4 m4 = *reinterpret_cast<const float4*>(mk + e);
+      float4 r;
+      r.x = dr.x + (s0.x + s1.x + s2.x) * m4.x;
+      r.y = dr.y + (s0.y + s1.y + s2.y) * m4.y;
+      r.z = dr.z + (s0.z + s1.z + s2.z) * m4.z;
+      r.w = dr.w + (s0.w + s1.w + s2.w) * m4.w;
+      *reinterpret_cast<float4*>(dhacc + e) = r;
+    }
+    __syncthreads();
+  }
+
+  for (int idx = tid; idx < nrows * H4g; idx += NT) {
+    const int b = idx / H4g, i = (idx - b * H4g) << 2;
+    *reinterpret_cast<float4*>(a.dh0 + (size_t)(row0 + b) * H + i) = *reinterpret_cast<const float4*>(dhacc + b * H + i);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------
+
+static size_t optin_smem2() {
+  int dev = 0, v = 0;
+  cudaGetDevice(&dev);
+  if (cudaDeviceGetAttribute(&v, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) != cudaSuccess) return 48 * 1024;
+  return (size_t)v;
+}
+
+static int rsz_of(int Hpad) { return (Hpad + (Hpad >> 3) + 3) & ~3; }
+
+static size_t smem2(bool fwd, int BT, int H, int Hpad, int nstages, int mode) {
+  const size_t half = Hpad / 2;
+  const size_t tw = mode == 1 ? (size_t)3 * nstages * half * 16 : (mode == 2 ? (size_t)2 * 9 * half * 16 : 0);
+  const size_t RSZ = rsz_of(Hpad);
+  size_t fl;
+  if (fwd) fl = (size_t)4 * BT * RSZ + (size_t)4 * BT * H + (size_t)3 * H;
+  else fl = (size_t)3 * BT * RSZ + (size_t)9 * BT * H;
+  return 32 + tw + fl * sizeof(float);
+}
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// Chooses BT and the twiddle mode; false if this variant does not apply.
+static bool plan2(bool fwd, const BflyArgs& a, int want_bt, int* BT, int* mode, size_t* smem) {
+  if (a.H % 4 != 0 || a.Hpad < 4) return false;
+  const size_t lim = optin_smem2();
+  for (int bt = want_bt; bt >= 1; bt >>= 1) {
+    const int modes[3] = {1, 2, 0};
+    for (int m = 0; m < 3; ++m) {
+      const size_t s = smem2(fwd, bt, a.H, a.Hpad, a.nstages, modes[m]);
+      if (s <= lim) { *BT = bt; *mode = modes[m]; *smem = s; return true; }
+    }
+  }
+  return false;
+}
+
+template <typename K>
+static int set_smem2(K kernel, size_t bytes) {
+  return cudaFuncSetAttribute((const void*)kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes) ==
+                 cudaSuccess ? 0 : B200GRU_UNSUPPORTED;
+}
+
+// returns -1 if the staged variant does not apply (caller falls back), else a status
+int bfly2_launch_forward(BflyArgs a, int want_bt, cudaStream_t st) {
+  if (!(aligned16(a.gi) && aligned16(a.h0) && aligned16(a.tw) && aligned16(a.out) && aligned16(a.save) &&
+        aligned16(a.h0_tail) && aligned16(a.bh))) return -1;
+  int BT, mode; size_t smem;
+  if (!plan2(true, a, want_bt, &BT, &mode, &smem)) return -1;
+  a.tw_mode = mode; a.RSZ = rsz_of(a.Hpad);
+  const unsigned grid = (unsigned)cdiv(a.B, BT);
+  int rc = 0;
+  switch (BT) {
+    case 1:
+      if (mode) { rc = set_smem2(bfly_fwd2_kernel<1, true>, smem); if (!rc) bfly_fwd2_kernel<1, true><<<grid, NT, smem, st>>>(a); }
+      else { rc = set_smem2(bfly_fwd2_kernel<1, false>, smem); if (!rc) bfly_fwd2_kernel<1, false><<<grid, NT, smem, st>>>(a); }
+      break;
+    default:
+      if (mode) { rc = set_smem2(bfly_fwd2_kernel<2, true>, smem); if (!rc) bfly_fwd2_kernel<2, true><<<grid, NT, smem, st>>>(a); }
+      else { rc = set_smem2(bfly_fwd2_kernel<2, false>, smem); if (!rc) bfly_fwd2_kernel<2, false><<<grid, NT, smem, st>>>(a); }
+      break;
+  }
+  if (rc) return rc;
+  note_launch();
+  return check_launch("bfly_fwd2_kernel");
+}
+
+int bfly2_launch_backward(BflyArgs a, int want_bt, cudaStream_t st) {
+  if (!(aligned16(a.gi) && aligned16(a.h0) && aligned16(a.tw) && aligned16(a.out_c) && aligned16(a.S) &&
+        aligned16(a.dout) && aligned16(a.dgi) && aligned16(a.dh0))) return -1;
+  int BT, mode; size_t smem;
+  if (!plan2(false, a, want_bt, &BT, &mode, &smem)) return -1;
+  a.tw_mode = mode; a.RSZ = rsz_of(a.Hpad);
+  const unsigned grid = (unsigned)cdiv(a.B, BT);
+  int rc = 0;
+  switch (BT) {
+    case 1:
+      if (mode) { rc = set_smem2(bfly_bwd2_kernel<1, true>, smem); if (!rc) bfly_bwd2_kernel<1, true><<<grid, NT, smem, st>>>(a); }
+      else { rc = set_smem2(bfly_bwd2_kernel<1, false>, smem); if (!rc) bfly_bwd2_kernel<1, false><<<grid, NT, smem, st>>>(a); }
+      break;
+    default:
+      if (mode) { rc = set_smem2(bfly_bwd2_kernel<2, true>, smem); if (!rc) bfly_bwd2_kernel<2, true><<<grid, NT, smem, st>>>(a); }
+      else { rc = set_smem2(bfly_bwd2_kernel<2, false>, smem); if (!rc) bfly_bwd2_kernel<2, false><<<grid, NT, smem, st>>>(a); }
+      break;
+  }
+  if (rc) return rc;
+  note_launch();
+  return check_launch("bfly_bwd2_kernel");
+}
+
+int bfly_read_status(int reset) {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_bfly_status, sizeof(int)) != cudaSuccess) return -1;
+  if (reset && v != 0) {
+    const int z = 0;
+    cudaMemcpyToSymbol(g_bfly_status, &z, sizeof(int));
+  }
+  return v;
+}
+
+}  // namespace b200gru
+
+B200GRU_DEFINE_PHASE_READER(b200gru_debug_phase_cycles_bfly2)

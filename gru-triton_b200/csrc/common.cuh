@@ -160,6 +160,7 @@ __host__ __device__ inline int cdiv(int a, int b) { return (a + b - 1) / b; }
 
 // Health flag of the diagonal kernels' bounded waits (diag_scan.cu); -1 on CUDA error.
 int diag_read_status(int reset);
+int bfly_read_status(int reset);     // same for the staged butterfly kernels (butterfly_scan2.cu)
 
 // Launch bookkeeping shared by all translation units (defined in api.cu).
 void note_launch(int n = 1);

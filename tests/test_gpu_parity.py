@@ -103,6 +103,24 @@ def test_scan_parity(kind, T, B, H, quant):
     check_backward(kind, grads, gi, h0, W, bh, out, dout, quant)
 
 
+@pytest.mark.parametrize("quant", [None, Q8], ids=["fp32", "q8"])
+@pytest.mark.parametrize("T,B,H,extra", [(8, 4, 32, {}), (16, 32, 512, {}), (5, 3, 48, {"butterfly_nblocks": 2}),
+                                         (3, 2, 1024, {})])
+def test_butterfly_alternate_kernels(monkeypatch, T, B, H, extra, quant):
+    """The library keeps two butterfly kernels per direction (staged twiddles, the default, and the
+    older register/global-twiddle one for unaligned problems); the variable, read at every call,
+    selects the older pair so that it keeps parity coverage on aligned shapes too."""
+    monkeypatch.setenv("B200GRU_BFLY_LEGACY", "1")
+    fwd, bwd, _ = _mods()["butterfly"]
+    gi, h0, W, bh, dout = orc.make_problem("butterfly", T, B, H, seed=7 + T + H, **extra)
+    kw = dict(h_in_quant=quant[0], h_out_quant=quant[1]) if quant else {}
+    d = _cuda(gi, h0, W, bh, dout)
+    out = fwd(*d[:4], **kw)
+    check_forward("butterfly", out, gi, h0, W, bh, quant)
+    grads = bwd(*d[:4], out, d[4], **kw)
+    check_backward("butterfly", grads, gi, h0, W, bh, out, dout, quant)
+
+
 @pytest.mark.parametrize("kind,name", SCAN_GOLDEN_FLAT)
 def test_golden_vectors_through_the_cuda_path(kind, name):
     g = load_golden(name)
