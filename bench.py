@@ -250,6 +250,8 @@ def run_device(args):
 
     from gru_triton_b200 import _lib
     cfg = CONFIGS[args.config]
+    if args.T or args.B:
+        cfg = CONFIGS[args.config] = dict(cfg, T=args.T or cfg["T"], B=args.B or cfg["B"])
     wl = DeviceWorkload(args.config, cfg, rank, world, dev)
     flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
 
@@ -317,7 +319,9 @@ def run_device(args):
         "config": {"workload": f"{args.config}: {cfg['desc']}", "T": wl.T, "B_per_gpu": wl.B, "H": wl.H,
                    "hidden_kind": cfg["kind"], "int8_hidden": bool(cfg["quant"]), "weight_bits": cfg["wbits"],
                    "train_step": bool(cfg["train"]), "parallelism": f"batch-shard x{world}" if world > 1 else "1 GPU",
-                   "l2": "256 MiB buffer written between timed steps (outside the timed events)"},
+                   "l2": "256 MiB buffer written between timed steps (outside the timed events)",
+                   **({"override": "T/B changed on the command line: a profiling case, not a result"}
+                      if (args.T or args.B) else {})},
         "e2e": {"value": units / (e2e_ms * 1e-3), "unit": "seq-steps/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": wl.x_host.numel() * 4 + wl.h0_host.numel() * 4,
                 "d2h_bytes_per_step": 4},
@@ -440,6 +444,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--config", default="c1", choices=sorted(CONFIGS))
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--T", type=int, default=0, help="override the sequence length (profiling a smaller case; "
+                    "the line then carries config.override and is not a benchmark result)")
+    ap.add_argument("--B", type=int, default=0, help="override the batch, as --T")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-kinds", dest="kinds", action="store_false")
     args = ap.parse_args()

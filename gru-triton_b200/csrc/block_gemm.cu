@@ -147,120 +147,164 @@ int launch_recompute_gates(const BlockGemmArgs& a, cudaStream_t st) {
 }
 
 // ---------------------------------------------------------------------------
-// weight_grads
+// weight gradients: for each block n, C[m][k] = sum_tb A[tb][m] * Bm[tb][k] with
+//   m = g*Hb + o  (3*Hb rows),  A[tb][m] = dgh[tb][g][n*Hb + o],  Bm[tb][k] = fq_in(h_prev)[tb][n*Hb + k].
+// Both operands are contiguous along the output dimensions, so this is an outer-product SGEMM:
+// CTA tile (16*TM) x (16*TN), 16 x 16 threads, each thread TM x TN accumulators held as packed
+// FP32 pairs; per tb a thread reads TM/4 + TN/4 float4 from shared memory for TM*TN/2 packed FMAs.
+// The next 16 rows are fetched into registers (r-scaling of the n gate and the input fake-quant
+// applied on the way) while the current 16 are consumed; one barrier per 16 rows.
+// Rows are split over blockIdx.y into partial buffers that a second kernel sums in a fixed order.
 // ---------------------------------------------------------------------------
-constexpr int WG_O = 64;       // output units per CTA (x 3 gates)
-constexpr int WG_K = 64;       // input units per CTA (two per lane)
-constexpr int WG_R = 16;       // rows (t,b) per shared-memory chunk
+constexpr int WG_BK = 16;      // rows (t,b) per shared-memory stage
 
-// CTA tile: dW[g, 64 o, 64 k] for one row range.  Warp w owns 8 output units, lane l owns
-// input units 2l, 2l+1: 48 accumulators per thread, 7 shared loads per 48 FMAs.  The next
-// chunk's operands are fetched into registers (fake-quant / r-scaling applied) while the
-// current chunk is consumed from shared memory.
-__global__ void __launch_bounds__(256)
-weight_grads_kernel(const BlockGemmArgs a, float* __restrict__ dst, int rows_per_split) {
-  __shared__ __align__(16) float Ds[WG_R][3 * WG_O];     // dgh[row][g*64 + o]
-  __shared__ __align__(16) float Hs[WG_R][WG_K];         // fq_in(h_prev)[row][k]
+template <int TM, int TN, bool VEC>
+__global__ void __launch_bounds__(256, 2)
+weight_grads_kernel(const BlockGemmArgs a, float* __restrict__ dst, int rows_per_split, int ntm, int ntn) {
+  constexpr int BM = 16 * TM, BN = 16 * TN;
+  constexpr int NA = TM / 4, NB = TN / 4;                 // float4 groups per thread per stage
+  __shared__ __align__(16) float As[2][WG_BK][BM];
+  __shared__ __align__(16) float Bs[2][WG_BK][BN];
   const int Hb = a.Hb, H = a.H, B = a.B;
   const int TB = a.T * B;
-  const int nkt = cdiv(Hb, WG_K), not_ = cdiv(Hb, WG_O);
+  const int M = 3 * Hb;
   int bx = blockIdx.x;
-  const int kt = bx % nkt; bx /= nkt;
-  const int ot = bx % not_;
-  const int n = bx / not_;
-  const int split = blockIdx.y;
-  const int r_begin = split * rows_per_split;
+  const int nt = bx % ntn; bx /= ntn;
+  const int mt = bx % ntm;
+  const int n = bx / ntm;
+  const int m0 = mt * BM, k0 = nt * BN;
+  const int r_begin = blockIdx.y * rows_per_split;
   const int r_end = min(TB, r_begin + rows_per_split);
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
 
-  constexpr int ND = WG_R * 3 * WG_O / 256;               // 12 dgh values per thread per chunk
-  constexpr int NH_ = WG_R * WG_K / 256;                  // 4 h values per thread per chunk
-  float dreg[ND], hreg[NH_];
+  float4 areg[NA], breg[NB];
 
   auto fetch = [&](int r0) {
 #pragma unroll
-    for (int m = 0; m < ND; ++m) {
-      const int idx = tid + m * 256;
-      const int r = idx / (3 * WG_O), go = idx - r * (3 * WG_O);
-      const int g = go / WG_O, o = go - g * WG_O;
-      const int tb = r0 + r, uo = ot * WG_O + o;
-      float v = 0.f;
-      if (tb < r_end && uo < Hb) {
-        const int u = n * Hb + uo;
-        v = __ldg(a.dgi + (size_t)tb * 3 * H + (size_t)g * H + u);
-        if (g == 2) v = v * __ldg(a.S + (size_t)tb * H + u);         // dgh_n = dgi_n * r
-      }
-      dreg[m] = v;
-    }
+    for (int j = 0; j < NA; ++j) {
+      const int idx = tid + j * 256;
+      const int r = idx / (BM / 4), c = (idx - r * (BM / 4)) * 4;
+      const int tb = r0 + r, m = m0 + c;
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (tb < r_end) {
+        if (VEC) {
+          if (m < M) {                                   // Hb % 4 == 0: the four share gate and validity
+            const int g = m / Hb, u = n * Hb + (m - g * Hb);
+            v = __ldg(reinterpret_cast<const float4*>(a.dgi + (size_t)tb * 3 * H + (size_t)g * H + u));
+            if (g == 2) {                                // dgh_n = dgi_n * r
+              const float4 rr = __ldg(reinterpret_cast<const float4*>(a.S + (size_t)tb * H + u));
+              v.x = v.x * rr.x; v.y = v.y * rr.y; v.z = v.z * rr.z; v.w = v.w * rr.w;
+            }
+          }
+        } else {
+          float e[4];
 #pragma unroll
-    for (int m = 0; m < NH_; ++m) {
-      const int idx = tid + m * 256;
-      const int r = idx / WG_K, k = idx - r * WG_K;
-      const int tb = r0 + r, uk = kt * WG_K + k;
-      float v = 0.f;
-      if (tb < r_end && uk < Hb) {
-        v = h_prev_at(a.h0, a.out, tb, B, H, n * Hb + uk);
-        if (a.qin.enabled) v = fake_quant<true>(v, a.qin);
-      }
-      hreg[m] = v;
-    }
-  };
-  auto stash = [&]() {
-#pragma unroll
-    for (int m = 0; m < ND; ++m) (&Ds[0][0])[tid + m * 256] = dreg[m];
-#pragma unroll
-    for (int m = 0; m < NH_; ++m) (&Hs[0][0])[tid + m * 256] = hreg[m];
-  };
-
-  float2 acc[3][2][4];                                  // [gate][k of the pair][unit pair]: packed FP32 FMA
-#pragma unroll
-  for (int g = 0; g < 3; ++g)
-#pragma unroll
-    for (int kk = 0; kk < 2; ++kk)
-#pragma unroll
-      for (int i = 0; i < 4; ++i) acc[g][kk][i] = make_float2(0.f, 0.f);
-
-  fetch(r_begin);
-  for (int r0 = r_begin; r0 < r_end; r0 += WG_R) {
-    stash();
-    __syncthreads();
-    if (r0 + WG_R < r_end) fetch(r0 + WG_R);
-#pragma unroll 4
-    for (int r = 0; r < WG_R; ++r) {
-      const float2 h = *reinterpret_cast<const float2*>(&Hs[r][2 * lane]);
-      const float2 h0 = make_float2(h.x, h.x), h1 = make_float2(h.y, h.y);
-#pragma unroll
-      for (int g = 0; g < 3; ++g) {
-        const float4 d0 = *reinterpret_cast<const float4*>(&Ds[r][g * WG_O + warp * 8]);
-        const float4 d1 = *reinterpret_cast<const float4*>(&Ds[r][g * WG_O + warp * 8 + 4]);
-        const float2 d[4] = {make_float2(d0.x, d0.y), make_float2(d0.z, d0.w), make_float2(d1.x, d1.y),
-                             make_float2(d1.z, d1.w)};
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          acc[g][0][i] = __ffma2_rn(d[i], h0, acc[g][0][i]);
-          acc[g][1][i] = __ffma2_rn(d[i], h1, acc[g][1][i]);
+          for (int q = 0; q < 4; ++q) {
+            e[q] = 0.f;
+            const int mq = m + q;
+            if (mq < M) {
+              const int g = mq / Hb, u = n * Hb + (mq - g * Hb);
+              e[q] = __ldg(a.dgi + (size_t)tb * 3 * H + (size_t)g * H + u);
+              if (g == 2) e[q] = e[q] * __ldg(a.S + (size_t)tb * H + u);
+            }
+          }
+          v = make_float4(e[0], e[1], e[2], e[3]);
         }
       }
+      areg[j] = v;
     }
-    __syncthreads();
-  }
+#pragma unroll
+    for (int j = 0; j < NB; ++j) {
+      const int idx = tid + j * 256;
+      const int r = idx / (BN / 4), c = (idx - r * (BN / 4)) * 4;
+      const int tb = r0 + r, k = k0 + c;
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (tb < r_end) {
+        const float* hp = (tb < B) ? a.h0 + (size_t)tb * H : a.out + (size_t)(tb - B) * H;   // h_{t-1}
+        hp += n * Hb;
+        if (VEC) {
+          if (k < Hb) v = __ldg(reinterpret_cast<const float4*>(hp + k));
+        } else {
+          if (k < Hb) v.x = __ldg(hp + k);
+          if (k + 1 < Hb) v.y = __ldg(hp + k + 1);
+          if (k + 2 < Hb) v.z = __ldg(hp + k + 2);
+          if (k + 3 < Hb) v.w = __ldg(hp + k + 3);
+        }
+        if (a.qin.enabled) {
+          v.x = fake_quant<true>(v.x, a.qin); v.y = fake_quant<true>(v.y, a.qin);
+          v.z = fake_quant<true>(v.z, a.qin); v.w = fake_quant<true>(v.w, a.qin);
+        }
+      }
+      breg[j] = v;
+    }
+  };
+  auto stash = [&](int buf) {
+#pragma unroll
+    for (int j = 0; j < NA; ++j) reinterpret_cast<float4*>(&As[buf][0][0])[tid + j * 256] = areg[j];
+#pragma unroll
+    for (int j = 0; j < NB; ++j) reinterpret_cast<float4*>(&Bs[buf][0][0])[tid + j * 256] = breg[j];
+  };
 
-  const int k = kt * WG_K + 2 * lane;
-  if (k >= Hb) return;
-  const size_t dw_elems = (size_t)3 * a.nb * Hb * Hb;      // dense: 3*H*H as well
-  float* base = dst + (size_t)split * dw_elems + (size_t)n * a.w_block_stride;
+  float2 acc[TM][TN / 2];
 #pragma unroll
-  for (int g = 0; g < 3; ++g)
+  for (int i = 0; i < TM; ++i)
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int o = ot * WG_O + warp * 8 + i;
-      if (o < Hb) {
-        float* p = base + (size_t)g * a.w_gate_stride + (size_t)o * Hb + k;
-        const float2 v0 = acc[g][0][i >> 1], v1 = acc[g][1][i >> 1];
-        p[0] = (i & 1) ? v0.y : v0.x;
-        if (k + 1 < Hb) p[1] = (i & 1) ? v1.y : v1.x;
+    for (int j = 0; j < TN / 2; ++j) acc[i][j] = make_float2(0.f, 0.f);
+
+  fetch(r_begin);
+  stash(0);
+  __syncthreads();
+  int buf = 0;
+  for (int r0 = r_begin; r0 < r_end; r0 += WG_BK) {
+    const bool more = r0 + WG_BK < r_end;
+    if (more) fetch(r0 + WG_BK);
+#pragma unroll 4
+    for (int kk = 0; kk < WG_BK; ++kk) {
+      float av[TM], bv[TN];
+#pragma unroll
+      for (int j = 0; j < NA; ++j) {
+        const float4 t = *reinterpret_cast<const float4*>(&As[buf][kk][j * 64 + ty * 4]);
+        av[4 * j] = t.x; av[4 * j + 1] = t.y; av[4 * j + 2] = t.z; av[4 * j + 3] = t.w;
+      }
+#pragma unroll
+      for (int j = 0; j < NB; ++j) {
+        const float4 t = *reinterpret_cast<const float4*>(&Bs[buf][kk][j * 64 + tx * 4]);
+        bv[4 * j] = t.x; bv[4 * j + 1] = t.y; bv[4 * j + 2] = t.z; bv[4 * j + 3] = t.w;
+      }
+#pragma unroll
+      for (int i = 0; i < TM; ++i) {
+        const float2 aa = make_float2(av[i], av[i]);
+#pragma unroll
+        for (int j = 0; j < TN / 2; ++j)
+          acc[i][j] = __ffma2_rn(aa, make_float2(bv[2 * j], bv[2 * j + 1]), acc[i][j]);
       }
     }
+    if (more) stash(buf ^ 1);
+    __syncthreads();
+    buf ^= 1;
+  }
+
+  float* base = dst + (size_t)blockIdx.y * ((size_t)3 * a.nb * Hb * Hb) + (size_t)n * a.w_block_stride;
+#pragma unroll
+  for (int i = 0; i < TM; ++i) {
+    const int m = m0 + (i >> 2) * 64 + ty * 4 + (i & 3);
+    if (m >= M) continue;
+    const int g = m / Hb, o = m - g * Hb;
+    float* row = base + (size_t)g * a.w_gate_stride + (size_t)o * Hb;
+#pragma unroll
+    for (int j = 0; j < NB; ++j) {
+      const int k = k0 + j * 64 + tx * 4;
+      const float2 v0 = acc[i][2 * j], v1 = acc[i][2 * j + 1];
+      if (VEC) {
+        if (k < Hb) *reinterpret_cast<float4*>(row + k) = make_float4(v0.x, v0.y, v1.x, v1.y);
+      } else {
+        if (k < Hb) row[k] = v0.x;
+        if (k + 1 < Hb) row[k + 1] = v0.y;
+        if (k + 2 < Hb) row[k + 2] = v1.x;
+        if (k + 3 < Hb) row[k + 3] = v1.y;
+      }
+    }
+  }
 }
 
 // dbh: column sums of dgh over a range of rows; partial[split][3H]
@@ -291,17 +335,27 @@ bias_grads_kernel(const float* __restrict__ dgi, const float* __restrict__ S, fl
   }
 }
 
-static void wg_splits(int T, int B, int nb, int Hb, int* nsplit, int* rows_per_split) {
+// Tile shape and row split of the weight-gradient GEMM: big tiles when a block is at least 128
+// wide, and enough row ranges for about two CTAs per SM.
+struct WgPlan { int tm, tn, ntm, ntn, nsplit, rows_per_split; };
+
+static WgPlan wg_plan(int T, int B, int nb, int Hb) {
+  WgPlan p;
   const int TB = T * B;
-  const long long tiles = (long long)nb * cdiv(Hb, WG_O) * cdiv(Hb, WG_K);
-  long long s = (2 * 148 + tiles - 1) / tiles;
-  const long long max_by_rows = (TB + 8 * WG_R - 1) / (8 * WG_R);
+  p.tm = (3 * Hb >= 128) ? 8 : 4;
+  p.tn = (Hb >= 128) ? 8 : 4;
+  p.ntm = cdiv(3 * Hb, 16 * p.tm);
+  p.ntn = cdiv(Hb, 16 * p.tn);
+  const long long tiles = (long long)nb * p.ntm * p.ntn;
+  long long s = (2 * 148) / tiles;
+  const long long max_by_rows = cdiv(TB, 8 * WG_BK);
   if (s > max_by_rows) s = max_by_rows;
   if (s > 32) s = 32;
   if (s < 1) s = 1;
-  int rps = cdiv(cdiv(TB, (int)s), WG_R) * WG_R;
-  *nsplit = cdiv(TB, rps);
-  *rows_per_split = rps;
+  const int rps = cdiv(cdiv(TB, (int)s), WG_BK) * WG_BK;
+  p.nsplit = cdiv(TB, rps);
+  p.rows_per_split = rps;
+  return p;
 }
 
 static void bg_splits(int T, int B, int* nsplit, int* rows_per_split) {
@@ -334,8 +388,8 @@ int launch_bias_grads(const float* dgi, const float* S, float* partial, float* d
 }
 
 size_t weight_grads_scratch_bytes(int T, int B, int H, int nb, int Hb) {
-  int ns, rps, nsb, rpsb;
-  wg_splits(T, B, nb, Hb, &ns, &rps);
+  int nsb, rpsb;
+  const int ns = wg_plan(T, B, nb, Hb).nsplit;
   bg_splits(T, B, &nsb, &rpsb);
   size_t f = 0;
   if (ns > 1) f += (size_t)ns * 3 * nb * Hb * Hb;
@@ -344,15 +398,28 @@ size_t weight_grads_scratch_bytes(int T, int B, int H, int nb, int Hb) {
 }
 
 int launch_weight_grads(const BlockGemmArgs& a, cudaStream_t st) {
-  int ns, rps, nsb, rpsb;
-  wg_splits(a.T, a.B, a.nb, a.Hb, &ns, &rps);
+  int nsb, rpsb;
+  const WgPlan p = wg_plan(a.T, a.B, a.nb, a.Hb);
+  const int ns = p.nsplit;
   bg_splits(a.T, a.B, &nsb, &rpsb);
   const size_t dw_elems = (size_t)3 * a.nb * a.Hb * a.Hb;
   float* part_w = a.partial;
   float* part_b = a.partial + (ns > 1 ? (size_t)ns * dw_elems : 0);
+  float* dst = ns > 1 ? part_w : a.dW;
 
-  dim3 grid(cdiv(a.Hb, WG_K) * cdiv(a.Hb, WG_O) * a.nb, ns);
-  weight_grads_kernel<<<grid, 256, 0, st>>>(a, ns > 1 ? part_w : a.dW, rps);
+  auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15u) == 0; };
+  const bool vec = a.Hb % 4 == 0 && a.H % 4 == 0 && a.w_gate_stride % 4 == 0 && a.w_block_stride % 4 == 0 &&
+                   al16(a.dgi) && al16(a.S) && al16(a.h0) && al16(a.out) && al16(dst);
+  dim3 grid(p.ntm * p.ntn * a.nb, ns);
+#define B200GRU_WG(TM_, TN_)                                                                              \
+  do {                                                                                                    \
+    if (vec) weight_grads_kernel<TM_, TN_, true><<<grid, 256, 0, st>>>(a, dst, p.rows_per_split, p.ntm, p.ntn);  \
+    else weight_grads_kernel<TM_, TN_, false><<<grid, 256, 0, st>>>(a, dst, p.rows_per_split, p.ntm, p.ntn);     \
+  } while (0)
+  if (p.tm == 8 && p.tn == 8) B200GRU_WG(8, 8);
+  else if (p.tm == 8) B200GRU_WG(8, 4);
+  else B200GRU_WG(4, 4);
+#undef B200GRU_WG
   note_launch();
   int rc = check_launch("weight_grads_kernel");
   if (rc) return rc;
