@@ -46,6 +46,16 @@ CONFIGS = {
 }
 
 
+# DRAM traffic (dram read + write bytes) of ONE launch of the roofline kernel, from the ncu captures
+# summarised under profiles/ (the same bench command under ncu; c2 captured at --T 128 and scaled by
+# T, since the kernel streams gi/out once per time step).  None where no capture exists.
+ROOFLINE_TRAFFIC = {
+    "c1": dict(bytes=15.85e6, T=64),
+    "c2": dict(bytes=514.9e6, T=128),
+    "c4": dict(bytes=215.0e6, T=128),
+}
+
+
 # ---------------------------------------------------------------------------
 # synthetic problem (same generator on every rank, rank-specific data seed)
 # ---------------------------------------------------------------------------
@@ -332,7 +342,9 @@ def run_device(args):
                                 "diagonal": "diag_fwd_tma_kernel", "butterfly": "bfly_fwd2_kernel"}[cfg["kind"]],
                      "bound": "hbm", "achieved": achieved, "peak": peak_gbs, "unit": "GB/s",
                      "frac": achieved / peak_gbs, "peak_source": "measured" if peaks else "fallback",
-                     "traffic": None, "launch_ms": k_ms, "per_step_us": k_ms * 1e3 / wl.T,
+                     "traffic": (ROOFLINE_TRAFFIC[args.config]["bytes"] * wl.T / ROOFLINE_TRAFFIC[args.config]["T"]
+                                 if args.config in ROOFLINE_TRAFFIC and not args.B else None),
+                     "launch_ms": k_ms, "per_step_us": k_ms * 1e3 / wl.T,
                      "launches_per_call": scan_launches,
                      "algorithmic_bytes_per_launch": wl.scan_fwd_bytes()},
     }
