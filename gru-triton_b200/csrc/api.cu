@@ -88,14 +88,21 @@ static bool parse_shape(const b200gru_shape* s, Dims* d) {
 
 static size_t s_bytes(const Dims& d) { return align_up((size_t)4 * d.T * d.B * d.H * sizeof(float), 256); }
 
+static size_t wt_bytes(const Dims& d) {
+  return align_up((size_t)3 * d.nb * d.Hb * transposed_row_bound(d.Hb) * sizeof(float), 256);
+}
+static bool step_path(const Dims& d) { return d.kind == B200GRU_DENSE && dense_step_path(d.B, d.H); }
+
 // backward: 0 forward, 1 backward that recomputes the gates, 2 backward that is given `save`
 static size_t workspace_bytes(const Dims& d, int backward) {
   const size_t s_need = (backward == 2) ? 0 : s_bytes(d);
   switch (d.kind) {
     case B200GRU_DENSE:
     case B200GRU_MONARCH:
-      if (!backward) return align_up((size_t)3 * d.nb * d.Hb * transposed_row_bound(d.Hb) * sizeof(float), 256);
-      return s_need + weight_grads_scratch_bytes(d.T, d.B, d.H, d.nb, d.Hb);
+      if (!backward)
+        return wt_bytes(d) + (step_path(d) ? dense_step_fwd_scratch_bytes(d.B, d.H) : 0);
+      return s_need + weight_grads_scratch_bytes(d.T, d.B, d.H, d.nb, d.Hb) +
+             (step_path(d) ? dense_step_bwd_scratch_bytes(d.B, d.H) : 0);
     case B200GRU_DIAGONAL:
       return backward ? diag_bwd_workspace_bytes(d.T, d.B, d.H) : 0;
     case B200GRU_BUTTERFLY: {
@@ -154,6 +161,14 @@ int b200gru_scan_forward(const b200gru_shape* shape, const float* gi, const floa
       return diag_forward(gi, h0, W, bh, out, d.T, d.B, d.H, qi, qo, st);
     case B200GRU_DENSE:
     case B200GRU_MONARCH: {
+      if (step_path(d)) {
+        float* Wt = static_cast<float*>(workspace);
+        float* scratch = reinterpret_cast<float*>(static_cast<char*>(workspace) + wt_bytes(d));
+        const int WtR = ((d.H + 3) & ~3) + 4;
+        int rc = launch_transpose_weights(W, Wt, 1, d.H, WtR, d.gate_stride, d.block_stride, st);
+        if (rc) return rc;
+        return launch_dense_step_forward(gi, h0, Wt, WtR, bh, out, save, scratch, d.T, d.B, d.H, qi, qo, st);
+      }
       BlockScanConfig cfg;
       if (!choose_block_config(true, d.B, d.Hb, d.nb, &cfg)) return B200GRU_UNSUPPORTED;
       BlockScanArgs a;
@@ -218,6 +233,13 @@ int b200gru_scan_backward(const b200gru_shape* shape, const float* gi, const flo
         int rc = launch_recompute_gates(g, st);
         if (rc) return rc;
         S = S_ws;
+      }
+      if (step_path(d)) {
+        float* step_ws = reinterpret_cast<float*>(ws + s_off + weight_grads_scratch_bytes(d.T, d.B, d.H, d.nb, d.Hb));
+        int rc = launch_dense_step_backward(h0, W, out, S, dout, dgi, dh0, step_ws, d.T, d.B, d.H, qi, qo, st);
+        if (rc) return rc;
+        g.S = const_cast<float*>(S);
+        return launch_weight_grads(g, st);
       }
       BlockScanConfig cfg;
       if (!choose_block_config(false, d.B, d.Hb, d.nb, &cfg)) return B200GRU_UNSUPPORTED;

@@ -121,6 +121,29 @@ def test_butterfly_alternate_kernels(monkeypatch, T, B, H, extra, quant):
     check_backward("butterfly", grads, gi, h0, W, bh, out, dout, quant)
 
 
+@pytest.mark.parametrize("quant", [None, Q8, Q8_ASYM], ids=["fp32", "q8", "q8asym"])
+@pytest.mark.parametrize("T,B,H", [(5, 128, 544), (6, 134, 576), (3, 130, 1024), (1, 128, 640), (4, 257, 608)])
+def test_dense_per_step_path(T, B, H, quant):
+    """Dense problems whose weight slice misses a cluster's shared memory, at batch >= 128, run as
+    one fused SGEMM launch per time step (forward and backward); ragged batches exercise the
+    padded transposed operand buffers."""
+    fwd, bwd, auto = _mods()["dense"]
+    gi, h0, W, bh, dout = orc.make_problem("dense", T, B, H, seed=T + B + H)
+    kw = dict(h_in_quant=quant[0], h_out_quant=quant[1]) if quant else {}
+    d = _cuda(gi, h0, W, bh, dout)
+    out = fwd(*d[:4], **kw)
+    check_forward("dense", out, gi, h0, W, bh, quant)
+    grads = bwd(*d[:4], out, d[4], **kw)
+    check_backward("dense", grads, gi, h0, W, bh, out, dout, quant)
+    # autograd route (the forward hands its gate activations to the backward)
+    leaves = [t.clone().requires_grad_(True) for t in d[:4]]
+    out2 = auto(*leaves, **kw)
+    assert torch.equal(out2.detach(), out)
+    out2.backward(d[4])
+    for g_auto, g_exp in zip([t.grad for t in leaves], grads):
+        assert rel_err(g_auto, g_exp) <= GRAD_TOL
+
+
 @pytest.mark.parametrize("kind,name", SCAN_GOLDEN_FLAT)
 def test_golden_vectors_through_the_cuda_path(kind, name):
     g = load_golden(name)
