@@ -319,10 +319,15 @@ block_fwd_kernel(const BlockScanArgs a) {
     float* hnxt = hbuf + (p ^ 1) * HbP * BT;
     PHASE_START();
     if (t > 0) {
-      mbar_wait(full0 + 8 * p, p ? phase1 : phase0, dead, a.status);
-      if (p) phase1 ^= 1u; else phase0 ^= 1u;
-      // buffer p is filled again by the sends of step t+1
-      if (tid == 0 && t + 1 <= a.T - 2) mbar_arm(full0 + 8 * p, step_bytes);
+      if (C == 1) {
+        // a single CTA owns the whole block: plain stores and one CTA barrier per step
+        __syncthreads();
+      } else {
+        mbar_wait(full0 + 8 * p, p ? phase1 : phase0, dead, a.status);
+        if (p) phase1 ^= 1u; else phase0 ^= 1u;
+        // buffer p is filled again by the sends of step t+1
+        if (tid == 0 && t + 1 <= a.T - 2) mbar_arm(full0 + 8 * p, step_bytes);
+      }
     }
     const unsigned nxt_addr = smem_u32(hnxt);
     const unsigned nxt_bar = full0 + 8 * (p ^ 1);
@@ -387,10 +392,14 @@ block_fwd_kernel(const BlockScanArgs a) {
             hq = a.qin.enabled ? fake_quant<true>(hnew, a.qin) : hnew;
           }
           if (t + 1 < a.T) {
-            // publish fq_in(h_t) of this element to every CTA of the cluster (itself included)
-            const unsigned eoff = (unsigned)(((u0 + j) * BT + eb) * sizeof(float));
-            for (int r = 0; r < C; ++r)
-              st_async_f32(map_to_rank(nxt_addr + eoff, r), hq, map_to_rank(nxt_bar, r));
+            if (C == 1) {
+              hnxt[(u0 + j) * BT + eb] = hq;
+            } else {
+              // publish fq_in(h_t) of this element to every CTA of the cluster (itself included)
+              const unsigned eoff = (unsigned)(((u0 + j) * BT + eb) * sizeof(float));
+              for (int r = 0; r < C; ++r)
+                st_async_f32(map_to_rank(nxt_addr + eoff, r), hq, map_to_rank(nxt_bar, r));
+            }
           }
         }
         gr[q] = ngr; gz[q] = ngz; gn[q] = ngn;
@@ -654,7 +663,17 @@ block_bwd_kernel(const BlockScanArgs a) {
           }
         }
         const int dst0 = kbase / Hc, jj0 = kbase - dst0 * Hc;
-        if ((TW * BT) % 4 == 0 && jj0 + TW <= Hc) {
+        if (C == 1) {
+          // single CTA: the "receive" rows are local
+#pragma unroll
+          for (int i = 0; i < TW; ++i) {
+            const int k = kbase + i;
+            if (k < HbP) {
+#pragma unroll
+              for (int bb = 0; bb < BT; ++bb) rcur[k * BT + bb] = acc[i * BT + bb];
+            }
+          }
+        } else if ((TW * BT) % 4 == 0 && jj0 + TW <= Hc) {
           // the TW positions of this lane belong to one rank and form one contiguous run there
           const unsigned doff = (unsigned)((rank * slice + jj0 * BT) * sizeof(float));
           const unsigned daddr = map_to_rank(rcur_addr + doff, dst0), dbar = map_to_rank(rcur_bar, dst0);
@@ -677,9 +696,13 @@ block_bwd_kernel(const BlockScanArgs a) {
       }
     }
     PHASE_MARK(12);
-    mbar_wait(rcur_bar, par ? phase1 : phase0, dead, a.status);
-    if (par) phase1 ^= 1u; else phase0 ^= 1u;
-    if (tid == 0 && t >= 2) mbar_arm(rcur_bar, step_bytes);     // this buffer receives again two steps on
+    if (C == 1) {
+      __syncthreads();
+    } else {
+      mbar_wait(rcur_bar, par ? phase1 : phase0, dead, a.status);
+      if (par) phase1 ^= 1u; else phase0 ^= 1u;
+      if (tid == 0 && t >= 2) mbar_arm(rcur_bar, step_bytes);     // this buffer receives again two steps on
+    }
     PHASE_MARK(13);
 
     // ---- dh for the owned elements: C partials in rank order
