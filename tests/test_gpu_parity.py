@@ -340,6 +340,33 @@ def test_baseline_config_shapes_forward_backward():
         check_backward(kind, sub, gi[:, :bsub], h0[:bsub], W, bh, out[:, :bsub], dout[:, :bsub], quant)
 
 
+def test_baseline_config5_shard_shape():
+    """C5 as one of eight GPUs sees it (B=512, H=1024, int8 weights and hidden state), T cut to 8:
+    the full launch runs on the device, the oracle checks a slice of the independent batch rows
+    (forward codes, dgi and dh0); dW and dbh are checked through their linearity in the batch:
+    the gradient of the whole batch equals the sum over two halves run separately."""
+    T, B, H, bsub = 8, 512, 1024, 3
+    fwd, bwd, _ = _mods()["dense"]
+    gi, h0, W, bh, dout = orc.make_problem("dense", T, B, H, seed=5, h0_scale=0.1)
+    W = orc.per_row_weight_fake_quant(W)                      # int8 grid per output row
+    quant = ((0.008, -127, 127), (0.008, -127, 127))
+    kw = dict(h_in_quant=quant[0], h_out_quant=quant[1])
+    d = _cuda(gi, h0, W, bh, dout)
+    out = fwd(*d[:4], **kw)
+    check_forward("dense", out[:, :bsub], gi[:, :bsub], h0[:bsub], W, bh, quant)
+    grads = bwd(*d[:4], out, d[4], **kw)
+    ref = orc.scan_backward("dense", gi[:, :bsub], h0[:bsub], W, bh, out[:, :bsub].cpu(), dout[:, :bsub], *quant)
+    assert rel_err(grads[0][:, :bsub].cpu(), ref[0]) <= GRAD_TOL
+    assert rel_err(grads[1][:bsub].cpu(), ref[1]) <= GRAD_TOL
+    halves = []
+    for sl in (slice(0, B // 2), slice(B // 2, B)):
+        halves.append(bwd(d[0][:, sl].contiguous(), d[1][sl].contiguous(), d[2], d[3], out[:, sl].contiguous(),
+                          d[4][:, sl].contiguous(), **kw))
+    assert rel_err(halves[0][2] + halves[1][2], grads[2]) <= GRAD_TOL
+    assert rel_err(halves[0][3] + halves[1][3], grads[3]) <= GRAD_TOL
+    assert torch.equal(torch.cat([halves[0][0], halves[1][0]], dim=1), grads[0])     # rows are independent
+
+
 @pytest.mark.parametrize("kind,T,B,H,extra", [("dense", 16, 32, 512, {}), ("dense", 6, 3, 1024, {}),
                                               ("monarch", 16, 32, 512, {"nblocks": 8}),
                                               ("monarch", 8, 5, 1024, {"nblocks": 2})])
