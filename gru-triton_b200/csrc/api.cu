@@ -227,6 +227,8 @@ int b200gru_scan_backward(const b200gru_shape* shape, const float* gi, const flo
       g.dW = dW; g.dbh = dbh; g.partial = scratch;
       g.T = d.T; g.B = d.B; g.H = d.H; g.nb = d.nb; g.Hb = d.Hb;
       g.w_gate_stride = d.gate_stride; g.w_block_stride = d.block_stride; g.qin = qi;
+      g.out_on_qin_grid = (qi.enabled && qo.enabled && qi.scale == qo.scale && qi.qmin == qo.qmin &&
+                           qi.qmax == qo.qmax) ? 1 : 0;
       const float* S = save;
       if (S == nullptr) {
         g.S = S_ws;

@@ -230,7 +230,9 @@ weight_grads_kernel(const BlockGemmArgs a, float* __restrict__ dst, int rows_per
           if (k + 2 < Hb) v.z = __ldg(hp + k + 2);
           if (k + 3 < Hb) v.w = __ldg(hp + k + 3);
         }
-        if (a.qin.enabled) {
+        // h_t (t >= 0) is already on the output grid: when both quantisers are the same grid,
+        // fq_in leaves it unchanged, so only rows taken from h0 need the rounding
+        if (a.qin.enabled && !(a.out_on_qin_grid && tb >= B)) {
           v.x = fake_quant<true>(v.x, a.qin); v.y = fake_quant<true>(v.y, a.qin);
           v.z = fake_quant<true>(v.z, a.qin); v.w = fake_quant<true>(v.w, a.qin);
         }
@@ -347,11 +349,19 @@ static WgPlan wg_plan(int T, int B, int nb, int Hb) {
   p.ntm = cdiv(3 * Hb, 16 * p.tm);
   p.ntn = cdiv(Hb, 16 * p.tn);
   const long long tiles = (long long)nb * p.ntm * p.ntn;
-  long long s = (2 * 148) / tiles;
-  const long long max_by_rows = cdiv(TB, 8 * WG_BK);
-  if (s > max_by_rows) s = max_by_rows;
-  if (s > 32) s = 32;
-  if (s < 1) s = 1;
+  // two CTAs fit an SM: pick the split count whose CTA total fills whole waves of 2 * 148 best
+  // (ties go to fewer splits: less partial traffic)
+  const long long slots = 2 * 148;
+  long long max_s = cdiv(TB, 8 * WG_BK);
+  if (max_s > 32) max_s = 32;
+  if (max_s < 1) max_s = 1;
+  long long s = 1;
+  double best = 0.0;
+  for (long long c = 1; c <= max_s; ++c) {
+    const long long ctas = tiles * c;
+    const double eff = (double)ctas / (double)(((ctas + slots - 1) / slots) * slots);
+    if (eff > best + 0.03) { best = eff; s = c; }
+  }
   const int rps = cdiv(cdiv(TB, (int)s), WG_BK) * WG_BK;
   p.nsplit = cdiv(TB, rps);
   p.rows_per_split = rps;

@@ -67,6 +67,7 @@ struct BlockGemmArgs {
   int T, B, H, nb, Hb;
   long long w_gate_stride, w_block_stride;
   Quant qin;
+  int out_on_qin_grid;   // weight_grads: `out` was produced by an output quantiser identical to qin
 };
 
 int launch_transpose_weights(const float* W, float* Wt, int nb, int Hb, int WtR, long long w_gate_stride,
