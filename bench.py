@@ -455,6 +455,9 @@ def run_reference(args):
         times.append(time.perf_counter() - t0)
     dt = sum(times) / len(times)
     v = units / dt
+    if args.gpus > 1:
+        sample = sample.replace("the full workload", f"one rank's shard (1/{args.gpus} of the job; the host's "
+                                "throughput does not depend on how many shards it is given)")
     print(json.dumps({
         "impl": "reference", "metric": "sequence-steps/sec (T*B/s)", "value": v, "unit": "seq-steps/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
