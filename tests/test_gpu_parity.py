@@ -170,7 +170,7 @@ def test_golden_vectors_through_the_cuda_path(kind, name):
     ("butterfly", 5, 3, 2, {}), ("butterfly", 5, 3, 12, {}), ("butterfly", 4, 2, 8, {"butterfly_nblocks": 2}),
     ("butterfly", 3, 5, 48, {"butterfly_nblocks": 3}), ("butterfly", 3, 2, 1024, {}),
 ])
-@pytest.mark.parametrize("quant", [None, Q8], ids=["fp32", "q8"])
+@pytest.mark.parametrize("quant", [None, Q8, Q8_ASYM], ids=["fp32", "q8", "q8asym"])
 def test_edge_shapes(kind, T, B, H, extra, quant):
     fwd, bwd, _ = _mods()[kind]
     gi, h0, W, bh, dout = orc.make_problem(kind, T, B, H, seed=7 + H, **extra)
