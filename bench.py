@@ -51,7 +51,7 @@ CONFIGS = {
 # T, since the kernel streams gi/out once per time step).  None where no capture exists.
 ROOFLINE_TRAFFIC = {
     "c1": dict(bytes=15.85e6, T=64),
-    "c2": dict(bytes=514.9e6, T=128),
+    "c2": dict(bytes=514.3e6, T=128),
     "c4": dict(bytes=215.0e6, T=128),
 }
 
