@@ -17,7 +17,11 @@
 // Reference: the same recurrence as scan.py:389-432 (forward) and scan.py:450-616 (backward),
 // where a spin barrier across batch tiles plays the role of the launch boundary.
 
+#include <cooperative_groups.h>
+
 #include "block_scan.cuh"
+
+namespace cg = cooperative_groups;
 
 namespace b200gru {
 
@@ -258,15 +262,24 @@ dense_step_bwd_first_kernel(const StepArgs a) {
           make_float4(tr[g][c][0], tr[g][c][1], tr[g][c][2], tr[g][c][3]);
 }
 
-// backward step t: CTA tile = (16*TM rows) x (16*TN positions k)
-template <int TM, int TN>
+// backward step t: CTA tile = (16*TM rows) x (16*TN positions k).
+// KSPLIT = 2 (64 x 64 tiles only): the two CTAs of a cluster (blockIdx.z) each take half of the
+// contraction range; CTA 1 then writes its accumulators into CTA 0's operand buffers (DSMEM stores
+// between two cluster barriers), CTA 0 adds them and runs the epilogue.  This doubles the number of
+// CTAs when the batch shard is too small to give every SM two tiles.
+template <int TM, int TN, int KSPLIT>
 __global__ void __launch_bounds__(256, 2)
 dense_step_bwd_kernel(const StepArgs a) {
   constexpr int BM = 16 * TM, BN = 16 * TN;
   constexpr int NA = TM / 4, NB = TN / 4;
-  __shared__ __align__(16) float As[2][DS_BK][BM];
-  __shared__ __align__(16) float Bs[2][DS_BK][BN];
-  const int H = a.H, B = a.B, Bp = a.Bp, K = 3 * a.H;
+  static_assert(KSPLIT == 1 || TM * TN * 256 <= 2 * DS_BK * (BM + BN), "accumulators must fit the operand buffers");
+  __shared__ __align__(16) float tiles[2 * DS_BK * (BM + BN)];
+  float (*As)[DS_BK][BM] = reinterpret_cast<float (*)[DS_BK][BM]>(tiles);
+  float (*Bs)[DS_BK][BN] = reinterpret_cast<float (*)[DS_BK][BN]>(tiles + 2 * DS_BK * BM);
+  const int H = a.H, B = a.B, Bp = a.Bp;
+  const int Kall = 3 * a.H;
+  const int kbeg = (KSPLIT == 1) ? 0 : (int)blockIdx.z * (Kall / KSPLIT);
+  const int K = (KSPLIT == 1) ? Kall : kbeg + Kall / KSPLIT;      // end of this CTA's range
   const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
   const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
 
@@ -300,11 +313,11 @@ dense_step_bwd_kernel(const StepArgs a) {
 #pragma unroll
     for (int j = 0; j < TN / 2; ++j) acc[i][j] = make_float2(0.f, 0.f);
 
-  fetch(0);
+  fetch(kbeg);
   stash(0);
   __syncthreads();
   int buf = 0;
-  for (int k0 = 0; k0 < K; k0 += DS_BK) {
+  for (int k0 = kbeg; k0 < K; k0 += DS_BK) {
     const bool more = k0 + DS_BK < K;
     if (more) fetch(k0 + DS_BK);
 #pragma unroll 4
@@ -331,6 +344,29 @@ dense_step_bwd_kernel(const StepArgs a) {
     if (more) stash(buf ^ 1);
     __syncthreads();
     buf ^= 1;
+  }
+
+  if (KSPLIT == 2) {
+    cg::cluster_group cluster = cg::this_cluster();
+    cluster.sync();                                        // both CTAs are done with their operand buffers
+    float4* mine = reinterpret_cast<float4*>(tiles) + tid * (TM * TN / 4);
+    if (blockIdx.z == 1) {
+      float4* dst = cluster.map_shared_rank(mine, 0);
+#pragma unroll
+      for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int j = 0; j < TN / 4; ++j)
+          dst[i * (TN / 4) + j] = make_float4(acc[i][2 * j].x, acc[i][2 * j].y, acc[i][2 * j + 1].x, acc[i][2 * j + 1].y);
+    }
+    cluster.sync();                                        // the partial sums have landed in CTA 0
+    if (blockIdx.z == 1) return;
+#pragma unroll
+    for (int i = 0; i < TM; ++i)
+#pragma unroll
+      for (int j = 0; j < TN / 4; ++j) {
+        const float4 v = mine[i * (TN / 4) + j];
+        acc[i][2 * j].x += v.x; acc[i][2 * j].y += v.y; acc[i][2 * j + 1].x += v.z; acc[i][2 * j + 1].y += v.w;
+      }
   }
 
   // ---- dh_{t-1} = direct_t + mask_in(h_{t-1}) * via, then the gate gradients of step t-1
@@ -460,12 +496,26 @@ int launch_dense_step_backward(const float* h0, const float* W, const float* out
 
   const long long t128 = (long long)cdiv(B, 128) * cdiv(H, 128);
   const long long t8464 = (long long)cdiv(B, 128) * cdiv(H, 64);
+  const long long t6464 = (long long)cdiv(B, 64) * cdiv(H, 64);
   int flip = 0;
   for (int t = T - 1; t >= 0; --t) {
     a.t = t; a.opT_in = opT[flip]; a.opT_out = opT[flip ^ 1];
-    if (t128 >= 120) dense_step_bwd_kernel<8, 8><<<dim3(cdiv(B, 128), cdiv(H, 128)), 256, 0, st>>>(a);
-    else if (t8464 >= 120) dense_step_bwd_kernel<8, 4><<<dim3(cdiv(B, 128), cdiv(H, 64)), 256, 0, st>>>(a);
-    else dense_step_bwd_kernel<4, 4><<<dim3(cdiv(B, 64), cdiv(H, 64)), 256, 0, st>>>(a);
+    if (t128 >= 120) dense_step_bwd_kernel<8, 8, 1><<<dim3(cdiv(B, 128), cdiv(H, 128)), 256, 0, st>>>(a);
+    else if (t8464 >= 120) dense_step_bwd_kernel<8, 4, 1><<<dim3(cdiv(B, 128), cdiv(H, 64)), 256, 0, st>>>(a);
+    else if (t6464 >= 2 * 148) dense_step_bwd_kernel<4, 4, 1><<<dim3(cdiv(B, 64), cdiv(H, 64)), 256, 0, st>>>(a);
+    else {
+      // too few tiles for two CTAs per SM: pairs of CTAs split the contraction
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(cdiv(B, 64), cdiv(H, 64), 2);
+      cfg.blockDim = dim3(256, 1, 1);
+      cfg.dynamicSmemBytes = 0;
+      cfg.stream = st;
+      cudaLaunchAttribute at[1];
+      at[0].id = cudaLaunchAttributeClusterDimension;
+      at[0].val.clusterDim.x = 1; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 2;
+      cfg.attrs = at; cfg.numAttrs = 1;
+      cudaLaunchKernelEx(&cfg, dense_step_bwd_kernel<4, 4, 2>, a);
+    }
     note_launch();
     flip ^= 1;
   }
