@@ -345,6 +345,10 @@ def run_device(args):
                     "launch_ms": k_ms, "per_step_us": k_ms * 1e3 / wl.T,
                     "launches_per_call": scan_launches,
                     "algorithmic_bytes_per_launch": wl.scan_fwd_bytes()}
+        if cfg["kind"] != "diagonal":
+            roofline["note"] = ("a serial chain of T dependent steps inside one launch: DRAM is nearly idle and no "
+                                "pipe is saturated (ncu: profiles/); the bound is the latency of one step, reported "
+                                "as per_step_us")
 
     units = wl.units() * world
     line = {
