@@ -50,6 +50,9 @@ __device__ int g_scan_status;
 
 namespace {
 
+#ifndef B200GRU_FWD_NR
+#define B200GRU_FWD_NR 6
+#endif
 constexpr int NT = BLOCK_SCAN_THREADS;   // threads per CTA
 constexpr int NW = NT / 32;
 
@@ -74,6 +77,28 @@ __device__ __forceinline__ void load_rows(const float* p, float (&v)[BT]) {
 #pragma unroll
     for (int q = 0; q < BT; ++q) v[q] = p[q];
   }
+}
+
+// The first BT floats of a 16-byte aligned row, in as few and as narrow loads as cover them
+// (5 rows: one float4 and one scalar).  Every lane reads the same row, and a broadcast load still
+// returns its full width to each lane, so loading the padding would cost return bandwidth.
+template <int BT, int BTX>
+__device__ __forceinline__ void load_rows_exact(const float* p, float (&v)[BTX]) {
+  int at = 0;
+  if constexpr (BT >= 4) {
+#pragma unroll
+    for (int q = 0; q < BT / 4; ++q) {
+      const float4 x = *reinterpret_cast<const float4*>(p + 4 * q);
+      v[4 * q] = x.x; v[4 * q + 1] = x.y; v[4 * q + 2] = x.z; v[4 * q + 3] = x.w;
+    }
+    at = (BT / 4) * 4;
+  }
+  if constexpr (BT % 4 >= 2) {
+    const float2 x = *reinterpret_cast<const float2*>(p + at);
+    v[at] = x.x; v[at + 1] = x.y;
+    at += 2;
+  }
+  if constexpr (BT % 2 == 1) v[at] = p[at];
 }
 
 // Sum `vals` over the 32 lanes of the warp.  While more than one value is left, each
@@ -306,6 +331,22 @@ block_fwd_kernel(const BlockScanArgs a) {
   }
   cluster.sync();            // weights, h_{-1} and the armed mbarriers are in place everywhere
 
+  // One item per warp: the weights of the first NR k-slabs stay in registers for the whole scan
+  // (the step is bound by the shared-memory return path, and a quarter of the register file is
+  // otherwise unused).
+  constexpr int NR = (IPW == 1) ? B200GRU_FWD_NR : 0;
+  float4 wreg[NR > 0 ? NR : 1][3];
+  if (NR > 0 && a.w_in_smem) {
+#pragma unroll
+    for (int i = 0; i < NR; ++i)
+#pragma unroll
+      for (int g = 0; g < 3; ++g) {
+        const int k = lane + 32 * i;
+        wreg[i][g] = (warp < nitems && k < Hb) ? *reinterpret_cast<const float4*>(wsm + k * a.RS + g * Hc4 + warp * 4)
+                                               : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+  }
+
   const size_t gi_step = (size_t)a.B * 3 * H;
   const size_t out_step = (size_t)a.B * H;
   const size_t comp = (size_t)a.T * out_step;
@@ -353,8 +394,22 @@ block_fwd_kernel(const BlockScanArgs a) {
             for (int b = 0; b < BT; ++b) acc[g][c][b] = make_float2(0.f, 0.f);
 
         const float* wp = wbase + item * 4;
-        if (a.w_in_smem) fwd_contract<BT, true>(acc, wp, kstride, gstride, hcur, lane, Hb);
-        else fwd_contract<BT, false>(acc, wp, kstride, gstride, hcur, lane, Hb);
+        if (a.w_in_smem) {
+          if (NR > 0) {
+#pragma unroll
+            for (int i = 0; i < NR; ++i) {
+              const int k = lane + 32 * i;
+              float hv[BT];
+              if (k < Hb) {
+                load_rows<BT>(hcur + k * BT, hv);
+                fwd_fma<BT>(acc, wreg[i], hv);
+              }
+            }
+          }
+          fwd_contract<BT, true>(acc, wp, kstride, gstride, hcur, lane + 32 * NR, Hb);
+        } else {
+          fwd_contract<BT, false>(acc, wp, kstride, gstride, hcur, lane, Hb);
+        }
         PHASE_MARK(0);
 
         float s[3];
@@ -593,7 +648,7 @@ block_bwd_kernel(const BlockScanArgs a) {
                 w[0] = wp[0];
               }
               float xv[BTX];
-              load_rows<BTX>(xp, xv);
+              load_rows_exact<BT, BTX>(xp, xv);
               if constexpr (TW == 4) {
                 // packed FP32 FMA: positions (0,1) and (2,3) of the weight float4 share an instruction
 #pragma unroll
@@ -621,7 +676,7 @@ block_bwd_kernel(const BlockScanArgs a) {
               w[i] = (j < nown && kbase + i < Hb)
                          ? __ldg(wbase + (size_t)g * gstride + (size_t)j * rstride + kbase + i) : 0.f;
             float xv[BTX];
-            load_rows<BTX>(xs + c * BTX, xv);
+            load_rows_exact<BT, BTX>(xs + c * BTX, xv);
 #pragma unroll
             for (int i = 0; i < TW; ++i)
 #pragma unroll
