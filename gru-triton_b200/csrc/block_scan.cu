@@ -331,20 +331,23 @@ block_fwd_kernel(const BlockScanArgs a) {
   }
   cluster.sync();            // weights, h_{-1} and the armed mbarriers are in place everywhere
 
-  // One item per warp: the weights of the first NR k-slabs stay in registers for the whole scan
-  // (the step is bound by the shared-memory return path, and a quarter of the register file is
-  // otherwise unused).
-  constexpr int NR = (IPW == 1) ? B200GRU_FWD_NR : 0;
-  float4 wreg[NR > 0 ? NR : 1][3];
+  // A warp meets the same weights at every step, so the first NR k-slabs of each of its items stay
+  // in registers for the whole scan (the step is bound by the shared-memory return path, and a
+  // quarter of the register file is otherwise unused).
+  constexpr int NR = (IPW == 1) ? B200GRU_FWD_NR : (IPW == 2 ? B200GRU_FWD_NR / 2 : 0);
+  float4 wreg[IPW][NR > 0 ? NR : 1][3];
   if (NR > 0 && a.w_in_smem) {
 #pragma unroll
-    for (int i = 0; i < NR; ++i)
+    for (int q = 0; q < IPW; ++q)
 #pragma unroll
-      for (int g = 0; g < 3; ++g) {
-        const int k = lane + 32 * i;
-        wreg[i][g] = (warp < nitems && k < Hb) ? *reinterpret_cast<const float4*>(wsm + k * a.RS + g * Hc4 + warp * 4)
-                                               : make_float4(0.f, 0.f, 0.f, 0.f);
-      }
+      for (int i = 0; i < NR; ++i)
+#pragma unroll
+        for (int g = 0; g < 3; ++g) {
+          const int k = lane + 32 * i, item = warp + q * NW;
+          wreg[q][i][g] = (item < nitems && k < Hb)
+                              ? *reinterpret_cast<const float4*>(wsm + k * a.RS + g * Hc4 + item * 4)
+                              : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
   }
 
   const size_t gi_step = (size_t)a.B * 3 * H;
@@ -402,7 +405,7 @@ block_fwd_kernel(const BlockScanArgs a) {
               float hv[BT];
               if (k < Hb) {
                 load_rows<BT>(hcur + k * BT, hv);
-                fwd_fma<BT>(acc, wreg[i], hv);
+                fwd_fma<BT>(acc, wreg[q][i], hv);
               }
             }
           }
