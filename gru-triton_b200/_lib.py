@@ -30,7 +30,22 @@ class CShape(ctypes.Structure):
                 ("nblocks", ctypes.c_int), ("log2_hpad", ctypes.c_int)]
 
 
+class CGemmArgs(ctypes.Structure):
+    _fields_ = [("dtype", ctypes.c_int), ("M", ctypes.c_int), ("N", ctypes.c_int), ("K", ctypes.c_int),
+                ("A", ctypes.c_void_p), ("B", ctypes.c_void_p),
+                ("a_planes", ctypes.c_int), ("b_planes", ctypes.c_int),
+                ("a_mn_major", ctypes.c_int), ("b_mn_major", ctypes.c_int),
+                ("lda", ctypes.c_longlong), ("ldb", ctypes.c_longlong),
+                ("a_plane_stride", ctypes.c_longlong), ("b_plane_stride", ctypes.c_longlong),
+                ("npairs", ctypes.c_int), ("pair_a", ctypes.c_int * 9), ("pair_b", ctypes.c_int * 9),
+                ("split_k", ctypes.c_int), ("tile_n", ctypes.c_int), ("chunk_kblocks", ctypes.c_int),
+                ("alpha", ctypes.c_float),
+                ("row_scale", ctypes.c_void_p), ("col_scale", ctypes.c_void_p), ("bias", ctypes.c_void_p),
+                ("C", ctypes.c_void_p), ("ldc", ctypes.c_longlong), ("split_stride", ctypes.c_longlong)]
+
+
 _P = ctypes.c_void_p
+_GP = ctypes.POINTER(CGemmArgs)
 _QP = ctypes.POINTER(CQuant)
 _SP = ctypes.POINTER(CShape)
 _I = ctypes.c_int
@@ -51,6 +66,9 @@ SIGNATURES = {
     "b200gru_butterfly_forward": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _I, _QP, _QP, _P, _P, _P, _Z, _P]),
     "b200gru_butterfly_backward": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _QP, _QP, _P, _P, _P, _P, _P, _Z, _P]),
     "b200gru_diagonal_backward_noalloc": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _QP, _QP, _P, _P, _P, _P, _P]),
+    "b200gru_tc_gemm": (_I, [_GP, _P]),
+    "b200gru_tc_gemm_splits": (_I, [_GP, _I]),
+    "b200gru_split_bf16": (_I, [_P, _P, _Z, _Z, _I, _P, _I, _P]),
     "b200gru_device_status": (_I, [_I]),
     "b200gru_launch_count": (ctypes.c_ulonglong, []),
     "b200gru_strerror": (ctypes.c_char_p, [_I]),

@@ -1,0 +1,153 @@
+// Blackwell tensor-core plumbing shared by the tcgen05 kernels (sm_100a): mbarrier, TMA tile
+// loads (no multicast form anywhere), tensor-memory allocation, UMMA descriptors, tcgen05.mma /
+// commit / ld wrappers, and bounded waits.
+//
+// Waits: every mbarrier wait polls try_wait against a clock64() budget.  A wait that runs out
+// marks the CTA dead (shared flag) and sets the device status word; from then on every wait of
+// that CTA returns at once, the roles fall through their loops, tensor memory is freed and the
+// kernel returns.  A CTA that starts while the status word is already set leaves immediately.
+#pragma once
+
+#include <cuda.h>         // CUtensorMap and its enums (types only; the encoder is looked up at run time)
+#include <cuda_bf16.h>
+
+#include "common.cuh"
+
+namespace b200gru {
+namespace tc {
+
+constexpr long long WAIT_BUDGET_CYCLES = 1ll << 30;   // about half a second at 1.9 GHz
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_fence_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+               "selp.u32 %0, 1, 0, p;\n\t}" : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+
+// Bounded wait.  `dead` is a CTA-shared int; `status` the device-wide health word.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* dead, int* status) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long start = clock64();
+  while (true) {
+    if (*dead) return false;
+    if (mbar_try_wait(bar, parity)) return true;
+    if (clock64() - start > WAIT_BUDGET_CYCLES) {
+      *dead = 1;
+      atomicExch(status, 1);
+      return false;
+    }
+  }
+}
+
+// ---- TMA tile loads (tensor map in kernel parameter space, destination in this CTA) ----------
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2,
+                                            uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_map(const CUtensorMap* map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
+
+// ---- tensor memory ---------------------------------------------------------------------------
+// Whole warp, converged.  ncols: power of two in [32, 512].
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// 32 lanes x 32 consecutive columns: thread i of the warp receives lane (base lane + i).
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+        "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+        "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// ---- UMMA descriptors --------------------------------------------------------------------------
+// Shared-memory matrix descriptor, 128-byte swizzle, descriptor version 1 (Blackwell).
+//   bits [0,14)  start address >> 4      bits [16,30) leading byte offset >> 4
+//   bits [32,46) stride byte offset >> 4 bits [46,48) version   bits [61,64) layout (2 = SWIZZLE_128B)
+// K-major operand (rows of 128 bytes along K, 8-row groups 1024 bytes apart): LBO unused, SBO 1024.
+// MN-major operand (rows of 128 bytes along M/N, one row per k; 64-element chunks `lbo` apart):
+// LBO = chunk stride, SBO = 1024 (eight k rows).
+__device__ __forceinline__ uint64_t umma_smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr >> 4) & 0x3fffu);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3fffu) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3fffu) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
+// Instruction descriptor of tcgen05.mma (dense, no negate, no saturate):
+//   bits [4,6) accumulator format (1 = F32, 2 = S32)   bits [7,10) A format   bits [10,13) B format
+//   (kind::f16: 1 = BF16; kind::i8: 1 = signed 8 bit)   bit 15 A is MN-major   bit 16 B is MN-major
+//   bits [17,23) N >> 3   bits [24,29) M >> 4
+__host__ __device__ constexpr uint32_t umma_idesc(bool is_i8, bool a_mn, bool b_mn, int M, int N) {
+  return ((is_i8 ? 2u : 1u) << 4) | (1u << 7) | (1u << 10) | ((a_mn ? 1u : 0u) << 15) | ((b_mn ? 1u : 0u) << 16) |
+         ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+
+// D[tmem] (+)= A[smem] * B[smem]; issued by one thread.
+template <bool I8>
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                     uint32_t accumulate) {
+  if (I8) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+  } else {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+  }
+}
+
+// The mbarrier receives one arrival once every tcgen05.mma issued so far by this thread is done.
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// ---- host side ---------------------------------------------------------------------------------
+// 3-D tiled tensor map (dims innermost first), 128-byte swizzle, zero fill out of bounds.
+// Returns B200GRU_OK or an error status; looks the driver's encoder up on first use.
+int make_tensor_map_3d(CUtensorMap* map, CUtensorMapDataType dtype, const void* base, unsigned long long d0,
+                       unsigned long long d1, unsigned long long d2, unsigned long long stride1_bytes,
+                       unsigned long long stride2_bytes, unsigned box0, unsigned box1);
+
+// Device-wide health word of the tcgen05 kernels (tc_gemm.cu); -1 on CUDA error.
+int tc_read_status(int reset);
+int* tc_status_word();
+
+}  // namespace tc
+}  // namespace b200gru

@@ -151,6 +151,59 @@ int b200gru_butterfly_backward(const float* gi, const float* h0, const float* tw
                                float* dgi, float* dh0, float* dtwiddles, float* dbh,
                                void* workspace, size_t workspace_bytes, void* stream);
 
+/* ---- tensor-core GEMM core (tcgen05 / tensor memory) ------------------------------------------
+ * The products of the path that are real GEMMs -- the input projection gi = x . Wi^T + bi
+ * (F.linear, src/gru_qat/gru_layer.py:251-253, src/gru_qat/gru_cell.py:410-435), the per-step
+ * h . Wh^T and dgh . Wh at GEMM-sized batch (tl.dot, src/gru_qat/triton_kernels/scan.py:153-155,
+ * 521-569) and the weight gradients dgh^T . h (scan.py:573-616) -- run on one kernel:
+ *
+ *   C[s][M,N] = alpha * row_scale[m] * col_scale[n] * sum_q A_{pair_a[q]} . B_{pair_b[q]}^T + bias[n]
+ *
+ * Operands are bf16 (dtype 0, fp32 accumulation) or int8 (dtype 1, exact int32 accumulation) and
+ * come as 1..3 planes: an fp32 operand is split into bf16 terms hi + mid + lo by
+ * b200gru_split_bf16 (three planes are exact), an operand on an int8 grid is one exact plane of
+ * codes.  pair_a / pair_b list the plane cross products to accumulate.
+ *   a_mn_major == 0: A is [planes][M][lda] (K contiguous);  1: A is [planes][K][lda] (M contiguous)
+ *   b_mn_major == 0: B is [planes][N][ldb] (K contiguous);  1: B is [planes][K][ldb] (N contiguous)
+ * (int8 operands: K contiguous only).  Strides in elements; bases 16-byte aligned; byte strides
+ * multiples of 16; N and ldc multiples of 4.  split_k > 1 writes split_k partial matrices
+ * `split_stride` floats apart (sum them in order); it must be the value b200gru_tc_gemm_splits
+ * returns for the wanted count.  row_scale / col_scale / bias may be NULL.
+ * The tensor core's fp32 accumulator truncates, so the sum is built in chunks: chunk_kblocks
+ * k-blocks (64 bf16 / 128 int8 elements of K each) are accumulated in tensor memory, then added
+ * to a register total with round-to-nearest.  0 picks at most 32 accumulation steps per chunk
+ * (int8: one chunk, the int32 sum is exact). */
+typedef struct {
+  int dtype;
+  int M, N, K;
+  const void* A;
+  const void* B;
+  int a_planes, b_planes;
+  int a_mn_major, b_mn_major;
+  long long lda, ldb, a_plane_stride, b_plane_stride;
+  int npairs;
+  int pair_a[9], pair_b[9];
+  int split_k;
+  int tile_n;             /* 0 = library's choice, else 64, 128 or 256 */
+  int chunk_kblocks;      /* 0 = library's choice; see below */
+  float alpha;
+  const float* row_scale;
+  const float* col_scale;
+  const float* bias;
+  float* C;
+  long long ldc, split_stride;
+} b200gru_gemm_args;
+
+int b200gru_tc_gemm(const b200gru_gemm_args* args, void* stream);
+int b200gru_tc_gemm_splits(const b200gru_gemm_args* args, int wanted);
+
+/* dst[p][i] (bf16, planes `plane_stride` elements apart) = p-th bf16 term of
+ * src[i] * col_scale[i % ncols] (col_scale may be NULL): hi = RN(x), mid = RN(x - hi),
+ * lo = RN(x - hi - mid).  n % 4 == 0.  Operand preparation for b200gru_tc_gemm; the reference
+ * feeds fp32 tensors to tl.dot / cuBLAS directly. */
+int b200gru_split_bf16(const float* src, void* dst, size_t n, size_t plane_stride, int planes,
+                       const float* col_scale, int ncols, void* stream);
+
 /* Diagonal backward for callers that cannot allocate device memory.  It has no counterpart in
  * the reference (whose wrappers always allocate their scratch with torch).  Same inputs, outputs
  * and results as b200gru_diagonal_backward, but no workspace argument: the partial sums go into a
