@@ -53,6 +53,11 @@ SCAN_GOLDEN = {
 }
 SCAN_GOLDEN_FLAT = [(k, n) for k, names in SCAN_GOLDEN.items() for n in names]
 
+# Butterfly fixtures produced on a GPU by the reference's own Triton kernels
+# (tests/golden/make_golden_butterfly_gpu.py): they pin the stage / stride / twiddle convention.
+BUTTERFLY_REFERENCE_GOLDEN = ["ref_butterfly_h16", "ref_butterfly_h8_nb2", "ref_butterfly_h12_pad",
+                              "ref_butterfly_h32_nb2", "ref_butterfly_h16_q8"]
+
 
 def rel_err(a: torch.Tensor, b: torch.Tensor) -> float:
     """max|a-b| / max(1e-30, max|b|) -- the reference tests' 'relative' measure."""

@@ -1,7 +1,8 @@
 """Generate the golden fixtures under tests/golden/ from the reference itself.
 
-Run where the reference checkout is importable (its ``src`` directory is taken
-from ``$GRU_QAT_REFERENCE_SRC``, default ``/root/reference/src``):
+Run where the reference package is importable: from ``$GRU_QAT_REFERENCE_SRC`` (the
+checkout's ``src`` directory) or, by default, from the copy that ``python oracle/make_ref.py``
+installs into ``oracle/_ref``:
 
     python tests/golden/make_golden.py
 
@@ -40,7 +41,7 @@ import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 REPO = os.path.dirname(os.path.dirname(HERE))
-REF_SRC = os.environ.get("GRU_QAT_REFERENCE_SRC", "/root/reference/src")
+REF_SRC = os.environ.get("GRU_QAT_REFERENCE_SRC", os.path.join(REPO, "oracle", "_ref"))
 sys.path.insert(0, REF_SRC)
 sys.path.insert(0, REPO)
 

@@ -181,7 +181,7 @@ def test_library_exports_every_declared_symbol():
     """The shared library loads and exports each function include/b200gru.h declares."""
     header = open(os.path.join(REPO, "include", "b200gru.h")).read()
     header = re.sub(r"/\*.*?\*/", "", header, flags=re.S)
-    declared = set(re.findall(r"\b(b200gru_[a-z_]+)\s*\(", header))
+    declared = set(re.findall(r"\b(b200gru_[a-z0-9_]+)\s*\(", header))
     assert declared == set(_lib.SIGNATURES), declared ^ set(_lib.SIGNATURES)
     lib = _lib.load()
     for name in declared:

@@ -7,7 +7,7 @@ import os
 import pytest
 import torch
 
-from conftest import SCAN_GOLDEN_FLAT, load_golden, rel_err
+from conftest import BUTTERFLY_REFERENCE_GOLDEN, SCAN_GOLDEN_FLAT, load_golden, rel_err
 from oracle import gru_scan_oracle as orc
 
 FWD_TOL = 1e-5     # fp32 forward: 1e-5 absolute and relative
@@ -42,6 +42,21 @@ def test_autograd_form_matches_scan_form(kind, name):
     assert rel_err(out.detach(), g["out"]) < FWD_TOL
     for nm, leaf in zip(("dgi", "dh0", "dW", "dbh"), leaves):
         assert rel_err(leaf.grad, g[nm]) < GRAD_TOL, nm
+
+
+@pytest.mark.parametrize("name", BUTTERFLY_REFERENCE_GOLDEN)
+def test_butterfly_oracle_matches_the_references_own_kernels(name):
+    """The fixtures are outputs of the reference's Triton butterfly scan (forward and backward,
+    scan_butterfly.py:369-459, 971-1075) run on a B200: they pin the oracle's reading of the stage
+    order (reversed on odd factors), the twiddle axis and the 2x2 orientation.  That kernel has no
+    tensor-core product, so it agrees with fp32 CPU arithmetic far inside the usual bars."""
+    g = load_golden(name)
+    out = orc.scan_forward("butterfly", g["gi"], g["h0"], g["W"], g["bh"], g["q_in"], g["q_out"])
+    assert (out - g["out"]).abs().max().item() < FWD_TOL
+    got = orc.scan_backward("butterfly", g["gi"], g["h0"], g["W"], g["bh"], g["out"], g["dout"],
+                            g["q_in"], g["q_out"])
+    for nm, a in zip(("dgi", "dh0", "dW", "dbh"), got):
+        assert rel_err(a, g[nm]) < GRAD_TOL, nm
 
 
 @pytest.mark.parametrize("n,nblocks", [(2, 1), (8, 1), (16, 2), (32, 3)])
@@ -90,10 +105,13 @@ def test_layer_train_step_matches_reference(name, kind):
     assert rel_err(grads["dbi"], torch.cat([G["cell.b_ir"], G["cell.b_iz"], G["cell.b_in"]])) < GRAD_TOL
 
 
-REF_SRC = os.environ.get("GRU_QAT_REFERENCE_SRC", "/root/reference/src")
+# The unmodified reference package: $GRU_QAT_REFERENCE_SRC, else the copy oracle/make_ref.py installs.
+REF_SRC = os.environ.get("GRU_QAT_REFERENCE_SRC",
+                         os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "oracle", "_ref"))
 
 
-@pytest.mark.skipif(not os.path.isdir(REF_SRC), reason="reference checkout not present")
+@pytest.mark.skipif(not os.path.isfile(os.path.join(REF_SRC, "gru_qat", "__init__.py")),
+                    reason="reference package not installed (python oracle/make_ref.py)")
 @pytest.mark.parametrize("kind", ["dense", "diagonal", "monarch"])
 @pytest.mark.parametrize("quant", [None, ((0.02, -127, 127), (0.015, -127, 127))])
 def test_oracle_against_live_reference(kind, quant):
