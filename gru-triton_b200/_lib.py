@@ -38,7 +38,7 @@ class CGemmArgs(ctypes.Structure):
                 ("lda", ctypes.c_longlong), ("ldb", ctypes.c_longlong),
                 ("a_plane_stride", ctypes.c_longlong), ("b_plane_stride", ctypes.c_longlong),
                 ("npairs", ctypes.c_int), ("pair_a", ctypes.c_int * 9), ("pair_b", ctypes.c_int * 9),
-                ("split_k", ctypes.c_int), ("tile_n", ctypes.c_int), ("chunk_kblocks", ctypes.c_int),
+                ("split_k", ctypes.c_int), ("tile_n", ctypes.c_int), ("chunk_kblocks", ctypes.c_int), ("accumulate", ctypes.c_int),
                 ("alpha", ctypes.c_float),
                 ("row_scale", ctypes.c_void_p), ("col_scale", ctypes.c_void_p), ("bias", ctypes.c_void_p),
                 ("C", ctypes.c_void_p), ("ldc", ctypes.c_longlong), ("split_stride", ctypes.c_longlong)]
@@ -66,6 +66,11 @@ SIGNATURES = {
     "b200gru_butterfly_forward": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _I, _QP, _QP, _P, _P, _P, _Z, _P]),
     "b200gru_butterfly_backward": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _QP, _QP, _P, _P, _P, _P, _P, _Z, _P]),
     "b200gru_diagonal_backward_noalloc": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _QP, _QP, _P, _P, _P, _P, _P]),
+    "b200gru_quantize_rows": (_I, [_P, _I, _I, _I, _P, _P, _P, _P]),
+    "b200gru_quantize_rows_backward": (_I, [_P, _P, _I, _I, _I, _P, _P]),
+    "b200gru_dense_q8_forward": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _QP, _QP, _P, _P, _P, _Z, _P]),
+    "b200gru_dense_q8_backward": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _QP, _QP, _P, _P, _P, _P,
+                                       _P, _Z, _P]),
     "b200gru_tc_gemm": (_I, [_GP, _P]),
     "b200gru_tc_gemm_splits": (_I, [_GP, _I]),
     "b200gru_split_bf16": (_I, [_P, _P, _Z, _Z, _I, _P, _I, _P]),
@@ -133,10 +138,42 @@ def launch_count() -> int:
     return int(load().b200gru_launch_count())
 
 
+def quantize_rows(W: torch.Tensor, bits: int = 8):
+    """Per-output-row symmetric fake-quant of ``W[rows, cols]``: ``(codes int8, scales, Wq)``."""
+    lib = load()
+    W = W.contiguous()
+    rows, cols = W.shape
+    codes = torch.empty((rows, cols), device=W.device, dtype=torch.int8)
+    scales = torch.empty((rows,), device=W.device, dtype=torch.float32)
+    Wq = torch.empty_like(W)
+    with torch.cuda.device(W.device):
+        stream = torch.cuda.current_stream().cuda_stream
+        rc = lib.b200gru_quantize_rows(_ptr(W), rows, cols, bits, _ptr(codes), _ptr(scales), _ptr(Wq),
+                                       ctypes.c_void_p(stream))
+    if rc:
+        _raise(rc, "quantize_rows")
+    return codes, scales, Wq
+
+
+def quantize_rows_backward(W: torch.Tensor, dWq: torch.Tensor, bits: int = 8) -> torch.Tensor:
+    """Gradient of :func:`quantize_rows` with respect to ``W`` (straight-through, dynamic scale)."""
+    lib = load()
+    W, dWq = W.contiguous(), dWq.contiguous()
+    rows, cols = W.shape
+    dW = torch.empty_like(W)
+    with torch.cuda.device(W.device):
+        stream = torch.cuda.current_stream().cuda_stream
+        rc = lib.b200gru_quantize_rows_backward(_ptr(W), _ptr(dWq), rows, cols, bits, _ptr(dW), ctypes.c_void_p(stream))
+    if rc:
+        _raise(rc, "quantize_rows_backward")
+    return dW
+
+
 def scan_forward(kind: str, gi, h0, W, bh, h_in_quant: Quant, h_out_quant: Quant, *, nblocks: int = 1,
-                 log2_hpad: int = 0, want_save: bool = False):
+                 log2_hpad: int = 0, want_save: bool = False, codes=None, scales=None):
     """Run the forward scan on the current stream of ``gi``'s device.
-    Returns ``(out, save)``; ``save`` is None unless asked for (and the kind has one)."""
+    Returns ``(out, save)``; ``save`` is None unless asked for (and the kind has one).
+    ``codes`` / ``scales`` (dense only): the int8 form of ``W`` from :func:`quantize_rows`."""
     lib = load()
     T, B, _ = gi.shape
     H = h0.shape[1]
@@ -149,16 +186,21 @@ def scan_forward(kind: str, gi, h0, W, bh, h_in_quant: Quant, h_out_quant: Quant
     qi, qo = _cquant(h_in_quant), _cquant(h_out_quant)
     with torch.cuda.device(gi.device):
         stream = torch.cuda.current_stream().cuda_stream
-        rc = lib.b200gru_scan_forward(ctypes.byref(shape), _ptr(gi), _ptr(h0), _ptr(W), _ptr(bh),
-                                      ctypes.byref(qi), ctypes.byref(qo), _ptr(out), _ptr(save), _ptr(ws),
-                                      0 if ws is None else ws.numel(), ctypes.c_void_p(stream))
+        if codes is not None:
+            rc = lib.b200gru_dense_q8_forward(_ptr(gi), _ptr(h0), _ptr(W), _ptr(codes), _ptr(scales), _ptr(bh), T, B, H,
+                                              ctypes.byref(qi), ctypes.byref(qo), _ptr(out), _ptr(save), _ptr(ws),
+                                              0 if ws is None else ws.numel(), ctypes.c_void_p(stream))
+        else:
+            rc = lib.b200gru_scan_forward(ctypes.byref(shape), _ptr(gi), _ptr(h0), _ptr(W), _ptr(bh),
+                                          ctypes.byref(qi), ctypes.byref(qo), _ptr(out), _ptr(save), _ptr(ws),
+                                          0 if ws is None else ws.numel(), ctypes.c_void_p(stream))
     if rc:
         _raise(rc, f"{kind} scan forward")
     return out, save
 
 
 def scan_backward(kind: str, gi, h0, W, bh, out, dout, save, h_in_quant: Quant, h_out_quant: Quant, *,
-                  nblocks: int = 1, log2_hpad: int = 0):
+                  nblocks: int = 1, log2_hpad: int = 0, codes=None, scales=None):
     """Run the backward scan.  Returns ``(dgi, dh0, dW, dbh)``."""
     lib = load()
     T, B, _ = gi.shape
@@ -172,10 +214,16 @@ def scan_backward(kind: str, gi, h0, W, bh, out, dout, save, h_in_quant: Quant, 
     qi, qo = _cquant(h_in_quant), _cquant(h_out_quant)
     with torch.cuda.device(gi.device):
         stream = torch.cuda.current_stream().cuda_stream
-        rc = lib.b200gru_scan_backward(ctypes.byref(shape), _ptr(gi), _ptr(h0), _ptr(W), _ptr(bh), _ptr(out),
-                                       _ptr(dout), _ptr(save), ctypes.byref(qi), ctypes.byref(qo), _ptr(dgi),
-                                       _ptr(dh0), _ptr(dW), _ptr(dbh), _ptr(ws),
-                                       0 if ws is None else ws.numel(), ctypes.c_void_p(stream))
+        if codes is not None:
+            rc = lib.b200gru_dense_q8_backward(_ptr(gi), _ptr(h0), _ptr(W), _ptr(codes), _ptr(scales), _ptr(bh),
+                                               _ptr(out), _ptr(dout), _ptr(save), T, B, H, ctypes.byref(qi),
+                                               ctypes.byref(qo), _ptr(dgi), _ptr(dh0), _ptr(dW), _ptr(dbh), _ptr(ws),
+                                               0 if ws is None else ws.numel(), ctypes.c_void_p(stream))
+        else:
+            rc = lib.b200gru_scan_backward(ctypes.byref(shape), _ptr(gi), _ptr(h0), _ptr(W), _ptr(bh), _ptr(out),
+                                           _ptr(dout), _ptr(save), ctypes.byref(qi), ctypes.byref(qo), _ptr(dgi),
+                                           _ptr(dh0), _ptr(dW), _ptr(dbh), _ptr(ws),
+                                           0 if ws is None else ws.numel(), ctypes.c_void_p(stream))
     if rc:
         _raise(rc, f"{kind} scan backward")
     return dgi, dh0, dW, dbh

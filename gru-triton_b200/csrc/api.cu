@@ -7,6 +7,7 @@
 
 #include "block_scan.cuh"
 #include "butterfly_scan.cuh"
+#include "tc_scan.cuh"
 
 namespace b200gru {
 
@@ -91,7 +92,8 @@ static size_t s_bytes(const Dims& d) { return align_up((size_t)4 * d.T * d.B * d
 static size_t wt_bytes(const Dims& d) {
   return align_up((size_t)3 * d.nb * d.Hb * transposed_row_bound(d.Hb) * sizeof(float), 256);
 }
-static bool step_path(const Dims& d) { return d.kind == B200GRU_DENSE && dense_step_path(d.B, d.H); }
+static size_t tc_max(size_t a, size_t b) { return a > b ? a : b; }
+static bool step_path(const Dims& d) { return d.kind == B200GRU_DENSE && tc::tc_dense_path(d.B, d.H); }
 
 // backward: 0 forward, 1 backward that recomputes the gates, 2 backward that is given `save`
 static size_t workspace_bytes(const Dims& d, int backward) {
@@ -99,10 +101,13 @@ static size_t workspace_bytes(const Dims& d, int backward) {
   switch (d.kind) {
     case B200GRU_DENSE:
     case B200GRU_MONARCH:
-      if (!backward)
-        return wt_bytes(d) + (step_path(d) ? dense_step_fwd_scratch_bytes(d.B, d.H) : 0);
-      return s_need + weight_grads_scratch_bytes(d.T, d.B, d.H, d.nb, d.Hb) +
-             (step_path(d) ? dense_step_bwd_scratch_bytes(d.B, d.H) : 0);
+      if (step_path(d))          // tensor-core path: its own scratch (weights as fp32 values)
+        return backward ? s_need + tc_max(tc::tc_dense_bwd_scratch_bytes(d.T, d.B, d.H, false),
+                                          tc::tc_dense_bwd_scratch_bytes(d.T, d.B, d.H, true))
+                        : tc_max(tc::tc_dense_fwd_scratch_bytes(d.T, d.B, d.H, false),
+                                 tc::tc_dense_fwd_scratch_bytes(d.T, d.B, d.H, true));
+      if (!backward) return wt_bytes(d);
+      return s_need + weight_grads_scratch_bytes(d.T, d.B, d.H, d.nb, d.Hb);
     case B200GRU_DIAGONAL:
       return backward ? diag_bwd_workspace_bytes(d.T, d.B, d.H) : 0;
     case B200GRU_BUTTERFLY: {
@@ -142,9 +147,11 @@ size_t b200gru_save_bytes(const b200gru_shape* shape) {
   return (size_t)4 * d.T * d.B * d.H * sizeof(float);
 }
 
-int b200gru_scan_forward(const b200gru_shape* shape, const float* gi, const float* h0, const float* W,
-                         const float* bh, const b200gru_quant* q_in, const b200gru_quant* q_out, float* out,
-                         float* save, void* workspace, size_t workspace_bytes_, void* stream) {
+// codes / scales: optional int8 form of a dense W (W then holds codes * scales)
+static int scan_forward_impl(const b200gru_shape* shape, const float* gi, const float* h0, const float* W,
+                             const signed char* codes, const float* scales,
+                             const float* bh, const b200gru_quant* q_in, const b200gru_quant* q_out, float* out,
+                             float* save, void* workspace, size_t workspace_bytes_, void* stream) {
   Dims d;
   if (!parse_shape(shape, &d)) return B200GRU_INVALID_ARGUMENT;
   if (!gi || !h0 || !W || !bh || !out) return B200GRU_INVALID_ARGUMENT;
@@ -162,12 +169,8 @@ int b200gru_scan_forward(const b200gru_shape* shape, const float* gi, const floa
     case B200GRU_DENSE:
     case B200GRU_MONARCH: {
       if (step_path(d)) {
-        float* Wt = static_cast<float*>(workspace);
-        float* scratch = reinterpret_cast<float*>(static_cast<char*>(workspace) + wt_bytes(d));
-        const int WtR = ((d.H + 3) & ~3) + 4;
-        int rc = launch_transpose_weights(W, Wt, 1, d.H, WtR, d.gate_stride, d.block_stride, st);
-        if (rc) return rc;
-        return launch_dense_step_forward(gi, h0, Wt, WtR, bh, out, save, scratch, d.T, d.B, d.H, qi, qo, st);
+        const tc::TcWeights w = {W, codes, scales};
+        return tc::launch_tc_dense_forward(gi, h0, w, bh, out, save, workspace, d.T, d.B, d.H, qi, qo, st);
       }
       BlockScanConfig cfg;
       if (!choose_block_config(true, d.B, d.Hb, d.nb, &cfg)) return B200GRU_UNSUPPORTED;
@@ -197,10 +200,18 @@ int b200gru_scan_forward(const b200gru_shape* shape, const float* gi, const floa
   return B200GRU_INVALID_ARGUMENT;
 }
 
-int b200gru_scan_backward(const b200gru_shape* shape, const float* gi, const float* h0, const float* W,
-                          const float* bh, const float* out, const float* dout, const float* save,
-                          const b200gru_quant* q_in, const b200gru_quant* q_out, float* dgi, float* dh0,
-                          float* dW, float* dbh, void* workspace, size_t workspace_bytes_, void* stream) {
+int b200gru_scan_forward(const b200gru_shape* shape, const float* gi, const float* h0, const float* W,
+                         const float* bh, const b200gru_quant* q_in, const b200gru_quant* q_out, float* out,
+                         float* save, void* workspace, size_t workspace_bytes_, void* stream) {
+  return scan_forward_impl(shape, gi, h0, W, nullptr, nullptr, bh, q_in, q_out, out, save, workspace, workspace_bytes_,
+                           stream);
+}
+
+static int scan_backward_impl(const b200gru_shape* shape, const float* gi, const float* h0, const float* W,
+                              const signed char* codes, const float* scales,
+                              const float* bh, const float* out, const float* dout, const float* save,
+                              const b200gru_quant* q_in, const b200gru_quant* q_out, float* dgi, float* dh0,
+                              float* dW, float* dbh, void* workspace, size_t workspace_bytes_, void* stream) {
   Dims d;
   if (!parse_shape(shape, &d)) return B200GRU_INVALID_ARGUMENT;
   if (!gi || !h0 || !W || !bh || !out || !dout || !dgi || !dh0 || !dW || !dbh) return B200GRU_INVALID_ARGUMENT;
@@ -237,11 +248,9 @@ int b200gru_scan_backward(const b200gru_shape* shape, const float* gi, const flo
         S = S_ws;
       }
       if (step_path(d)) {
-        float* step_ws = reinterpret_cast<float*>(ws + s_off + weight_grads_scratch_bytes(d.T, d.B, d.H, d.nb, d.Hb));
-        int rc = launch_dense_step_backward(h0, W, out, S, dout, dgi, dh0, step_ws, d.T, d.B, d.H, qi, qo, st);
-        if (rc) return rc;
-        g.S = const_cast<float*>(S);
-        return launch_weight_grads(g, st);
+        const tc::TcWeights w = {W, codes, scales};
+        return tc::launch_tc_dense_backward(h0, w, out, S, dout, dgi, dh0, dW, dbh, ws + s_off, d.T, d.B, d.H, qi, qo,
+                                            st);
       }
       BlockScanConfig cfg;
       if (!choose_block_config(false, d.B, d.Hb, d.nb, &cfg)) return B200GRU_UNSUPPORTED;
@@ -286,6 +295,14 @@ int b200gru_scan_backward(const b200gru_shape* shape, const float* gi, const flo
     }
   }
   return B200GRU_INVALID_ARGUMENT;
+}
+
+int b200gru_scan_backward(const b200gru_shape* shape, const float* gi, const float* h0, const float* W,
+                          const float* bh, const float* out, const float* dout, const float* save,
+                          const b200gru_quant* q_in, const b200gru_quant* q_out, float* dgi, float* dh0,
+                          float* dW, float* dbh, void* workspace, size_t workspace_bytes_, void* stream) {
+  return scan_backward_impl(shape, gi, h0, W, nullptr, nullptr, bh, out, dout, save, q_in, q_out, dgi, dh0, dW, dbh,
+                            workspace, workspace_bytes_, stream);
 }
 
 // ---- per-kind conveniences ---------------------------------------------------
@@ -364,6 +381,37 @@ int b200gru_butterfly_backward(const float* gi, const float* h0, const float* tw
   const b200gru_shape s = mk_shape(B200GRU_BUTTERFLY, T, B, H, nblocks, log2_hpad);
   return b200gru_scan_backward(&s, gi, h0, twiddles, bh_cat, out, dout, save, q_in, q_out, dgi, dh0, dtwiddles,
                                dbh, workspace, workspace_bytes_, stream);
+}
+
+int b200gru_quantize_rows(const float* W, int rows, int cols, int bits, signed char* codes, float* scales, float* Wq,
+                          void* stream) {
+  return tc::launch_quantize_rows(W, rows, cols, bits, codes, scales, Wq, static_cast<cudaStream_t>(stream));
+}
+
+int b200gru_quantize_rows_backward(const float* W, const float* dWq, int rows, int cols, int bits, float* dW,
+                                   void* stream) {
+  return tc::launch_quantize_rows_backward(W, dWq, rows, cols, bits, dW, static_cast<cudaStream_t>(stream));
+}
+
+int b200gru_dense_q8_forward(const float* gi, const float* h0, const float* Wq, const signed char* codes,
+                             const float* scales, const float* bh_cat, int T, int B, int H,
+                             const b200gru_quant* q_in, const b200gru_quant* q_out, float* out, float* save,
+                             void* workspace, size_t workspace_bytes_, void* stream) {
+  if (!codes || !scales) return B200GRU_INVALID_ARGUMENT;
+  const b200gru_shape s = mk_shape(B200GRU_DENSE, T, B, H, 1, 0);
+  return scan_forward_impl(&s, gi, h0, Wq, codes, scales, bh_cat, q_in, q_out, out, save, workspace, workspace_bytes_,
+                           stream);
+}
+
+int b200gru_dense_q8_backward(const float* gi, const float* h0, const float* Wq, const signed char* codes,
+                              const float* scales, const float* bh_cat, const float* out, const float* dout,
+                              const float* save, int T, int B, int H, const b200gru_quant* q_in,
+                              const b200gru_quant* q_out, float* dgi, float* dh0, float* dWq, float* dbh,
+                              void* workspace, size_t workspace_bytes_, void* stream) {
+  if (!codes || !scales) return B200GRU_INVALID_ARGUMENT;
+  const b200gru_shape s = mk_shape(B200GRU_DENSE, T, B, H, 1, 0);
+  return scan_backward_impl(&s, gi, h0, Wq, codes, scales, bh_cat, out, dout, save, q_in, q_out, dgi, dh0, dWq, dbh,
+                            workspace, workspace_bytes_, stream);
 }
 
 unsigned long long b200gru_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }

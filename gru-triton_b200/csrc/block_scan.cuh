@@ -76,15 +76,4 @@ int launch_recompute_gates(const BlockGemmArgs& a, cudaStream_t st);
 size_t weight_grads_scratch_bytes(int T, int B, int H, int nb, int Hb);
 int launch_weight_grads(const BlockGemmArgs& a, cudaStream_t st);
 
-// dense_step.cu -- dense scan at GEMM-sized batch, one launch per time step.
-bool dense_step_path(int B, int H);
-size_t dense_step_fwd_scratch_bytes(int B, int H);
-size_t dense_step_bwd_scratch_bytes(int B, int H);
-int launch_dense_step_forward(const float* gi, const float* h0, const float* Wt, int WtR, const float* bh, float* out,
-                              float* save, float* scratch, int T, int B, int H, Quant qin, Quant qout,
-                              cudaStream_t st);
-int launch_dense_step_backward(const float* h0, const float* W, const float* out, const float* S, const float* dout,
-                               float* dgi, float* dh0, float* scratch, int T, int B, int H, Quant qin, Quant qout,
-                               cudaStream_t st);
-
 }  // namespace b200gru

@@ -25,6 +25,7 @@ bool to_internal(const b200gru_gemm_args* a, tc::TcGemm* g) {
   g->split_k = a->split_k < 1 ? 1 : a->split_k;
   g->tile_n = a->tile_n;
   g->chunk_kb = a->chunk_kblocks;
+  g->accumulate = a->accumulate;
   g->alpha = a->alpha; g->row_scale = a->row_scale; g->col_scale = a->col_scale; g->bias = a->bias;
   g->C = a->C; g->ldc = a->ldc; g->split_stride = a->split_stride;
   return true;

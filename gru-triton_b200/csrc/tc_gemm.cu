@@ -47,6 +47,7 @@ struct GemmParams {
   int pa[TC_MAX_PAIRS], pb[TC_MAX_PAIRS];
   int stages;
   int chunk_kb;                              // k-blocks summed in tensor memory before a drain
+  int accumulate;
   float alpha;
   const float* row_scale;
   const float* col_scale;
@@ -223,6 +224,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             if (p.bias != nullptr) r = r + __ldg(p.bias + n + e);
             o[e] = r;
           }
+          if (p.accumulate) {
+            const float4 old = *reinterpret_cast<const float4*>(crow + n);
+            o[0] += old.x; o[1] += old.y; o[2] += old.z; o[3] += old.w;
+          }
           *reinterpret_cast<float4*>(crow + n) = make_float4(o[0], o[1], o[2], o[3]);
         }
       }
@@ -363,13 +368,19 @@ int tc_read_status(int reset) {
 
 int tc_gemm_tile_n(const TcGemm& g) {
   if (g.tile_n == 64 || g.tile_n == 128 || g.tile_n == 256) return g.tile_n;
-  // widest tile whose two-stage ring fits; narrower when N is small
+  // Fewest waves over the 148 SMs, weighted by a tile's cost (a fixed part for the A operand and
+  // the pipeline fill plus a part proportional to the tile width); the ring needs two stages.
+  const int splits = g.split_k < 1 ? 1 : g.split_k;
+  int best = 0;
+  long long best_cost = 0;
   for (int bn = 256; bn >= 64; bn >>= 1) {
-    if (bn > 64 && g.N <= bn / 2) continue;
     const int stage = g.a_planes * 16384 + g.b_planes * bn * 128;
-    if (2 * stage <= TC_SMEM_BUDGET) return bn;
+    if (2 * stage > TC_SMEM_BUDGET) continue;
+    const long long tiles = (long long)cdiv(g.M, BM) * cdiv(g.N, bn) * splits;
+    const long long cost = ((tiles + 147) / 148) * (128 + bn);
+    if (best == 0 || cost < best_cost) { best = bn; best_cost = cost; }
   }
-  return 0;
+  return best;
 }
 
 int launch_tc_gemm(const TcGemm& g, cudaStream_t st) {
@@ -406,6 +417,7 @@ int launch_tc_gemm(const TcGemm& g, cudaStream_t st) {
   if (g.chunk_kb > 0) p.chunk_kb = g.chunk_kb;
   else if (i8) p.chunk_kb = p.kb_per_split;                   // int32 accumulation is exact
   else p.chunk_kb = (32 / (4 * g.npairs)) > 0 ? 32 / (4 * g.npairs) : 1;   // at most 32 accumulation steps per chunk
+  p.accumulate = g.accumulate;
   p.alpha = g.alpha; p.row_scale = g.row_scale; p.col_scale = g.col_scale; p.bias = g.bias;
   p.C = g.C; p.ldc = g.ldc; p.split_stride = g.split_stride;
 

@@ -32,6 +32,7 @@ struct TcGemm {
   int split_k;
   int tile_n;                  // 0 = choose; else 64 / 128 / 256
   int chunk_kb;                // 0 = choose; k-blocks accumulated in tensor memory between drains
+  int accumulate;              // != 0: add the result to what C already holds
   float alpha;
   const float* row_scale;
   const float* col_scale;

@@ -5,7 +5,10 @@ same constructor keywords, ``forward(x, h0=None) -> (out, h_T)``,
 ``calibrate()`` / ``freeze()``.  With ``use_triton`` in effect (the keyword keeps
 the reference's name; there is no Triton here) a CUDA input takes the fast path:
 one GEMM for the input projection of the whole sequence, then ONE persistent
-CUDA scan over all T steps (diagonal / monarch / butterfly hidden side).  CPU
+CUDA scan over all T steps.  Eligible: diagonal / monarch / butterfly hidden
+side with fused gates, as in the reference, and -- an extension the reference
+does not have (its dense layers always step in Python, gru_layer.py:109-124) --
+fully dense layers with fused gates and no gate-activation quantizer.  CPU
 tensors, ineligible layers and ``calibrate()`` run the per-step loop.
 """
 
@@ -17,7 +20,7 @@ import torch
 import torch.nn as nn
 
 from .gru_cell import GateLayout, GRUCellQuant
-from .quantizers import FakeQuantize, FakeQuantizePerTensor, QuantRecipe
+from .quantizers import FakeQuantize, FakeQuantizePerChannel, FakeQuantizePerTensor, Identity, QuantRecipe
 from .structure import StructureConfig
 
 _FAST_KINDS = ("diagonal", "monarch", "butterfly")
@@ -50,15 +53,22 @@ class GRULayer(nn.Module):
         self.hidden_size, self.batch_first, self.pre_batch_input = hidden_size, batch_first, pre_batch_input
 
         kind = structure_hidden.kind if structure_hidden is not None else None
-        self._fast_dispatch_eligible = kind in _FAST_KINDS and gate_layout == "fused"
-        self._dispatch_kind = kind if self._fast_dispatch_eligible else None
+        if kind in (None, "dense"):
+            kind = "dense"
+            eligible = (not self.cell.is_structured and gate_layout == "fused" and
+                        all(isinstance(getattr(self.cell, f"quant_gate_{g}"), Identity) for g in "rzn"))
+        else:
+            eligible = kind in _FAST_KINDS and gate_layout == "fused"
+        self._fast_dispatch_eligible = eligible
+        self._dispatch_kind = kind if eligible else None
         if use_triton == "auto":
-            self.use_triton = self._fast_dispatch_eligible
+            self.use_triton = eligible
         else:
             self.use_triton = bool(use_triton)
-            if self.use_triton and not self._fast_dispatch_eligible:
-                raise ValueError("use_triton=True requires structure_hidden.kind in "
-                                 "{'diagonal', 'monarch', 'butterfly'} and gate_layout='fused'.")
+            if self.use_triton and not eligible:
+                raise ValueError("use_triton=True requires gate_layout='fused' and either structure_hidden.kind in "
+                                 "{'diagonal', 'monarch', 'butterfly'} or a fully dense layer without gate-"
+                                 "activation quantizers.")
 
         if self.cell.is_structured:
             body = self.cell.step_structured
@@ -97,19 +107,58 @@ class GRULayer(nn.Module):
         out = torch.stack(outs, dim=0)
         return (out.transpose(0, 1) if self.batch_first else out), h
 
+    def _weight_bits_on_device(self, side: str):
+        """Bit width if the three weight quantizers of a side are the per-output-row symmetric
+        dynamic int<=8 kind the weight-prep kernel implements, 32 if they are identities, else None
+        (then the quantizer modules themselves run, as in the per-step path)."""
+        qs = [getattr(self.cell, f"quant_W_{side}{g}") for g in "rzn"]
+        if all(isinstance(q, Identity) for q in qs):
+            return 32
+        c = qs[0].config
+        if (all(isinstance(q, FakeQuantizePerChannel) for q in qs) and c.axis == 0 and c.symmetric and
+                c.mode == "dynamic" and c.bits <= 8 and
+                all(q.config.bits == c.bits and q.config.mode == "dynamic" and q.config.symmetric for q in qs)):
+            return int(c.bits)
+        return None
+
+    def _input_projection_fast(self, x):
+        """``gi[T,B,3H]`` on the tensor cores (fp32-accurate split products)."""
+        from . import tc
+        cell = self.cell
+        bits = self._weight_bits_on_device("i")
+        xq = cell.quant_x(x)
+        I = cell.input_size
+        if bits is None or I % 8 or self.hidden_size % 8 or xq.dtype != torch.float32:
+            Wi_cat, bi_cat = cell.quantize_input_weights()
+            return nn.functional.linear(xq, Wi_cat, bi_cat)
+        Wi_raw = torch.cat([getattr(cell, f"W_i{g}") for g in "rzn"], dim=0)
+        return tc.linear(xq, Wi_raw, cell._cat_bias("i"), weight_bits=bits)
+
     def _forward_fast_dispatch(self, x, h0):
         """Input projection hoisted to one GEMM, then the persistent CUDA scan
         (gru_layer.py:234-302)."""
         cell = self.cell
         if cell._input_dense:
-            Wi_cat, bi_cat = cell.quantize_input_weights()
-            gi = nn.functional.linear(cell.quant_x(x), Wi_cat, bi_cat)
+            gi = self._input_projection_fast(x)
         else:
             gi = cell.structured_input_projection(x)
         quant = dict(h_in_quant=_extract_h_quant_params(cell.quant_h_in),
                      h_out_quant=_extract_h_quant_params(cell.quant_h_out))
 
-        if self._dispatch_kind == "diagonal":
+        if self._dispatch_kind == "dense":
+            from . import tc
+            from .scan import gru_scan_persistent
+            bits = self._weight_bits_on_device("h")
+            bh_cat = cell._cat_bias("h")
+            if bh_cat is None:
+                bh_cat = gi.new_zeros(3 * self.hidden_size)
+            if bits is not None and bits <= 8 and self.hidden_size % 4 == 0:
+                Wh_raw = torch.cat([getattr(cell, f"W_h{g}") for g in "rzn"], dim=0)
+                out = tc.gru_scan_dense_q8(gi, h0, Wh_raw, bh_cat, weight_bits=bits, **quant)
+            else:
+                Wh_cat = torch.cat([getattr(cell, f"quant_W_h{g}")(getattr(cell, f"W_h{g}")) for g in "rzn"], dim=0)
+                out = gru_scan_persistent(gi, h0, Wh_cat, bh_cat, **quant)
+        elif self._dispatch_kind == "diagonal":
             from .scan_diagonal import extract_diagonal_factors, gru_scan_diagonal
             out = gru_scan_diagonal(gi, h0, *extract_diagonal_factors(cell), **quant)
         elif self._dispatch_kind == "monarch":

@@ -1,16 +1,22 @@
 """Tensor-core products of the GRU path (tcgen05 GEMM core of ``libb200gru.so``).
 
-``split_bf16`` turns an fp32 tensor into bf16 planes (hi, mid, lo); ``gemm`` multiplies two
-plane sets, ``C = alpha * row_scale * col_scale * sum_pairs A_i @ B_j^T + bias``, with fp32
-(bf16 planes) or exact int32 (int8 codes) accumulation.  These stand in for the reference's
-``F.linear`` input projection (src/gru_qat/gru_layer.py:251-253) and its ``tl.dot`` tiles
-(src/gru_qat/triton_kernels/scan.py:153-155, 521-616).  CUDA tensors only; no fallback.
+* ``split_bf16`` / ``gemm``: operand preparation and the raw product
+  ``C = alpha * row_scale * col_scale * sum_pairs A_i @ B_j^T + bias`` with fp32 (bf16 planes)
+  or exact int32 (int8 codes) accumulation.
+* ``linear``: the input projection ``gi = x @ Wi^T + bi`` of a whole sequence and its gradients,
+  row-chunked so that operand planes stay small; with ``weight_bits <= 8`` the weights are
+  fake-quantised per output row on the device and multiplied as exact integer codes.
+  Stands in for ``F.linear`` at src/gru_qat/gru_layer.py:251-253 / gru_cell.py:410-435.
+* ``gru_scan_dense_q8``: the dense scan on int8 weights (weight fake-quant of
+  src/gru_qat/gru_cell.py:239-271 fused into a weight-prep kernel that emits codes and scales).
+
+CUDA tensors only; there is no fallback.
 """
 
 from __future__ import annotations
 
 import ctypes
-from typing import Optional, Sequence, Tuple
+from typing import Any, Optional, Sequence, Tuple
 
 import torch
 
@@ -18,23 +24,28 @@ from . import _lib
 
 # plane cross products, most significant first
 PAIRS_EXACT_B = {1: [(0, 0)], 2: [(0, 0), (1, 0)], 3: [(0, 0), (1, 0), (2, 0)]}
+PAIRS_EXACT_A = {1: [(0, 0)], 2: [(0, 0), (0, 1)], 3: [(0, 0), (0, 1), (0, 2)]}
 PAIRS_FULL = [(0, 0), (0, 1), (1, 0), (0, 2), (1, 1), (2, 0)]          # error about 2^-24 of |a||b|
 PAIRS_FAST = [(0, 0), (0, 1), (1, 0)]                                  # error about 2^-17 of |a||b|
+
+ROW_CHUNK = 32768          # rows of x handled per operand-preparation + GEMM round
 
 
 def _stream(t: torch.Tensor):
     return ctypes.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
 
 
-def split_bf16(x: torch.Tensor, planes: int = 3, col_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """``[planes, *x.shape]`` bf16 with ``sum(planes) == x * col_scale`` (to 8 bits per plane)."""
+def split_bf16(x: torch.Tensor, planes: int = 3, col_scale: Optional[torch.Tensor] = None,
+               out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``[planes, *x.shape]`` bf16 with ``sum(planes) == x * col_scale`` (8 mantissa bits per plane)."""
     if not x.is_cuda or x.dtype != torch.float32:
         raise ValueError("split_bf16 needs a CUDA float32 tensor")
     x = x.contiguous()
     n = x.numel()
     if n % 4:
         raise ValueError("element count must be a multiple of 4")
-    out = torch.empty((planes,) + tuple(x.shape), device=x.device, dtype=torch.bfloat16)
+    if out is None:
+        out = torch.empty((planes,) + tuple(x.shape), device=x.device, dtype=torch.bfloat16)
     ncols = x.shape[-1] if col_scale is not None else 0
     with torch.cuda.device(x.device):
         rc = _lib.load().b200gru_split_bf16(_lib._ptr(x), _lib._ptr(out), n, n, planes, _lib._ptr(col_scale),
@@ -48,10 +59,13 @@ def gemm(A: torch.Tensor, B: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
          pairs: Optional[Sequence[Tuple[int, int]]] = None, alpha: float = 1.0,
          row_scale: Optional[torch.Tensor] = None, col_scale: Optional[torch.Tensor] = None,
          bias: Optional[torch.Tensor] = None, split_k: int = 1, tile_n: int = 0, chunk_kblocks: int = 0,
-         out: Optional[torch.Tensor] = None) -> torch.Tensor:
+         out: Optional[torch.Tensor] = None, accumulate: bool = False, reduce_splits: bool = True) -> torch.Tensor:
     """``A``: ``[planes, M, K]`` (or ``[planes, K, M]`` with ``a_mn``); ``B``: ``[planes, N, K]``
-    (or ``[planes, K, N]`` with ``b_mn``); bf16 or int8, contiguous.  Returns fp32 ``[M, N]``
-    (``split_k`` partial results are summed in order)."""
+    (or ``[planes, K, N]`` with ``b_mn``); bf16 or int8, contiguous.  Returns fp32 ``[M, N]``.
+
+    ``split_k > 1`` computes that many partial products over slices of K: they are summed in order
+    unless ``reduce_splits`` is False, in which case ``out`` (``[splits, M, N]``) receives (or,
+    with ``accumulate``, is incremented by) the partial results and is returned as it is."""
     if A.dim() == 2:
         A = A[None]
     if B.dim() == 2:
@@ -76,7 +90,7 @@ def gemm(A: torch.Tensor, B: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     g.npairs = len(pairs)
     for q, (i, j) in enumerate(pairs):
         g.pair_a[q], g.pair_b[q] = i, j
-    g.tile_n, g.alpha, g.chunk_kblocks = tile_n, alpha, chunk_kblocks
+    g.tile_n, g.alpha, g.chunk_kblocks, g.accumulate = tile_n, alpha, chunk_kblocks, int(accumulate)
     g.row_scale = None if row_scale is None else row_scale.data_ptr()
     g.col_scale = None if col_scale is None else col_scale.data_ptr()
     g.bias = None if bias is None else bias.data_ptr()
@@ -84,16 +98,20 @@ def gemm(A: torch.Tensor, B: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     g.split_k = 1
     splits = lib.b200gru_tc_gemm_splits(ctypes.byref(g), split_k) if split_k > 1 else 1
     g.split_k = splits
-    if splits > 1:
+    if splits > 1 and not (out is not None and not reduce_splits):
         C = torch.empty((splits, M, N), device=A.device, dtype=torch.float32)
+    elif out is not None:
+        C = out
+        if not C.is_contiguous() or C.dtype != torch.float32 or C.numel() < splits * M * N:
+            raise ValueError("out must be a contiguous float32 tensor of the result's size")
     else:
-        C = out if out is not None else torch.empty((M, N), device=A.device, dtype=torch.float32)
+        C = torch.empty((M, N), device=A.device, dtype=torch.float32)
     g.C, g.ldc, g.split_stride = C.data_ptr(), N, M * N
     with torch.cuda.device(A.device):
         rc = lib.b200gru_tc_gemm(ctypes.byref(g), _stream(A))
     if rc:
         _lib._raise(rc, "tc gemm")
-    if splits > 1:
+    if splits > 1 and reduce_splits:
         res = C[0]
         for s in range(1, splits):
             res = res + C[s]
@@ -102,3 +120,131 @@ def gemm(A: torch.Tensor, B: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
             return out
         return res
     return C
+
+
+def gemm_splits(M: int, N: int, K: int, wanted: int) -> int:
+    """Number of K slices a bf16 product of this shape uses when ``wanted`` are asked for."""
+    g = _lib.CGemmArgs()
+    g.dtype, g.M, g.N, g.K, g.a_planes, g.b_planes, g.npairs = 0, M, N, K, 1, 1, 1
+    return int(_lib.load().b200gru_tc_gemm_splits(ctypes.byref(g), wanted))
+
+
+# ----------------------------------------------------------------------------------------------
+# input projection
+# ----------------------------------------------------------------------------------------------
+
+class _LinearFunction(torch.autograd.Function):
+    """``y[R,N] = x[R,I] @ fq(W)[N,I]^T + bias`` with fp32-accurate tensor-core products."""
+
+    @staticmethod
+    def forward(ctx: Any, x, W, bias, weight_bits: int):
+        R, I = x.shape
+        N = W.shape[0]
+        if weight_bits <= 8:
+            codes, scales, _ = _lib.quantize_rows(W, weight_bits)
+            Bop, col_scale, pairs = codes.to(torch.bfloat16)[None], scales, PAIRS_EXACT_B[3]
+        else:
+            Bop, col_scale, pairs = split_bf16(W), None, PAIRS_FULL
+        y = torch.empty((R, N), device=x.device, dtype=torch.float32)
+        for r0 in range(0, R, ROW_CHUNK):
+            r1 = min(R, r0 + ROW_CHUNK)
+            gemm(split_bf16(x[r0:r1]), Bop, pairs=pairs, col_scale=col_scale, bias=bias, out=y[r0:r1])
+        ctx.save_for_backward(x, W)
+        ctx.weight_bits, ctx.has_bias = weight_bits, bias is not None
+        ctx.col_scale, ctx.Bop = col_scale, Bop
+        return y
+
+    @staticmethod
+    def backward(ctx: Any, dy):
+        x, W = ctx.saved_tensors
+        dy = dy.contiguous()
+        R, I = x.shape
+        N = W.shape[0]
+        need_x, need_w, need_b = ctx.needs_input_grad[0], ctx.needs_input_grad[1], ctx.needs_input_grad[2] and ctx.has_bias
+        dx = torch.empty_like(x) if need_x else None
+        dWq = None
+        if need_w:
+            chunk_rows = min(R, ROW_CHUNK)
+            # enough K slices to cover the GPU with (N/128) x (I/256) tiles
+            tiles = -(-N // 128) * -(-I // 256)
+            splits = gemm_splits(N, I, chunk_rows, 1 if tiles >= 120 else -(-280 // tiles))
+            dWq = torch.zeros((splits, N, I), device=x.device, dtype=torch.float32)
+        for r0 in range(0, R, ROW_CHUNK):
+            r1 = min(R, r0 + ROW_CHUNK)
+            dyp = split_bf16(dy[r0:r1])
+            if need_w:
+                xp = split_bf16(x[r0:r1])
+                k_splits = gemm_splits(N, I, r1 - r0, dWq.shape[0])
+                gemm(dyp, xp, a_mn=True, b_mn=True, pairs=PAIRS_FULL, split_k=k_splits, out=dWq, accumulate=True,
+                     reduce_splits=False)
+            if need_x:
+                # dx = dy @ fq(W): W rows are the contraction index (MN-major B)
+                if ctx.weight_bits <= 8:
+                    dys = split_bf16(dy[r0:r1], col_scale=ctx.col_scale)
+                    gemm(dys, ctx.Bop, b_mn=True, pairs=PAIRS_EXACT_B[3], out=dx[r0:r1])
+                else:
+                    gemm(dyp, ctx.Bop, b_mn=True, pairs=PAIRS_FULL, out=dx[r0:r1])
+        dW = None
+        if need_w:
+            dWq = dWq.sum(dim=0) if dWq.shape[0] > 1 else dWq[0]
+            dW = _lib.quantize_rows_backward(W, dWq, ctx.weight_bits) if ctx.weight_bits <= 8 else dWq
+        db = dy.sum(dim=0) if need_b else None
+        return dx, dW, db, None
+
+
+def linear(x: torch.Tensor, W: torch.Tensor, bias: Optional[torch.Tensor] = None, *, weight_bits: int = 32):
+    """``x[..., I] @ fq(W)[N, I]^T + bias`` -> ``[..., N]`` (fp32).  ``weight_bits <= 8``: ``W`` is
+    fake-quantised per output row (dynamic symmetric scale) on the device, as the reference's
+    per-channel weight quantizer does, and multiplied as integer codes."""
+    if not (x.is_cuda and W.is_cuda) or x.dtype != torch.float32 or W.dtype != torch.float32:
+        raise ValueError("linear needs CUDA float32 tensors")
+    if x.shape[-1] != W.shape[1] or x.shape[-1] % 8 or W.shape[0] % 8:
+        raise ValueError("linear needs x[..., I] and W[N, I] with I % 8 == 0 and N % 8 == 0")
+    lead = x.shape[:-1]
+    y = _LinearFunction.apply(x.reshape(-1, x.shape[-1]).contiguous(), W.contiguous(), bias, int(weight_bits))
+    return y.reshape(*lead, W.shape[0])
+
+
+# ----------------------------------------------------------------------------------------------
+# dense scan on int8 weights
+# ----------------------------------------------------------------------------------------------
+
+class GRUScanDenseQ8Function(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx: Any, gi, h0, Wh_cat, bh_cat, weight_bits, h_in_quant, h_out_quant):
+        gi, h0, Wh_cat, bh_cat = (t.contiguous() for t in (gi, h0, Wh_cat, bh_cat))
+        codes, scales, Wq = _lib.quantize_rows(Wh_cat, weight_bits)
+        want = any(ctx.needs_input_grad[:4])
+        out, save = _lib.scan_forward("dense", gi, h0, Wq, bh_cat, h_in_quant, h_out_quant, want_save=want,
+                                      codes=codes, scales=scales)
+        ctx.save_for_backward(gi, h0, Wh_cat, bh_cat, out, Wq, codes, scales, *([save] if save is not None else []))
+        ctx.has_save = save is not None
+        ctx.quant, ctx.weight_bits = (h_in_quant, h_out_quant), weight_bits
+        return out
+
+    @staticmethod
+    def backward(ctx: Any, dout):
+        gi, h0, Wh_cat, bh_cat, out, Wq, codes, scales = ctx.saved_tensors[:8]
+        save = ctx.saved_tensors[8] if ctx.has_save else None
+        dgi, dh0, dWq, dbh = _lib.scan_backward("dense", gi, h0, Wq, bh_cat, out, dout.contiguous(), save,
+                                                ctx.quant[0], ctx.quant[1], codes=codes, scales=scales)
+        dW = _lib.quantize_rows_backward(Wh_cat, dWq, ctx.weight_bits)
+        return dgi, dh0, dW, dbh, None, None, None
+
+
+def gru_scan_dense_q8(gi, h0, Wh_cat, bh_cat, *, weight_bits: int = 8, h_in_quant=None, h_out_quant=None):
+    """Differentiable dense scan on the RAW fp32 weights ``Wh_cat[3H,H]``: the per-output-row
+    int8 fake-quant (dynamic symmetric scale) happens on the device and its straight-through
+    gradient is applied in the backward.  Equals ``gru_scan_persistent`` on
+    ``GRUCellQuant.quantize_weights().Wh_cat`` of a layer with an int8 per-channel weight recipe."""
+    from ._scan_common import check_quant, common_shapes, require_cuda, require_f32
+    require_cuda(gi=gi, h0=h0, Wh_cat=Wh_cat, bh_cat=bh_cat)
+    require_f32(gi=gi, h0=h0, Wh_cat=Wh_cat, bh_cat=bh_cat)
+    T, B, H = common_shapes(gi, h0, bh_cat)
+    if tuple(Wh_cat.shape) != (3 * H, H):
+        raise ValueError(f"Wh_cat shape must be (3H, H)=({3 * H}, {H}); got {tuple(Wh_cat.shape)}")
+    if H % 4:
+        raise ValueError("int8 weight preparation needs H % 4 == 0")
+    check_quant("h_in_quant", h_in_quant)
+    check_quant("h_out_quant", h_out_quant)
+    return GRUScanDenseQ8Function.apply(gi, h0, Wh_cat, bh_cat, int(weight_bits), h_in_quant, h_out_quant)

@@ -151,6 +151,38 @@ int b200gru_butterfly_backward(const float* gi, const float* h0, const float* tw
                                float* dgi, float* dh0, float* dtwiddles, float* dbh,
                                void* workspace, size_t workspace_bytes, void* stream);
 
+/* ---- dense layers with int8 weights ------------------------------------------------------------
+ * Weight preparation: per-output-row symmetric fake-quant of W[rows, cols]
+ * (s_r = max(max_k |W[r,k]|, 1e-8) / qmax, q = clamp(rint(W / s_r), -qmax, qmax), qmax = 2^(bits-1) - 1,
+ * 2 <= bits <= 8, cols % 4 == 0): emits the int8 codes, the row scales and (Wq may be NULL) the
+ * fake-quantised values q * s_r.  Replaces the per-gate FakeQuantizePerChannel(axis=0) calls of
+ * GRUCellQuant.quantize_weights / quantize_input_weights (src/gru_qat/gru_cell.py:239-299;
+ * src/gru_qat/quantizers.py:118-134, 177-189) for weights stacked r,z,n along the rows. */
+int b200gru_quantize_rows(const float* W, int rows, int cols, int bits, signed char* codes, float* scales,
+                          float* Wq, void* stream);
+/* Its gradient, dW from dWq, as autograd derives it from fake_quant_ste with a dynamic scale
+ * (src/gru_qat/ste.py:65-95): the clamp mask on dWq plus the term that reaches the row's largest
+ * element through s_r. */
+int b200gru_quantize_rows_backward(const float* W, const float* dWq, int rows, int cols, int bits, float* dW,
+                                   void* stream);
+
+/* Dense scan whose hidden weights come from b200gru_quantize_rows: Wq (fp32 values), codes and
+ * scales of Wh_cat[3H,H].  Same results as b200gru_dense_forward / _backward on Wq (same workspace
+ * sizes, b200gru_workspace_bytes with kind DENSE); at GEMM-sized batch the products run on the
+ * integer codes (int8 x int8 -> int32 in the forward when the hidden state is quantised too).
+ * dWq is the gradient with respect to Wq; feed it to b200gru_quantize_rows_backward.  Stands in
+ * for gru_scan_persistent on the weights of GRUCellQuant.quantize_weights() (README.md:65-74,
+ * src/gru_qat/gru_cell.py:239-271 of the reference). */
+int b200gru_dense_q8_forward(const float* gi, const float* h0, const float* Wq, const signed char* codes,
+                             const float* scales, const float* bh_cat, int T, int B, int H,
+                             const b200gru_quant* q_in, const b200gru_quant* q_out, float* out, float* save,
+                             void* workspace, size_t workspace_bytes, void* stream);
+int b200gru_dense_q8_backward(const float* gi, const float* h0, const float* Wq, const signed char* codes,
+                              const float* scales, const float* bh_cat, const float* out, const float* dout,
+                              const float* save, int T, int B, int H, const b200gru_quant* q_in,
+                              const b200gru_quant* q_out, float* dgi, float* dh0, float* dWq, float* dbh,
+                              void* workspace, size_t workspace_bytes, void* stream);
+
 /* ---- tensor-core GEMM core (tcgen05 / tensor memory) ------------------------------------------
  * The products of the path that are real GEMMs -- the input projection gi = x . Wi^T + bi
  * (F.linear, src/gru_qat/gru_layer.py:251-253, src/gru_qat/gru_cell.py:410-435), the per-step
@@ -186,6 +218,7 @@ typedef struct {
   int split_k;
   int tile_n;             /* 0 = library's choice, else 64, 128 or 256 */
   int chunk_kblocks;      /* 0 = library's choice; see below */
+  int accumulate;         /* != 0: add the result to what C already holds */
   float alpha;
   const float* row_scale;
   const float* col_scale;

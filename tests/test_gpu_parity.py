@@ -419,7 +419,11 @@ def test_baseline_config5_shard_shape():
                           d[4][:, sl].contiguous(), **kw))
     assert rel_err(halves[0][2] + halves[1][2], grads[2]) <= GRAD_TOL
     assert rel_err(halves[0][3] + halves[1][3], grads[3]) <= GRAD_TOL
-    assert torch.equal(torch.cat([halves[0][0], halves[1][0]], dim=1), grads[0])     # rows are independent
+    # rows are independent; the contraction of the backward product is split over CTAs according to
+    # the batch size, so halves and whole agree to rounding, not bit for bit
+    assert rel_err(torch.cat([halves[0][0], halves[1][0]], dim=1), grads[0]) <= 1e-5
+    out_half = fwd(d[0][:, :B // 2].contiguous(), d[1][:B // 2].contiguous(), d[2], d[3], **kw)
+    assert torch.equal(out_half, out[:, :B // 2])                                     # the forward is bit-exact
 
 
 @pytest.mark.parametrize("kind,T,B,H,extra", [("dense", 16, 32, 512, {}), ("dense", 6, 3, 1024, {}),

@@ -1,0 +1,218 @@
+"""GPU tests of the tensor-core products: the GEMM core against float64, the weight-prep kernel
+and the fused input projection against torch autograd, the dense scan on int8 weights and the
+dense ``GRULayer`` dispatch against the CPU oracle / the reference-generated layer fixtures.
+
+Tolerances as elsewhere: fp32 forward 1e-5 (absolute and relative), gradients 1e-4 of the
+largest reference entry; integer products are exact.
+"""
+
+from __future__ import annotations
+
+import copy
+
+import pytest
+import torch
+
+from conftest import load_golden, rel_err
+from oracle import gru_scan_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+FWD_TOL = 1e-5
+GRAD_TOL = 1e-4
+
+
+def _tc():
+    from gru_triton_b200 import tc
+    return tc
+
+
+@pytest.mark.parametrize("M,N,K,tile_n", [(128, 64, 128, 64), (300, 96, 1024, 0), (130, 3072, 1056, 256),
+                                          (1, 4, 16, 0), (257, 132, 144, 128)])
+def test_int8_product_is_exact(M, N, K, tile_n):
+    tc = _tc()
+    g = torch.Generator(device="cuda").manual_seed(M + N + K)
+    a = torch.randint(-127, 128, (M, K), device="cuda", dtype=torch.int8, generator=g)
+    b = torch.randint(-127, 128, (N, K), device="cuda", dtype=torch.int8, generator=g)
+    C = tc.gemm(a, b, tile_n=tile_n)
+    ref = (a.cpu().double() @ b.cpu().double().T)
+    assert torch.equal(C.cpu().double(), ref)
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (True, False), (False, True), (True, True)])
+@pytest.mark.parametrize("M,N,K", [(256, 256, 512), (200, 132, 456), (128, 1028, 64)])
+def test_bf16_operand_forms(a_mn, b_mn, M, N, K):
+    """Every combination of K-major / MN-major operands, ragged sizes, and a split over K."""
+    tc = _tc()
+    torch.manual_seed(M + K)
+    a = torch.randn(M, K, device="cuda").bfloat16()
+    b = torch.randn(N, K, device="cuda").bfloat16()
+    ref = a.cpu().double() @ b.cpu().double().T
+    A = a.T.contiguous() if a_mn else a
+    Bm = b.T.contiguous() if b_mn else b
+    if (a_mn and M % 8) or (b_mn and N % 8):
+        pytest.skip("an MN-major operand needs a 16-byte row stride")
+    for split in (1, 3):
+        C = tc.gemm(A, Bm, a_mn=a_mn, b_mn=b_mn, split_k=split)
+        assert rel_err(C.cpu(), ref) < 2e-6
+
+
+def test_split_products_reach_fp32_accuracy():
+    """Three bf16 planes per operand, six cross products, chunked accumulation: at least as close to
+    float64 as an fp32 SIMT product; scales, bias and accumulate are applied as documented."""
+    tc = _tc()
+    torch.manual_seed(0)
+    M, N, K = 384, 512, 1024
+    x = torch.randn(M, K, device="cuda")
+    w = (torch.rand(N, K, device="cuda") * 2 - 1) / 32
+    xp, wp = tc.split_bf16(x), tc.split_bf16(w)
+    assert float((xp.float().sum(0) - x).abs().max()) == 0.0          # three planes are exact
+    ref = x.cpu().double() @ w.cpu().double().T
+    err = rel_err(tc.gemm(xp, wp, pairs=tc.PAIRS_FULL).cpu(), ref)
+    assert err < 2e-6, err
+    bias, cs, rs = torch.randn(N, device="cuda"), torch.rand(N, device="cuda") + 0.5, torch.rand(M, device="cuda") + 0.5
+    ref2 = ref * rs.cpu().double()[:, None] * cs.cpu().double()[None, :] * 0.5 + bias.cpu().double()[None, :]
+    C = tc.gemm(xp, wp, pairs=tc.PAIRS_FULL, alpha=0.5, row_scale=rs, col_scale=cs, bias=bias)
+    assert rel_err(C.cpu(), ref2) < 2e-6
+    C2 = tc.gemm(xp, wp, pairs=tc.PAIRS_FULL, alpha=0.5, row_scale=rs, col_scale=cs, bias=bias, out=C.clone(),
+                 accumulate=True)
+    assert rel_err(C2.cpu(), 2 * ref2) < 2e-6
+    # a weight-gradient shaped product: long contraction, both operands MN-major, split + chunked
+    Kl = 65536
+    a, b = torch.randn(Kl, 128, device="cuda"), torch.randn(Kl, 256, device="cuda")
+    refl = a.cpu().double().T @ b.cpu().double()
+    got = tc.gemm(tc.split_bf16(a), tc.split_bf16(b), a_mn=True, b_mn=True, pairs=tc.PAIRS_FULL, split_k=8)
+    assert rel_err(got.cpu(), refl) < 3e-6
+
+
+@pytest.mark.parametrize("rows,cols,bits", [(48, 16, 8), (96, 1024, 8), (30, 260, 4)])
+def test_weight_prep_matches_autograd(rows, cols, bits):
+    """Codes, scales and values of the per-row fake-quant and its straight-through gradient
+    (including the term through the dynamic scale) against torch autograd on the CPU."""
+    from gru_triton_b200 import _lib
+    torch.manual_seed(rows + cols)
+    W = (torch.rand(rows, cols) * 2 - 1) * 0.1
+    Wl = W.clone().requires_grad_(True)
+    ref = orc.per_row_weight_fake_quant(Wl, bits)
+    g = torch.randn(rows, cols)
+    ref.backward(g)
+    codes, scales, Wq = _lib.quantize_rows(W.cuda(), bits)
+    qmax = 2 ** (bits - 1) - 1
+    s_ref = W.abs().amax(dim=1).clamp(min=1e-8) / qmax
+    assert torch.equal(scales.cpu(), s_ref)
+    assert torch.equal(Wq.cpu(), ref.detach())
+    assert torch.equal(codes.cpu().float() * s_ref[:, None], ref.detach())
+    dW = _lib.quantize_rows_backward(W.cuda(), g.cuda(), bits)
+    assert rel_err(dW.cpu(), Wl.grad) < 1e-5
+
+
+@pytest.mark.parametrize("bits", [32, 8])
+@pytest.mark.parametrize("R,I,N", [(60, 64, 192), (1000, 520, 136), (40000, 128, 384)])
+def test_input_projection_forward_and_gradients(R, I, N, bits):
+    tc = _tc()
+    torch.manual_seed(R)
+    x = torch.randn(R, I)
+    W = (torch.rand(N, I) * 2 - 1) / I ** 0.5
+    b = torch.randn(N) * 0.1
+    dy = torch.randn(R, N)
+    xl, bl = (t.double().requires_grad_(True) for t in (x, b))
+    Wl = W.clone().requires_grad_(True)                    # the fake-quant itself in fp32, as the reference does
+    Wq = (orc.per_row_weight_fake_quant(Wl, bits) if bits < 32 else Wl).double()
+    ref = torch.nn.functional.linear(xl, Wq, bl)
+    ref.backward(dy.double())
+    xg, Wg, bg = (t.cuda().requires_grad_(True) for t in (x, W, b))
+    y = tc.linear(xg, Wg, bg, weight_bits=bits)
+    y.backward(dy.cuda())
+    assert bool(((y.detach().cpu() - ref.detach()).abs() <= FWD_TOL + FWD_TOL * ref.detach().abs()).all())
+    assert rel_err(Wg.grad.cpu(), Wl.grad) < GRAD_TOL
+    assert rel_err(bg.grad.cpu(), bl.grad) < GRAD_TOL
+    assert rel_err(xg.grad.cpu(), xl.grad) < GRAD_TOL
+
+
+@pytest.mark.parametrize("T,B,H,hq", [(6, 130, 576, True), (5, 256, 1024, True), (4, 128, 544, False), (7, 5, 64, True)])
+def test_dense_scan_on_int8_weights(T, B, H, hq):
+    """gru_scan_dense_q8 (weight prep + int8 x int8 steps at GEMM-sized batch, cluster kernels
+    otherwise) against the oracle run on the fake-quantised weights, forward codes and all gradients
+    including the one that reaches the raw weights through the dynamic row scale."""
+    tc = _tc()
+    from test_gpu_parity import check_forward
+    gi, h0, W, bh, dout = orc.make_problem("dense", T, B, H, seed=T + B + H, h0_scale=0.1)
+    quant = ((0.008, -127, 127), (0.008, -127, 127)) if hq else None
+    qi, qo = quant if quant else (None, None)
+    Wl = W.clone().requires_grad_(True)
+    Wq = orc.per_row_weight_fake_quant(Wl)
+    leaves = [t.cuda().requires_grad_(True) for t in (gi, h0, W, bh)]
+    out = tc.gru_scan_dense_q8(*leaves, h_in_quant=qi, h_out_quant=qo)
+    bsub = min(B, 4)
+    check_forward("dense", out.detach()[:, :bsub], gi[:, :bsub], h0[:bsub], Wq.detach(), bh, quant)
+    out.backward(dout.cuda())
+    # oracle gradients from the device's own forward output, on all rows (dW needs them)
+    ref = orc.scan_backward("dense", gi, h0, Wq.detach(), bh, out.detach().cpu(), dout, qi, qo)
+    Wq.backward(ref[2])
+    for nm, a, b in zip(("dgi", "dh0", "dW", "dbh"), [l.grad for l in leaves], (ref[0], ref[1], Wl.grad, ref[3])):
+        assert rel_err(a.cpu(), b) <= GRAD_TOL, nm
+
+
+def _recipe(hidden_bits=32, weight_bits=32):
+    from gru_triton_b200 import QuantizerConfig, QuantRecipe
+    return QuantRecipe(weight=QuantizerConfig(bits=weight_bits, axis=0, name="W"),
+                       input_act=QuantizerConfig(bits=32, name="x_id"),
+                       hidden=QuantizerConfig(bits=hidden_bits, mode="frozen", name="h"))
+
+
+@pytest.mark.parametrize("name,wbits", [("layer_dense_fp32", 32), ("layer_dense_w8h8", 8)])
+def test_dense_layer_dispatch_against_reference_fixture(name, wbits):
+    """GRULayer(dense, fused) on CUDA -- the dispatch the reference does not have -- against the
+    fixture produced by the reference's own per-step GRULayer(use_triton=False)."""
+    from gru_triton_b200 import GRULayer
+    g = load_golden(name)
+    I, H = g["x"].shape[2], g["h0"].shape[1]
+    layer = GRULayer(I, H, _recipe(8 if g["q_in"] else 32, wbits), gate_layout="fused")
+    assert layer.use_triton
+    with torch.no_grad():
+        for k, v in g.items():
+            if k.startswith("p:"):
+                layer.get_parameter(k[2:]).copy_(v)
+    if g["q_in"]:
+        for q, p in ((layer.cell.quant_h_in, g["q_in"]), (layer.cell.quant_h_out, g["q_out"])):
+            q.scale, q.zero_point, q.config.mode = torch.tensor(p[0]), torch.tensor(0.0), "frozen"
+    layer = layer.cuda()
+    out, hT = layer(g["x"].cuda(), g["h0"].cuda())
+    out.sum().backward()
+    assert (out.detach().cpu() - g["out"]).abs().max().item() < FWD_TOL
+    assert torch.equal(hT, out[-1])
+    for k, v in g.items():
+        if k.startswith("g:"):
+            assert rel_err(layer.get_parameter(k[2:]).grad.cpu(), v) < GRAD_TOL, k
+
+
+@pytest.mark.parametrize("wbits,hbits,T,B,H", [(32, 32, 12, 5, 64), (8, 8, 9, 130, 576), (8, 32, 6, 128, 544),
+                                               (32, 8, 5, 132, 640)])
+def test_dense_layer_dispatch_matches_per_step_path(wbits, hbits, T, B, H):
+    """The same layer stepping on the CPU (per-step cell, autograd) and dispatched on CUDA:
+    cluster kernels at small batch, tensor-core steps at GEMM-sized batch, fp32 and int8 recipes."""
+    from gru_triton_b200 import GRULayer
+    torch.manual_seed(wbits + hbits + T)
+    lay = GRULayer(H, H, _recipe(hbits, wbits), gate_layout="fused", use_triton=False)
+    if hbits < 32:
+        for q in (lay.cell.quant_h_in, lay.cell.quant_h_out):
+            q.scale, q.zero_point = torch.tensor(0.008), torch.tensor(0.0)
+    x, h0 = torch.randn(T, B, H), torch.randn(B, H) * 0.1
+    ref, _ = lay(x, h0)
+    ref.sum().backward()
+    gl = copy.deepcopy(lay).cuda()
+    gl.zero_grad()
+    gl.use_triton = True
+    out, _ = gl(x.cuda(), h0.cuda())
+    out.sum().backward()
+    o = out.detach().cpu()
+    if hbits < 32:
+        # quantised trajectories may part at a rounding tie; compare teacher-forced through the scan test
+        # above and here only demand that nearly every code agrees
+        frac = float((o != ref.detach()).float().mean())
+        print(f"[layer] fraction of codes that differ from the CPU per-step trajectory: {frac:.2e}")
+        assert frac < 5e-3
+    else:
+        assert bool(((o - ref.detach()).abs() <= FWD_TOL + FWD_TOL * ref.detach().abs()).all())
+        for (n, p), (_, q) in zip(lay.named_parameters(), gl.named_parameters()):
+            assert rel_err(q.grad.cpu(), p.grad) <= GRAD_TOL, n

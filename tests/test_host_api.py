@@ -119,7 +119,7 @@ def test_structured_modules_feed_the_extractors():
 def test_layer_argument_errors():
     rec = _recipe()
     with pytest.raises(ValueError):
-        GRULayer(8, 8, rec, gate_layout="fused", use_triton=True)          # dense is not dispatchable
+        GRULayer(8, 8, rec, gate_layout="split", use_triton=True)          # split gates are not dispatchable
     with pytest.raises(ValueError):
         GRULayer(8, 8, rec, pre_batch_input=True)                          # needs fused
     with pytest.raises(ValueError):
@@ -134,7 +134,8 @@ def test_layer_argument_errors():
         lay(torch.zeros(0, 2, 8))
     with pytest.raises(ValueError, match="B"):
         lay(torch.zeros(3, 0, 8))
-    assert GRULayer(8, 8, rec, gate_layout="fused").use_triton is False
+    assert GRULayer(8, 8, rec, gate_layout="fused").use_triton is True     # dense + fused: this build's extension
+    assert GRULayer(8, 8, rec, gate_layout="split").use_triton is False
     assert GRULayer(8, 8, rec, gate_layout="fused",
                     structure_hidden=StructureConfig(kind="diagonal")).use_triton is True
     assert GRULayer(8, 8, rec, gate_layout="split",
