@@ -3,14 +3,17 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--config c1|c2|c3|c4|c5] [--impl reference]
 
-Default workload (every N): BASELINE config 1 -- dense fp32 train step at T=64, B=32 per
-GPU, I=H=512: input projection (cuBLAS, as the reference does), the CUDA scan forward,
-loss = out.sum(), scan backward + weight-gradient GEMMs, input-side gradients.  With N > 1
-each rank runs its own batch (weak scaling) and the weight gradients are all-reduced once
-per step over NCCL.  Metric: sequence-steps/s = T*B*N / step time.
+Every workload is a ``GRULayer`` of this package built from BASELINE.json's description and run
+through its public API: ``out, h_T = layer(x, h0)``, ``out.sum().backward()`` -- input projection
+on the tensor-core GEMM core, the CUDA scan, the weight gradients.  Default (every N): config 1,
+dense fp32 train step at T=64, B=32 per GPU, I=H=512; with N > 1 each rank runs its own batch
+(weak scaling) and the weight gradients are all-reduced once per step over NCCL through
+``data_parallel.GradBucket``.  Metric: sequence-steps/s = T*B*N / step time.  Each line also
+carries a ``c5`` record: config 5 (dense int8 QAT, T=512, H=1024, B=4096 split over the N GPUs),
+three timed steps.
 
-One JSON line on stdout (rank 0).  `--impl reference` times the CPU port of the reference's
-per-step path (oracle/) on the host cores instead.
+One JSON line on stdout (rank 0).  ``--impl reference`` times the reference's own CPU code
+(installed unmodified under oracle/_ref by oracle/make_ref.py) on the host cores instead.
 """
 
 from __future__ import annotations
@@ -29,8 +32,6 @@ import torch
 REPO = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, REPO)
 
-Q8 = 0.02   # placeholder scale replaced by calibration where a config asks for int8 hidden state
-
 CONFIGS = {
     # name: kind, T, B (per GPU for c1-c4; TOTAL for c5), H, quant, train, extras
     "c1": dict(kind="dense", T=64, B=32, H=512, quant=False, train=True, wbits=32, h0_scale=0.0,
@@ -44,7 +45,6 @@ CONFIGS = {
     "c5": dict(kind="dense", T=512, B=4096, H=1024, quant=True, train=True, wbits=8, h0_scale=0.0,
                desc="dense int8-weight int8-hidden train step T=512 B=4096 total I=H=1024, batch-sharded"),
 }
-
 
 # DRAM traffic (dram read + write bytes) of ONE launch of the roofline kernel, from the ncu captures
 # summarised under profiles/ (the same bench command under ncu; c2 captured at --T 128 and scaled by
@@ -70,21 +70,25 @@ def make_params(cfg, seed=0):
     def U(*shape, a):
         return (torch.rand(*shape, generator=gen) * 2 - 1) * a
 
-    if cfg is CONFIGS["c2"]:
+    if cfg is CONFIGS["c2"] or cfg.get("name") == "c2":
         W, bh = U(3, H, a=1.0), torch.zeros(3 * H)
         Wi, bi = U(3 * H, H, a=1 / 32), torch.zeros(3 * H)
-    elif cfg is CONFIGS["c3"]:
+    elif cfg.get("name") == "c3":
         W = torch.randn(3, 8, 64, 64, generator=gen) * 64 ** -0.5
         bh, Wi, bi = U(3 * H, a=k), U(3 * H, H, a=k), U(3 * H, a=k)
-    elif cfg is CONFIGS["c4"]:
+    elif cfg.get("name") == "c4":
         W = U(3, 1, 10, 512, 2, 2, a=2 ** -0.5)
         bh, Wi, bi = U(3 * H, a=k), U(3 * H, H, a=k), U(3 * H, a=k)
-    elif cfg is CONFIGS["c5"]:
+    elif cfg.get("name") == "c5":
         W, bh, Wi, bi = U(3 * H, H, a=1 / 32), U(3 * H, a=1 / 32), U(3 * H, H, a=1 / 32), U(3 * H, a=1 / 32)
     else:
         W, _ = orc.make_weights(kind, H, gen, nblocks=cfg.get("nblocks", 4))
         bh, Wi, bi = U(3 * H, a=k), U(3 * H, H, a=k), U(3 * H, a=k)
     return dict(W=W, bh=bh, Wi=Wi, bi=bi)
+
+
+for _n, _c in CONFIGS.items():
+    _c["name"] = _n
 
 
 def calibrated_scale(cfg, params):
@@ -99,10 +103,33 @@ def calibrated_scale(cfg, params):
     return float(out.abs().max()) / 127.0
 
 
-def per_row_fake_quant(Wm, bits=8):
-    qmax = 2 ** (bits - 1) - 1
-    s = Wm.abs().amax(dim=1, keepdim=True).clamp(min=1e-8) / qmax
-    return torch.round(Wm / s).clamp(-qmax, qmax) * s
+def build_layer(pkg, cfg, params, scale, use_triton):
+    """``GRULayer`` of ``pkg`` (this package, or the reference's ``gru_qat``) holding ``params``."""
+    H = cfg["H"]
+    recipe = pkg.QuantRecipe(weight=pkg.QuantizerConfig(bits=cfg["wbits"], axis=0, name="W"),
+                             input_act=pkg.QuantizerConfig(bits=32, name="x_id"),
+                             hidden=pkg.QuantizerConfig(bits=8 if cfg["quant"] else 32, mode="frozen", name="h"))
+    kind = cfg["kind"]
+    structure = None
+    if kind != "dense":
+        structure = pkg.StructureConfig(kind=kind, nblocks=cfg.get("nblocks", 4))
+    layer = pkg.GRULayer(H, H, recipe, gate_layout="fused", structure_hidden=structure, use_triton=use_triton)
+    cell = layer.cell
+    with torch.no_grad():
+        for gi_, g in enumerate("rzn"):
+            getattr(cell, f"W_i{g}").copy_(params["Wi"][gi_ * H:(gi_ + 1) * H])
+            getattr(cell, f"b_i{g}").copy_(params["bi"][gi_ * H:(gi_ + 1) * H])
+            getattr(cell, f"b_h{g}").copy_(params["bh"][gi_ * H:(gi_ + 1) * H])
+            if kind == "dense":
+                getattr(cell, f"W_h{g}").copy_(params["W"][gi_ * H:(gi_ + 1) * H])
+            elif kind == "butterfly":
+                getattr(cell, f"struct_Wh_{g}").b.twiddle.copy_(params["W"][gi_][None])
+            else:
+                getattr(cell, f"struct_Wh_{g}").weight.copy_(params["W"][gi_])
+    if cfg["quant"]:
+        for q in (cell.quant_h_in, cell.quant_h_out):
+            q.scale, q.zero_point, q.config.mode = torch.tensor(float(scale)), torch.tensor(0.0), "frozen"
+    return layer
 
 
 # ---------------------------------------------------------------------------
@@ -110,77 +137,69 @@ def per_row_fake_quant(Wm, bits=8):
 # ---------------------------------------------------------------------------
 
 class DeviceWorkload:
-    def __init__(self, name, cfg, rank, world, dev):
-        from gru_triton_b200 import scan, scan_butterfly, scan_diagonal, scan_monarch
+    def __init__(self, name, cfg, rank, world, dev, pinned=True):
+        import gru_triton_b200 as pkg
+        from gru_triton_b200.data_parallel import GradBucket
         self.cfg, self.name, self.rank, self.world, self.dev = cfg, name, rank, world, dev
-        kind = cfg["kind"]
         self.T, self.H = cfg["T"], cfg["H"]
         self.B = cfg["B"] // world if name == "c5" else cfg["B"]
-        self.fn = {"dense": scan.gru_scan_persistent, "diagonal": scan_diagonal.gru_scan_diagonal,
-                   "monarch": scan_monarch.gru_scan_monarch,
-                   "butterfly": scan_butterfly.gru_scan_butterfly_triton}[kind]
-        self.fwd_only = {"dense": scan.gru_scan_forward_persistent,
-                         "diagonal": scan_diagonal.gru_scan_diagonal_forward_triton,
-                         "monarch": scan_monarch.gru_scan_monarch_forward_triton,
-                         "butterfly": scan_butterfly.gru_scan_butterfly_forward_triton}[kind]
         p = make_params(cfg)
-        self.quant = None
-        if cfg["quant"]:
-            s = calibrated_scale(cfg, p)
-            self.quant = ((s, -127, 127), (s, -127, 127))
-        self.P = {k: v.to(dev).requires_grad_(cfg["train"]) for k, v in p.items()}
+        self.scale = calibrated_scale(cfg, p) if cfg["quant"] else None
+        self.quant = ((self.scale, -127, 127), (self.scale, -127, 127)) if cfg["quant"] else None
+        self.layer = build_layer(pkg, cfg, p, self.scale, "auto").to(dev)
+        assert self.layer.use_triton, "the benchmark times the CUDA scan path"
+        self.layer.train(cfg["train"])
+        self.raw = {k: v.to(dev) for k, v in p.items()}
         gen = torch.Generator().manual_seed(100 + rank)
-        self.x_host = torch.randn(self.T, self.B, self.H, generator=gen).pin_memory()
-        self.h0_host = (torch.randn(self.B, self.H, generator=gen) * cfg["h0_scale"]).pin_memory()
-        self.x = self.x_host.to(dev)
-        self.h0 = self.h0_host.to(dev)
-        self.bucket = None
+        x = torch.randn(self.T, self.B, self.H, generator=gen)
+        h0 = torch.randn(self.B, self.H, generator=gen) * cfg["h0_scale"]
+        self.x_host = x.pin_memory() if pinned else None
+        self.h0_host = h0.pin_memory() if pinned else None
+        self.x, self.h0 = x.to(dev), h0.to(dev)
+        del x, h0
+        self.bucket = GradBucket(list(self.layer.parameters())) if (world > 1 and cfg["train"]) else None
 
-    # -- one pass of the hot path ------------------------------------------
-    def _weights(self):
-        P = self.P
-        Wi, W = P["Wi"], P["W"]
-        if self.cfg["wbits"] < 32:
-            # dynamic per-output-row int8 weight fake-quant; straight-through gradient
-            Wi = Wi + (per_row_fake_quant(Wi.detach()) - Wi.detach())
-            W = W + (per_row_fake_quant(W.detach()) - W.detach())
-        return Wi, W
-
+    # -- one pass of the hot path through the public API -----------------------
     def step(self, x, h0):
-        P = self.P
-        kw = dict(h_in_quant=self.quant[0], h_out_quant=self.quant[1]) if self.quant else {}
         if not self.cfg["train"]:
             with torch.no_grad():
-                gi = torch.nn.functional.linear(x, P["Wi"], P["bi"])
-                return self.fn(gi, h0, P["W"], P["bh"], **kw)
-        for v in P.values():
-            v.grad = None
-        Wi, W = self._weights()
-        gi = torch.nn.functional.linear(x, Wi, P["bi"])
-        out = self.fn(gi, h0, W, P["bh"], **kw)
+                return self.layer(x, h0)[0]
+        self.layer.zero_grad(set_to_none=True)
+        out, _ = self.layer(x, h0)
         loss = out.sum()
         loss.backward()
-        if self.world > 1:
-            import torch.distributed as dist
-            grads = [P[k].grad for k in ("W", "Wi", "bh", "bi")]
-            flat = torch.cat([g.reshape(-1) for g in grads])
-            dist.all_reduce(flat)
+        if self.bucket is not None:
+            self.bucket.all_reduce()              # one flat NCCL all-reduce, gradients written back
         return loss
 
     def scan_only_forward(self):
-        """The dominant kernel in isolation (one launch): forward scan on resident gi."""
-        P = self.P
-        kw = dict(h_in_quant=self.quant[0], h_out_quant=self.quant[1]) if self.quant else {}
+        """The dominant kernel(s) in isolation: the forward scan on resident gi."""
+        from gru_triton_b200 import _lib
+        P = self.raw
+        qi, qo = self.quant if self.quant else (None, None)
         with torch.no_grad():
             if not hasattr(self, "_gi"):
                 self._gi = torch.nn.functional.linear(self.x, P["Wi"], P["bi"])
-            return self.fwd_only(self._gi, self.h0, P["W"], P["bh"], **kw)
+                self._codes = _lib.quantize_rows(P["W"], 8) if self.cfg["wbits"] <= 8 else None
+            kw = {}
+            if self.cfg["kind"] == "monarch":
+                kw["nblocks"] = P["W"].shape[1]
+            if self.cfg["kind"] == "butterfly":
+                kw["nblocks"], kw["log2_hpad"] = P["W"].shape[1], P["W"].shape[2]
+            if self._codes is not None:
+                codes, scales, Wq = self._codes
+                return _lib.scan_forward("dense", self._gi, self.h0, Wq, P["bh"], qi, qo, codes=codes, scales=scales)[0]
+            return _lib.scan_forward(self.cfg["kind"], self._gi, self.h0, P["W"], P["bh"], qi, qo, **kw)[0]
 
     def units(self):
         return self.T * self.B
 
     def scan_fwd_bytes(self):
         return 16 * self.H * self.T * self.B      # gi read 12H + out write 4H per sequence-step
+
+    def tensor_path(self):
+        return (self.cfg["kind"] == "dense" and self.H % 32 == 0 and self.B >= 128
+                and 12 * self.H * ((self.H + 15) // 16) > 200 * 1024)
 
 
 class ClockSampler:
@@ -245,6 +264,60 @@ def timed_loop(fn, steps, warmup, flush, sync_all):
     return [a.elapsed_time(b) for a, b in evs]
 
 
+def load_peaks():
+    ppath = os.path.join(REPO, "MEASURED_PEAKS.json")
+    return json.load(open(ppath)) if os.path.exists(ppath) else {}
+
+
+def tensor_roofline(wl, k_ms, scan_launches, peaks):
+    """Forward scan of the tensor-core path: T products [B,H] x [H,3H], int8 codes (exact) or bf16
+    planes, against the measured sustained bf16 GEMM rate."""
+    flops = 2.0 * wl.T * wl.B * wl.H * 3 * wl.H
+    peak_tf = float(peaks.get("bf16_tflops_sustained", 1400.0))
+    ach = flops / (k_ms * 1e-3) / 1e12
+    return {"kernel": "tc_gemm_kernel (+ gate_fwd_kernel), one pair per time step", "bound": "tensor",
+            "achieved": ach, "peak": peak_tf, "unit": "TFLOP/s", "frac": ach / peak_tf,
+            "peak_source": "measured (sustained bf16)" if peaks else "fallback",
+            "traffic": None, "launch_ms": k_ms / max(scan_launches, 1), "per_step_us": k_ms * 1e3 / wl.T,
+            "launches_per_call": scan_launches, "algorithmic_flops_per_launch": flops / wl.T,
+            "note": "each step is a small product (B x 3H x H) on the serial chain: the fraction of the tensor "
+                    "peak is bounded by per-step latency, reported as per_step_us"}
+
+
+def run_c5_record(dev, rank, world, flush, sync_all, max_over_ranks, peaks):
+    """Config 5 at this N: B = 4096 / N rows per GPU, three timed train steps (device-resident
+    inputs), the forward scan alone for its tensor-core fraction, and the all-reduce alone."""
+    import torch.distributed as dist
+    from gru_triton_b200 import _lib
+    cfg = CONFIGS["c5"]
+    rec = {"workload": cfg["desc"], "B_per_gpu": cfg["B"] // world, "scaling": "strong"}
+    try:
+        wl = DeviceWorkload("c5", cfg, rank, world, dev, pinned=False)
+        n0 = _lib.launch_count()
+        ms = max_over_ranks(timed_loop(lambda: wl.step(wl.x, wl.h0), 3, 1, flush, sync_all))
+        rec["gpu_launches_per_step"] = (_lib.launch_count() - n0) / 4
+        rec["ms_per_step"] = sum(ms) / len(ms)
+        rec["seq_steps_per_s"] = cfg["T"] * cfg["B"] / (rec["ms_per_step"] * 1e-3)
+        if wl.bucket is not None:
+            ar = max_over_ranks(timed_loop(lambda: dist.all_reduce(wl.bucket.flat), 5, 2, flush, sync_all))
+            rec["allreduce_ms"] = statistics.median(ar)
+            rec["allreduce_bytes"] = wl.bucket.flat.numel() * 4
+        wl.layer.zero_grad(set_to_none=True)
+        torch.cuda.empty_cache()
+        n1 = _lib.launch_count()
+        ks = max_over_ranks(timed_loop(wl.scan_only_forward, 3, 1, flush, sync_all))
+        rec["roofline"] = tensor_roofline(wl, statistics.median(ks), (_lib.launch_count() - n1) / 4, peaks)
+        # whole step: 30 H^2 flops per sequence-step (forward, backward and both weight gradients)
+        step_flops = 30.0 * cfg["H"] ** 2 * cfg["T"] * (cfg["B"] // world)
+        rec["step_tflops_fp32_equivalent"] = step_flops / (rec["ms_per_step"] * 1e-3) / 1e12
+        rec["peak_mem_gb"] = torch.cuda.max_memory_allocated(dev) / 1e9
+        del wl
+    except torch.cuda.OutOfMemoryError as e:
+        rec["error"] = f"out of memory: {str(e)[:120]}"
+    torch.cuda.empty_cache()
+    return rec
+
+
 def run_device(args):
     import torch.distributed as dist
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -302,74 +375,77 @@ def run_device(args):
     e2e_ms = sum(ms_e2e) / len(ms_e2e)
 
     # ---- (3) the dominant kernel alone (forward scan), for the roofline --------------
+    if cfg["train"]:
+        wl.layer.zero_grad(set_to_none=True)
     n1 = _lib.launch_count()
-    ks = timed_loop(wl.scan_only_forward, max(args.steps, 10), 3, flush, sync_all)
-    scan_launches = (_lib.launch_count() - n1) / (max(args.steps, 10) + 3)
+    ks = timed_loop(wl.scan_only_forward, max(min(args.steps, 20), 5), 3, flush, sync_all)
+    scan_launches = (_lib.launch_count() - n1) / (max(min(args.steps, 20), 5) + 3)
     k_ms = statistics.median(ks)
     clocks = sampler.stop() if sampler else None
+
+    peaks = load_peaks()
+    c5 = None
+    if args.c5 and args.config == "c1" and not (args.T or args.B):
+        h_bytes = wl.x_host.numel() * 4 + wl.h0_host.numel() * 4
+        units_main, tensor_main = wl.units(), wl.tensor_path()
+        scan_bytes, Tm, Bm, Hm = wl.scan_fwd_bytes(), wl.T, wl.B, wl.H
+        del wl
+        torch.cuda.empty_cache()
+        c5 = run_c5_record(dev, rank, world, flush, sync_all, max_over_ranks, peaks)
+    else:
+        h_bytes = wl.x_host.numel() * 4 + wl.h0_host.numel() * 4
+        units_main, tensor_main = wl.units(), wl.tensor_path()
+        scan_bytes, Tm, Bm, Hm = wl.scan_fwd_bytes(), wl.T, wl.B, wl.H
 
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
         return
 
-    peaks = {}
-    ppath = os.path.join(REPO, "MEASURED_PEAKS.json")
-    if os.path.exists(ppath):
-        peaks = json.load(open(ppath))
     peak_gbs = float(peaks.get("hbm_gbs", 6650.0))
-    achieved = wl.scan_fwd_bytes() / (k_ms * 1e-3) / 1e9
-
-    step_path = (cfg["kind"] == "dense" and wl.H % 32 == 0 and wl.B >= 128
-                 and 12 * wl.H * ((wl.H + 15) // 16) > 200 * 1024)
-    if step_path:
-        # large-batch dense: T fused SGEMM launches (FP32 FMA pipe); reported against the tensor peak
-        flops = 2.0 * wl.T * wl.B * wl.H * 3 * wl.H
-        peak_tf = float(peaks.get("bf16_tflops_sustained", 1400.0))
-        ach = flops / (k_ms * 1e-3) / 1e12
-        roofline = {"kernel": "dense_step_fwd_kernel", "bound": "tensor", "achieved": ach, "peak": peak_tf,
-                    "unit": "TFLOP/s", "frac": ach / peak_tf,
-                    "peak_source": "measured (sustained bf16)" if peaks else "fallback",
-                    "traffic": None, "launch_ms": k_ms / max(scan_launches - 2, 1),
-                    "per_step_us": k_ms * 1e3 / wl.T, "launches_per_call": scan_launches,
-                    "algorithmic_flops_per_launch": flops / wl.T,
-                    "note": "FP32 FMA kernel (parity bar 1e-5 rules out one-pass TF32/BF16); the fraction of the "
-                            "tensor peak states the headroom a split-precision tensor-core version would have"}
+    achieved = scan_bytes / (k_ms * 1e-3) / 1e9
+    if tensor_main:
+        class _W:
+            T, B, H = Tm, Bm, Hm
+        roofline = tensor_roofline(_W, k_ms, scan_launches, peaks)
     else:
+        latency_bound = cfg["kind"] != "diagonal"
+        fp32_peak = 148 * 128 * 2 * 1.965e9 / 1e12          # FMA lanes x 2 flops x max SM clock, nominal
+        scan_flops = {"dense": 6.0 * Hm * Hm, "monarch": 6.0 * Hm * (Hm // cfg.get("nblocks", 4)),
+                      "butterfly": 9.0 * Hm * max(1, (Hm - 1).bit_length()), "diagonal": 40.0 * Hm}[cfg["kind"]] * Tm * Bm
         roofline = {"kernel": {"dense": "block_fwd_kernel", "monarch": "block_fwd_kernel",
                                "diagonal": "diag_fwd_tma_kernel", "butterfly": "bfly_fwd2_kernel"}[cfg["kind"]],
-                    "bound": "hbm", "achieved": achieved, "peak": peak_gbs, "unit": "GB/s",
+                    "bound": "latency" if latency_bound else "hbm",
+                    "achieved": achieved, "peak": peak_gbs, "unit": "GB/s",
                     "frac": achieved / peak_gbs, "peak_source": "measured" if peaks else "fallback",
-                    "traffic": (ROOFLINE_TRAFFIC[args.config]["bytes"] * wl.T / ROOFLINE_TRAFFIC[args.config]["T"]
+                    "traffic": (ROOFLINE_TRAFFIC[args.config]["bytes"] * Tm / ROOFLINE_TRAFFIC[args.config]["T"]
                                 if args.config in ROOFLINE_TRAFFIC and not args.B else None),
-                    "launch_ms": k_ms, "per_step_us": k_ms * 1e3 / wl.T,
+                    "launch_ms": k_ms, "per_step_us": k_ms * 1e3 / Tm,
                     "launches_per_call": scan_launches,
-                    "algorithmic_bytes_per_launch": wl.scan_fwd_bytes()}
-        if cfg["kind"] != "diagonal":
+                    "algorithmic_bytes_per_launch": scan_bytes,
+                    "fp32_tflops": scan_flops / (k_ms * 1e-3) / 1e12,
+                    "fp32_frac_of_nominal_fma_peak": scan_flops / (k_ms * 1e-3) / 1e12 / fp32_peak}
+        if latency_bound:
             roofline["note"] = ("a serial chain of T dependent steps inside one launch: DRAM is nearly idle and no "
                                 "pipe is saturated (ncu: profiles/); the bound is the latency of one step, reported "
-                                "as per_step_us")
+                                "as per_step_us; frac is the HBM fraction, fp32_frac the FMA-pipe fraction")
 
-    units = wl.units() * world
+    units = units_main * world
     line = {
         "metric": "sequence-steps/sec (T*B/s)", "value": units / (ms_per_step * 1e-3), "unit": "seq-steps/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
         "higher_is_better": True, "scaling": "strong" if args.config == "c5" else "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"{args.config}: {cfg['desc']}", "T": wl.T, "B_per_gpu": wl.B, "H": wl.H,
-                   "hidden_kind": cfg["kind"], "int8_hidden": bool(cfg["quant"]), "weight_bits": cfg["wbits"],
-                   "train_step": bool(cfg["train"]), "parallelism": f"batch-shard x{world}" if world > 1 else "1 GPU",
-                   "l2": "256 MiB buffer written between timed steps (outside the timed events)",
-                   **({"override": "T/B changed on the command line: a profiling case, not a result"}
-                      if (args.T or args.B) else {})},
+        "config": config_dict(args.config, cfg, Bm, world, bool(args.T or args.B)),
         "e2e": {"value": units / (e2e_ms * 1e-3), "unit": "seq-steps/s", "ms_per_step": e2e_ms,
-                "h2d_bytes_per_step": wl.x_host.numel() * 4 + wl.h0_host.numel() * 4,
-                "d2h_bytes_per_step": 4},
+                "h2d_bytes_per_step": h_bytes, "d2h_bytes_per_step": 4},
         "gpu_launches": int(round(launches_per_step * args.steps)),
         "gpu_launches_per_step": launches_per_step,
         "clocks": clocks,
         "roofline": roofline,
     }
+    if c5 is not None:
+        line["c5"] = c5
     if world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(args.config, budget_s=15.0)
     if args.kinds and world == 1 and args.config == "c1":
@@ -379,23 +455,31 @@ def run_device(args):
         dist.destroy_process_group()
 
 
+def config_dict(name, cfg, B_per_gpu, world, override):
+    d = {"workload": f"{name}: {cfg['desc']}", "T": cfg["T"], "B_per_gpu": B_per_gpu, "H": cfg["H"],
+         "hidden_kind": cfg["kind"], "int8_hidden": bool(cfg["quant"]), "weight_bits": cfg["wbits"],
+         "train_step": bool(cfg["train"]), "parallelism": f"batch-shard x{world}" if world > 1 else "1 GPU",
+         "l2": "256 MiB buffer written between timed steps (outside the timed events)"}
+    if override:
+        d["override"] = "T/B changed on the command line: a profiling case, not a result"
+    return d
+
+
 def kinds_table(dev, flush, sync_all):
     """ms/iter of a train step at the headline shape (T=64, B=32, H=512) per hidden kind."""
     out = {}
-    for name, cfgname in (("dense", "c1"), ("monarch_nb8_int8h", "c3")):
-        wl = DeviceWorkload(cfgname, CONFIGS[cfgname], 0, 1, dev)
-        ms = timed_loop(lambda: wl.step(wl.x, wl.h0), 20, 3, flush, sync_all)
-        out[name] = {"ms_per_iter": statistics.median(ms), "seq_steps_per_s": wl.units() / (statistics.median(ms) * 1e-3)}
-    for name, kind in (("diagonal", "diagonal"), ("butterfly", "butterfly")):
-        cfg = dict(CONFIGS["c1"], kind=kind)
-        wl = DeviceWorkload("c1", cfg, 0, 1, dev)
+    cases = [("dense", "c1", CONFIGS["c1"]), ("monarch_nb8_int8h", "c3", CONFIGS["c3"]),
+             ("diagonal", "c1", dict(CONFIGS["c1"], kind="diagonal", name="c1k")),
+             ("butterfly", "c1", dict(CONFIGS["c1"], kind="butterfly", name="c1k"))]
+    for name, cfgname, cfg in cases:
+        wl = DeviceWorkload(cfgname, cfg, 0, 1, dev, pinned=False)
         ms = timed_loop(lambda: wl.step(wl.x, wl.h0), 20, 3, flush, sync_all)
         out[name] = {"ms_per_iter": statistics.median(ms), "seq_steps_per_s": wl.units() / (statistics.median(ms) * 1e-3)}
     return out
 
 
 # ---------------------------------------------------------------------------
-# CPU arm: the oracle's port of the reference's per-step PyTorch path
+# CPU arm: the reference's own code (oracle/_ref), or the oracle's port where it cannot run
 # ---------------------------------------------------------------------------
 
 def cpu_problem(name):
@@ -408,28 +492,67 @@ def cpu_problem(name):
     return cfg, T, B, sample
 
 
+def reference_package():
+    """The unmodified reference package installed by oracle/make_ref.py, or None."""
+    ref_dir = os.path.join(REPO, "oracle", "_ref")
+    if not os.path.isfile(os.path.join(ref_dir, "gru_qat", "__init__.py")):
+        return None
+    if ref_dir not in sys.path:
+        sys.path.insert(0, ref_dir)
+    import gru_qat
+    return gru_qat
+
+
 def cpu_step_fn(name):
+    """(step function, units per step, sample text, kind, what) for the CPU arm of config `name`."""
     from oracle import gru_scan_oracle as orc
     cfg, T, B, sample = cpu_problem(name)
     p = make_params(cfg)
-    quant = None
-    if cfg["quant"]:
-        s = calibrated_scale(cfg, p)
-        quant = ((s, -127, 127), (s, -127, 127))
+    scale = calibrated_scale(cfg, p) if cfg["quant"] else None
+    quant = ((scale, -127, 127), (scale, -127, 127)) if cfg["quant"] else None
     gen = torch.Generator().manual_seed(100)
     x = torch.randn(T, B, cfg["H"], generator=gen)
     h0 = torch.randn(B, cfg["H"], generator=gen) * cfg["h0_scale"]
     qi, qo = quant if quant else (None, None)
+    ref = reference_package()
+
+    if ref is not None and cfg["kind"] in ("dense", "diagonal"):
+        layer = build_layer(ref, cfg, p, scale, False)           # the reference's per-step PyTorch path
+
+        def step():
+            if cfg["train"]:
+                layer.zero_grad(set_to_none=True)
+                out, _ = layer(x, h0)
+                out.sum().backward()
+            else:
+                with torch.no_grad():
+                    layer(x, h0)
+        return step, T * B, sample, "reference", "gru_qat.GRULayer(use_triton=False) forward" + (
+            " + out.sum().backward()" if cfg["train"] else "")
+
+    if ref is not None and cfg["kind"] == "monarch":
+        from gru_qat.triton_kernels import scan_monarch as rm   # torch_structured is absent: scan-form functions
+        Wi, bi, W, bh = (p[k].clone().requires_grad_(True) for k in ("Wi", "bi", "W", "bh"))
+
+        def step():
+            gi = torch.nn.functional.linear(x, Wi, bi)
+            out = rm.gru_scan_monarch_forward_pytorch(gi.detach(), h0, W.detach(), bh.detach(), h_in_quant=qi,
+                                                      h_out_quant=qo)
+            dgi, _, _, _ = rm.gru_scan_monarch_backward_pytorch(gi.detach(), h0, W.detach(), bh.detach(), out,
+                                                                torch.ones_like(out), h_in_quant=qi, h_out_quant=qo)
+            gi.backward(dgi)
+        return step, T * B, sample, "reference", ("gru_qat gru_scan_monarch_forward_pytorch + _backward_pytorch "
+                                                  "(its cell needs the absent torch_structured) + F.linear autograd")
 
     def step():
         orc.layer_train_step(cfg["kind"], x, h0, p["Wi"], p["bi"], p["W"], p["bh"], qi, qo,
                              weight_bits=cfg["wbits"], backward=cfg["train"])
-    return step, T * B, sample
+    return step, T * B, sample, "port", "oracle.layer_train_step (the reference has no CPU path for this kind here)"
 
 
 def cpu_baseline(name, budget_s):
     torch.set_num_threads(os.cpu_count() or 1)
-    step, units, sample = cpu_step_fn(name)
+    step, units, sample, kind, what = cpu_step_fn(name)
     step()
     t0 = time.perf_counter()
     n = 0
@@ -439,8 +562,8 @@ def cpu_baseline(name, budget_s):
         if time.perf_counter() - t0 > budget_s or n >= 50:
             break
     dt = (time.perf_counter() - t0) / n
-    return {"value": units / dt, "unit": "seq-steps/s", "cores": torch.get_num_threads(), "kind": "port",
-            "ms_per_step": dt * 1e3, "sample": f"{sample}; {n} timed passes of oracle.layer_train_step"}
+    return {"value": units / dt, "unit": "seq-steps/s", "cores": torch.get_num_threads(), "kind": kind,
+            "ms_per_step": dt * 1e3, "sample": f"{sample}; {n} timed passes of {what}"}
 
 
 def run_reference(args):
@@ -449,7 +572,7 @@ def run_reference(args):
         return
     cfg = CONFIGS[args.config]
     torch.set_num_threads(os.cpu_count() or 1)
-    step, units, sample = cpu_step_fn(args.config)
+    step, units, sample, kind, what = cpu_step_fn(args.config)
     for _ in range(args.warmup):
         step()
     times = []
@@ -462,14 +585,16 @@ def run_reference(args):
     if args.gpus > 1:
         sample = sample.replace("the full workload", f"one rank's shard (1/{args.gpus} of the job; the host's "
                                 "throughput does not depend on how many shards it is given)")
+    world = args.gpus
+    B_per_gpu = cfg["B"] // world if args.config == "c5" else cfg["B"]
     print(json.dumps({
         "impl": "reference", "metric": "sequence-steps/sec (T*B/s)", "value": v, "unit": "seq-steps/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
         "higher_is_better": True, "scaling": "strong" if args.config == "c5" else "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"{args.config}: {cfg['desc']}", "hidden_kind": cfg["kind"]},
-        "cpu_baseline": {"value": v, "unit": "seq-steps/s", "cores": torch.get_num_threads(), "kind": "port",
-                         "sample": sample},
+        "config": config_dict(args.config, cfg, B_per_gpu, world, False),
+        "cpu_baseline": {"value": v, "unit": "seq-steps/s", "cores": torch.get_num_threads(), "kind": kind,
+                         "sample": f"{sample}; {what}"},
         "e2e": {"value": v, "unit": "seq-steps/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
 
@@ -486,6 +611,7 @@ def main():
     ap.add_argument("--B", type=int, default=0, help="override the batch, as --T")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-kinds", dest="kinds", action="store_false")
+    ap.add_argument("--no-c5", dest="c5", action="store_false", help="skip the config-5 record of the default run")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     if args.impl == "reference":
