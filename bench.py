@@ -137,7 +137,7 @@ def build_layer(pkg, cfg, params, scale, use_triton):
 # ---------------------------------------------------------------------------
 
 class DeviceWorkload:
-    def __init__(self, name, cfg, rank, world, dev, pinned=True):
+    def __init__(self, name, cfg, rank, world, dev, pinned=True, graph=True):
         import gru_triton_b200 as pkg
         from gru_triton_b200.data_parallel import GradBucket
         self.cfg, self.name, self.rank, self.world, self.dev = cfg, name, rank, world, dev
@@ -158,9 +158,17 @@ class DeviceWorkload:
         self.x, self.h0 = x.to(dev), h0.to(dev)
         del x, h0
         self.bucket = GradBucket(list(self.layer.parameters())) if (world > 1 and cfg["train"]) else None
+        # small problems are launch-bound: capture the whole step (forward, loss, backward) once
+        self.graphed = None
+        if graph and self.T * self.B <= 16384:
+            from gru_triton_b200 import _lib
+            from gru_triton_b200.graphed import GraphedStep
+            n0 = _lib.launch_count()
+            self.graphed = GraphedStep(self._body, [self.x, self.h0], warmup=3)
+            self.graph_launches = (_lib.launch_count() - n0) / 4      # 3 warm-up passes + the captured one
 
     # -- one pass of the hot path through the public API -----------------------
-    def step(self, x, h0):
+    def _body(self, x, h0):
         if not self.cfg["train"]:
             with torch.no_grad():
                 return self.layer(x, h0)[0]
@@ -168,9 +176,13 @@ class DeviceWorkload:
         out, _ = self.layer(x, h0)
         loss = out.sum()
         loss.backward()
+        return loss
+
+    def step(self, x, h0):
+        r = self.graphed(x, h0) if self.graphed is not None else self._body(x, h0)
         if self.bucket is not None:
             self.bucket.all_reduce()              # one flat NCCL all-reduce, gradients written back
-        return loss
+        return r
 
     def scan_only_forward(self):
         """The dominant kernel(s) in isolation: the forward scan on resident gi."""
@@ -335,7 +347,10 @@ def run_device(args):
     cfg = CONFIGS[args.config]
     if args.T or args.B:
         cfg = CONFIGS[args.config] = dict(cfg, T=args.T or cfg["T"], B=args.B or cfg["B"])
-    wl = DeviceWorkload(args.config, cfg, rank, world, dev)
+    wl = DeviceWorkload(args.config, cfg, rank, world, dev, graph=args.graph)
+    graph_note = ("the step (forward, loss, backward) is captured once by gru_triton_b200.graphed.GraphedStep and "
+                  "replayed; gpu_launches counts the kernels of the library inside one replay"
+                  if wl.graphed is not None else "not used")
     flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
 
     def flush():
@@ -360,6 +375,8 @@ def run_device(args):
     n0 = _lib.launch_count()
     ms = timed_loop(lambda: wl.step(wl.x, wl.h0), args.steps, args.warmup, flush, sync_all)
     launches_per_step = (_lib.launch_count() - n0) / (args.steps + args.warmup)
+    if wl.graphed is not None:
+        launches_per_step = wl.graph_launches        # kernels of the library inside one replay of the graph
     ms = max_over_ranks(ms)
     ms_per_step = sum(ms) / len(ms)
 
@@ -441,6 +458,7 @@ def run_device(args):
                 "h2d_bytes_per_step": h_bytes, "d2h_bytes_per_step": 4},
         "gpu_launches": int(round(launches_per_step * args.steps)),
         "gpu_launches_per_step": launches_per_step,
+        "cuda_graph": graph_note,
         "clocks": clocks,
         "roofline": roofline,
     }
@@ -612,6 +630,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-kinds", dest="kinds", action="store_false")
     ap.add_argument("--no-c5", dest="c5", action="store_false", help="skip the config-5 record of the default run")
+    ap.add_argument("--no-graph", dest="graph", action="store_false", help="issue the kernels of a step one by one")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     if args.impl == "reference":

@@ -1003,8 +1003,10 @@ extern "C" int b200gru_device_status(int reset) {
   }
   const int d = diag_read_status(reset);
   const int f = bfly_read_status(reset);
-  if (d < 0 || f < 0) return -1;
-  return (v != 0 || d != 0 || f != 0) ? 1 : 0;
+  const int g = tc::tc_read_status(reset);
+  const int s = tc::tc_step_read_status(reset);
+  if (d < 0 || f < 0 || g < 0 || s < 0) return -1;
+  return (v != 0 || d != 0 || f != 0 || g != 0 || s != 0) ? 1 : 0;
 }
 
 }  // namespace b200gru

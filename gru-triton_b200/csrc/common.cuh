@@ -163,6 +163,10 @@ __host__ __device__ inline int cdiv(int a, int b) { return (a + b - 1) / b; }
 // Health flag of the diagonal kernels' bounded waits (diag_scan.cu); -1 on CUDA error.
 int diag_read_status(int reset);
 int bfly_read_status(int reset);     // same for the staged butterfly kernels (butterfly_scan2.cu)
+namespace tc {
+int tc_read_status(int reset);       // tensor-core GEMM core (tc_gemm.cu)
+int tc_step_read_status(int reset);  // fused tensor-core step (tc_step.cu)
+}  // namespace tc
 
 // Launch bookkeeping shared by all translation units (defined in api.cu).
 void note_launch(int n = 1);

@@ -90,6 +90,15 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
         "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
       : "r"(taddr) : "memory");
 }
+// 32 lanes x 16 consecutive columns.
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+      : "r"(taddr) : "memory");
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // ---- UMMA descriptors --------------------------------------------------------------------------
@@ -145,9 +154,9 @@ int make_tensor_map_3d(CUtensorMap* map, CUtensorMapDataType dtype, const void* 
                        unsigned long long d1, unsigned long long d2, unsigned long long stride1_bytes,
                        unsigned long long stride2_bytes, unsigned box0, unsigned box1);
 
-// Device-wide health word of the tcgen05 kernels (tc_gemm.cu); -1 on CUDA error.
+// Device-wide health words of the tcgen05 kernels (tc_gemm.cu, tc_step.cu); -1 on CUDA error.
 int tc_read_status(int reset);
-int* tc_status_word();
+int tc_step_read_status(int reset);
 
 }  // namespace tc
 }  // namespace b200gru

@@ -29,6 +29,7 @@
 #include "butterfly_scan.cuh"
 #include "tc_gemm.cuh"
 #include "tc_scan.cuh"
+#include "tc_step.cuh"
 
 namespace b200gru {
 namespace tc {
@@ -400,6 +401,20 @@ int launch_tc_dense_forward(const float* gi, const float* h0, const TcWeights& w
   int rc = check_launch("h0_operand_kernel");
   if (rc) return rc;
 
+  if (p.i8) {
+    // both operands are integer codes: one fused kernel per step (product + gates + next codes)
+    FusedFwd f;
+    rc = f.init(w.codes, reinterpret_cast<signed char*>(op[0]), reinterpret_cast<signed char*>(op[1]), B, H);
+    if (rc) return rc;
+    for (int t = 0; t < T; ++t) {
+      rc = f.step(t, T, t & 1, gi, (t == 0) ? h0 : out + (size_t)(t - 1) * B * H, w.row_scale, bh,
+                  out + (size_t)t * B * H, save,
+                  (t + 1 < T) ? reinterpret_cast<signed char*>(op[(t + 1) & 1]) : nullptr, qin.scale, qin, qout, st);
+      if (rc) return rc;
+    }
+    return check_launch("tc_fwd_step_kernel");
+  }
+
   TcGemm g;
   memset(&g, 0, sizeof(g));
   g.kind = p.i8 ? TC_KIND_I8 : TC_KIND_BF16;
@@ -479,7 +494,15 @@ int launch_tc_dense_backward(const float* h0, const TcWeights& w, const float* o
   gw.M = 3 * H; gw.N = H;
   gw.A = dgh_op; gw.B = h_op; gw.a_planes = 3; gw.b_planes = hpl; gw.a_mn = 1; gw.b_mn = 1;
   gw.lda = 3 * H; gw.ldb = H; gw.a_plane_stride = (long long)rows * 3 * H; gw.b_plane_stride = (long long)rows * H;
-  gw.npairs = fill_pairs(3, hpl, gw.pa, gw.pb);
+  // Weight gradients are held to 1e-4 of their largest entry: the two leading planes of each fp32
+  // operand (16 mantissa bits) and the cross products down to 2^-16 are enough (error about 1e-5 of
+  // a term, averaged over rows * B terms); the chain product above keeps all three planes.
+  gw.npairs = 0;
+  for (int s2 = 0; s2 <= 1; ++s2)
+    for (int i = 0; i <= s2; ++i) {
+      const int j = s2 - i;
+      if (j < hpl) { gw.pa[gw.npairs] = i; gw.pb[gw.npairs] = j; ++gw.npairs; }
+    }
   gw.tile_n = 256;
   if (2 * (3 * 16384 + hpl * 256 * 128) > TC_SMEM_BUDGET) gw.tile_n = 128;
   gw.alpha = (w.row_scale != nullptr) ? 1.0f : h_scale;

@@ -1,0 +1,272 @@
+// Fused forward step of the dense QAT scan on the tensor cores (sm_100a).
+//
+// When weights and hidden state are both int8 codes, one kernel does a whole time step:
+//
+//   acc[b, (g,u)] = sum_k codes_h[b,k] * codes_W[(g,u),k]        tcgen05.mma kind::i8, int32, exact
+//   gh = acc * (s_h * s_row[(g,u)]) + bh ;  r, z, n gates ;  h_t = fq_out((1-z) n + z h_{t-1})
+//   out[t], save[r,z,n,gh_n], and the int8 codes of fq_in(h_t) for the next step
+//
+// CTA tile = 128 batch rows x 32 hidden units x 3 gates: the B operand of the MMA is the three
+// 32-row slabs W[g*H + u0 .. +32, :] stacked to N = 96, so that the r, z and n pre-activations of
+// one (row, unit) sit in the same tensor-memory lane and the gate math needs no exchange between
+// threads.  Warp 0 loads k-blocks by TMA (the weight slabs of the first stages before the
+// programmatic-dependency wait: they do not depend on the previous step), warp 1 issues the
+// MMAs, warps 2-9 prefetch gi[t] and h_{t-1} for their (row, 16 units), then read the accumulator
+// and run the gate epilogue.  One launch per step; the stream order is the recurrence.
+//
+// Reference: the per-step body of gru_scan_fwd_persistent_kernel
+// (src/gru_qat/triton_kernels/scan.py:120-184), with tl.dot replaced by an exact integer product.
+
+#include <cstring>
+#include <mutex>
+#include <set>
+#include <utility>
+
+#include "tc_common.cuh"
+#include "tc_step.cuh"
+
+namespace b200gru {
+namespace tc {
+
+__device__ int g_tc_step_status;
+
+namespace {
+
+constexpr int FS_BM = 128;          // batch rows per CTA
+constexpr int FS_UNITS = 32;        // hidden units per CTA
+constexpr int FS_BN = 3 * FS_UNITS; // MMA N
+constexpr int FS_KB = 128;          // int8 elements of K per stage
+constexpr int FS_A_BYTES = FS_BM * FS_KB;            // 16 KB
+constexpr int FS_B_SLAB = FS_UNITS * FS_KB;          // 4 KB per gate
+constexpr int FS_STAGE = FS_A_BYTES + 3 * FS_B_SLAB; // 28 KB
+constexpr int FS_MAX_STAGES = 8;
+constexpr int FS_EPI_WARPS = 8;
+constexpr int FS_THREADS = 64 + 32 * FS_EPI_WARPS;
+
+struct FusedFwdArgs {
+  const float* gi;       // [T][B][3H]
+  const float* h_prev;   // [B][H]
+  const float* col_scale;  // [3H] row scales of the weight codes
+  const float* bh;       // [3H]
+  float* out_t;          // [B][H]
+  float* save;           // [4][T][B][H] or NULL
+  signed char* codes_next;   // [B][H] or NULL
+  int t, T, B, H;
+  int nkb, stages;
+  float alpha;           // scale of the hidden codes
+  Quant qin, qout;
+};
+
+__global__ void __launch_bounds__(FS_THREADS, 1)
+tc_fwd_step_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                   const FusedFwdArgs a) {
+  constexpr uint32_t IDESC = umma_idesc(true, false, false, FS_BM, FS_BN);
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  __shared__ __align__(8) unsigned long long bar_full[FS_MAX_STAGES], bar_empty[FS_MAX_STAGES], bar_acc;
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int dead;
+  __shared__ float s_scale[FS_BN], s_bias[FS_BN];
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int u0 = blockIdx.x * FS_UNITS, m0 = blockIdx.y * FS_BM;
+  const int H = a.H;
+  int* status = &g_tc_step_status;
+
+  if (threadIdx.x == 0) {
+    dead = (*reinterpret_cast<volatile int*>(status) != 0) ? 1 : 0;
+    for (int s = 0; s < a.stages; ++s) {
+      mbar_init(smem_u32(&bar_full[s]), 1);
+      mbar_init(smem_u32(&bar_empty[s]), 1);
+    }
+    mbar_init(smem_u32(&bar_acc), 1);
+    mbar_fence_init();
+    tma_prefetch_map(&tmA);
+    tma_prefetch_map(&tmB);
+  }
+  if (threadIdx.x >= 64 && threadIdx.x < 64 + FS_BN) {
+    const int c = threadIdx.x - 64, g = c / FS_UNITS, j = c - g * FS_UNITS;
+    s_scale[c] = a.alpha * a.col_scale[g * H + u0 + j];
+    s_bias[c] = a.bh[g * H + u0 + j];
+  }
+  if (warp == 1) tmem_alloc(smem_u32(&tmem_base_slot), 128);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_acc = tmem_base_slot;
+  volatile int* deadp = &dead;
+
+  if (warp == 0) {
+    if (lane == 0 && !*deadp) {
+      for (int i = 0; i < a.nkb; ++i) {
+        const int s = i % a.stages, round = i / a.stages;
+        if (round > 0 && !mbar_wait(smem_u32(&bar_empty[s]), (round - 1) & 1, deadp, status)) break;
+        const uint32_t full = smem_u32(&bar_full[s]);
+        mbar_expect_tx(full, FS_STAGE);
+        unsigned char* st = smem + (size_t)s * FS_STAGE;
+#pragma unroll
+        for (int g = 0; g < 3; ++g)
+          tma_load_3d(smem_u32(st + FS_A_BYTES + g * FS_B_SLAB), &tmB, i * FS_KB, g * H + u0, 0, full);
+        tma_load_3d(smem_u32(st), &tmA, i * FS_KB, m0, 0, full);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && !*deadp) {
+      bool alive = true;
+      for (int i = 0; i < a.nkb && alive; ++i) {
+        const int s = i % a.stages, round = i / a.stages;
+        if (!mbar_wait(smem_u32(&bar_full[s]), round & 1, deadp, status)) { alive = false; break; }
+        tc_fence_after();
+        const uint32_t sa = smem_u32(smem + (size_t)s * FS_STAGE);
+        const uint32_t sb = sa + FS_A_BYTES;
+#pragma unroll
+        for (int kk = 0; kk < FS_KB / 32; ++kk)
+          umma<true>(tmem_acc, umma_smem_desc(sa + kk * 32, 16, 1024), umma_smem_desc(sb + kk * 32, 16, 1024), IDESC,
+                     (i > 0 || kk > 0) ? 1u : 0u);
+        umma_commit(smem_u32(&bar_empty[s]));
+      }
+      if (alive) umma_commit(smem_u32(&bar_acc));
+    }
+  } else {
+    // ---- epilogue: thread = (batch row, 16 units)
+    const int q = warp & 3, half = (warp - 2) >> 2;
+    const int b = m0 + q * 32 + lane;
+    const int ub = half * 16;                       // first unit of this thread inside the CTA's 32
+    const bool rowok = b < a.B;
+    const size_t o = (size_t)(rowok ? b : 0) * H + u0 + ub;
+    float gi_r[16], gi_z[16], gi_n[16], hp[16];
+    {
+      const float* g = a.gi + ((size_t)a.t * a.B + (rowok ? b : 0)) * 3 * H + u0 + ub;
+#pragma unroll
+      for (int j = 0; j < 16; j += 4) {
+        const float4 vr = __ldcs(reinterpret_cast<const float4*>(g + j));
+        const float4 vz = __ldcs(reinterpret_cast<const float4*>(g + H + j));
+        const float4 vn = __ldcs(reinterpret_cast<const float4*>(g + 2 * H + j));
+        const float4 vh = *reinterpret_cast<const float4*>(a.h_prev + o + j);
+        gi_r[j] = vr.x; gi_r[j + 1] = vr.y; gi_r[j + 2] = vr.z; gi_r[j + 3] = vr.w;
+        gi_z[j] = vz.x; gi_z[j + 1] = vz.y; gi_z[j + 2] = vz.z; gi_z[j + 3] = vz.w;
+        gi_n[j] = vn.x; gi_n[j + 1] = vn.y; gi_n[j + 2] = vn.z; gi_n[j + 3] = vn.w;
+        hp[j] = vh.x; hp[j + 1] = vh.y; hp[j + 2] = vh.z; hp[j + 3] = vh.w;
+      }
+    }
+    bool ok = mbar_wait(smem_u32(&bar_acc), 0, deadp, status);
+    ok = __all_sync(0xffffffffu, ok);
+    tc_fence_after();
+    uint32_t ar[16], az[16], an[16];
+    if (ok) {
+      const uint32_t tsrc = tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)ub;
+      tmem_ld16(tsrc, ar);
+      tmem_ld16(tsrc + FS_UNITS, az);
+      tmem_ld16(tsrc + 2 * FS_UNITS, an);
+      tmem_ld_wait();
+    } else {
+#pragma unroll
+      for (int j = 0; j < 16; ++j) { ar[j] = 0u; az[j] = 0u; an[j] = 0u; }
+    }
+    if (rowok) {
+      const size_t comp = (size_t)a.T * a.B * H, so = (size_t)a.t * a.B * H + o;
+      uint32_t cw[4];
+#pragma unroll
+      for (int j4 = 0; j4 < 16; j4 += 4) {
+        float hn[4], rr[4], zz[4], nn[4], gg[4];
+        uint32_t packed = 0;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int j = j4 + e, c = ub + j;
+          const float ghr = (float)(int)ar[j] * s_scale[c] + s_bias[c];
+          const float ghz = (float)(int)az[j] * s_scale[FS_UNITS + c] + s_bias[FS_UNITS + c];
+          const float ghn = (float)(int)an[j] * s_scale[2 * FS_UNITS + c] + s_bias[2 * FS_UNITS + c];
+          const GateOut go = gru_gates(gi_r[j], gi_z[j], gi_n[j], ghr, ghz, ghn, hp[j]);
+          rr[e] = go.r; zz[e] = go.z; nn[e] = go.n; gg[e] = ghn;
+          hn[e] = a.qout.enabled ? fake_quant<true>(go.h_raw, a.qout) : go.h_raw;
+          const float code = fminf(fmaxf(fq_code(hn[e], a.qin), a.qin.qmin), a.qin.qmax);
+          packed |= ((uint32_t)(int)code & 0xffu) << (8 * e);
+        }
+        cw[j4 >> 2] = packed;
+        *reinterpret_cast<float4*>(a.out_t + o + j4) = make_float4(hn[0], hn[1], hn[2], hn[3]);
+        if (a.save != nullptr) {
+          __stcs(reinterpret_cast<float4*>(a.save + so + j4), make_float4(rr[0], rr[1], rr[2], rr[3]));
+          __stcs(reinterpret_cast<float4*>(a.save + comp + so + j4), make_float4(zz[0], zz[1], zz[2], zz[3]));
+          __stcs(reinterpret_cast<float4*>(a.save + 2 * comp + so + j4), make_float4(nn[0], nn[1], nn[2], nn[3]));
+          __stcs(reinterpret_cast<float4*>(a.save + 3 * comp + so + j4), make_float4(gg[0], gg[1], gg[2], gg[3]));
+        }
+      }
+      if (a.codes_next != nullptr)
+        *reinterpret_cast<uint4*>(a.codes_next + o) = make_uint4(cw[0], cw[1], cw[2], cw[3]);
+    }
+  }
+
+  if (warp == 0 && lane == 0 && *deadp) {        // a CTA that gave up: let tile copies in flight land
+    const long long start = clock64();
+    while (clock64() - start < (1ll << 18)) {
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_acc, 128);
+  }
+}
+
+int prepare_once(const void* kernel, int smem) {
+  static std::mutex mu;
+  static std::set<std::pair<int, const void*>> done;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0) return B200GRU_LAUNCH_FAILURE;
+  std::lock_guard<std::mutex> lk(mu);
+  const auto key = std::make_pair(dev, kernel);
+  if (done.count(key) == 0) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+      return check_launch("cudaFuncSetAttribute(tc_fwd_step_kernel)");
+    done.insert(key);
+  }
+  return B200GRU_OK;
+}
+
+}  // namespace
+
+int tc_step_read_status(int reset) {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_tc_step_status, sizeof(int)) != cudaSuccess) return -1;
+  if (reset && v != 0) {
+    const int z = 0;
+    cudaMemcpyToSymbol(g_tc_step_status, &z, sizeof(int));
+  }
+  return v;
+}
+
+int FusedFwd::init(const signed char* w_codes, signed char* h_codes0, signed char* h_codes1, int B_, int H_) {
+  B = B_; H = H_;
+  int rc = make_tensor_map_3d(&mapW, CU_TENSOR_MAP_DATA_TYPE_UINT8, w_codes, H, 3ull * H, 1, H, 3ull * H * H, FS_KB,
+                              FS_UNITS);
+  if (rc) return rc;
+  signed char* bufs[2] = {h_codes0, h_codes1};
+  for (int i = 0; i < 2; ++i) {
+    rc = make_tensor_map_3d(&mapH[i], CU_TENSOR_MAP_DATA_TYPE_UINT8, bufs[i], H, B, 1, H, (unsigned long long)B * H,
+                            FS_KB, FS_BM);
+    if (rc) return rc;
+  }
+  nkb = cdiv(H, FS_KB);
+  stages = nkb < 7 ? nkb : 7;
+  smem = stages * FS_STAGE + 1024;
+  return prepare_once(reinterpret_cast<const void*>(tc_fwd_step_kernel), FS_MAX_STAGES * FS_STAGE + 1024);
+}
+
+int FusedFwd::step(int t, int T, int src, const float* gi, const float* h_prev, const float* col_scale,
+                   const float* bh, float* out_t, float* save, signed char* codes_next, float alpha, Quant qin,
+                   Quant qout, cudaStream_t st) const {
+  FusedFwdArgs a;
+  memset(&a, 0, sizeof(a));
+  a.gi = gi; a.h_prev = h_prev; a.col_scale = col_scale; a.bh = bh; a.out_t = out_t; a.save = save;
+  a.codes_next = codes_next; a.t = t; a.T = T; a.B = B; a.H = H; a.nkb = nkb; a.stages = stages;
+  a.alpha = alpha; a.qin = qin; a.qout = qout;
+  const dim3 grid(H / FS_UNITS, cdiv(B, FS_BM));
+  tc_fwd_step_kernel<<<grid, FS_THREADS, smem, st>>>(mapH[src], mapW, a);
+  note_launch();
+  return B200GRU_OK;
+}
+
+}  // namespace tc
+}  // namespace b200gru

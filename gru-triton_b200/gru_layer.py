@@ -28,11 +28,22 @@ _FAST_KINDS = ("diagonal", "monarch", "butterfly")
 
 def _extract_h_quant_params(quantizer: FakeQuantize):
     """``(scale, qmin, qmax)`` if the quantizer is frozen, per-tensor and symmetric --
-    the only form the scan kernels apply -- else None (gru_layer.py:30-48)."""
+    the only form the scan kernels apply -- else None (gru_layer.py:30-48).
+
+    The reference reads the scale with ``.item()`` at every forward (a device-to-host sync);
+    here the host copy is kept beside the quantizer and re-read only when the scale tensor was
+    replaced or written, so a frozen layer's forward neither synchronises nor breaks a CUDA-graph
+    capture."""
     cfg = quantizer.config
     if cfg.mode != "frozen" or not isinstance(quantizer, FakeQuantizePerTensor) or not cfg.symmetric:
         return None
-    return float(quantizer.scale.item()), int(quantizer.qmin), int(quantizer.qmax)
+    scale = quantizer.scale
+    key = (id(scale), scale._version, scale.device)
+    cached = getattr(quantizer, "_host_scale", None)
+    if cached is None or cached[0] != key:
+        cached = (key, float(scale.item()))
+        quantizer._host_scale = cached
+    return cached[1], int(quantizer.qmin), int(quantizer.qmax)
 
 
 class GRULayer(nn.Module):

@@ -171,11 +171,13 @@ class _LinearFunction(torch.autograd.Function):
             dWq = torch.zeros((splits, N, I), device=x.device, dtype=torch.float32)
         for r0 in range(0, R, ROW_CHUNK):
             r1 = min(R, r0 + ROW_CHUNK)
-            dyp = split_bf16(dy[r0:r1])
+            dyp = split_bf16(dy[r0:r1], planes=3 if need_x else 2)
             if need_w:
-                xp = split_bf16(x[r0:r1])
+                # weight gradients are held to 1e-4 of their largest entry: two planes per operand and
+                # the cross products down to 2^-16 (error about 1e-5 of a term, averaged over the rows)
+                xp = split_bf16(x[r0:r1], planes=2)
                 k_splits = gemm_splits(N, I, r1 - r0, dWq.shape[0])
-                gemm(dyp, xp, a_mn=True, b_mn=True, pairs=PAIRS_FULL, split_k=k_splits, out=dWq, accumulate=True,
+                gemm(dyp[:2], xp, a_mn=True, b_mn=True, pairs=PAIRS_FAST, split_k=k_splits, out=dWq, accumulate=True,
                      reduce_splits=False)
             if need_x:
                 # dx = dy @ fq(W): W rows are the contraction index (MN-major B)
