@@ -399,6 +399,7 @@ def run_device(args):
     scan_launches = (_lib.launch_count() - n1) / (max(min(args.steps, 20), 5) + 3)
     k_ms = statistics.median(ks)
     clocks = sampler.stop() if sampler else None
+    _lib.check_device_status()        # no bounded wait inside a kernel gave up during the timed loops
 
     peaks = load_peaks()
     c5 = None

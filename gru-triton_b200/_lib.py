@@ -75,6 +75,8 @@ SIGNATURES = {
     "b200gru_tc_gemm_splits": (_I, [_GP, _I]),
     "b200gru_split_bf16": (_I, [_P, _P, _Z, _Z, _I, _P, _I, _P]),
     "b200gru_device_status": (_I, [_I]),
+    "b200gru_test_select_kernels": (None, [_I, _I]),
+    "b200gru_test_wait_timeout": (_I, [_P]),
     "b200gru_launch_count": (ctypes.c_ulonglong, []),
     "b200gru_strerror": (ctypes.c_char_p, [_I]),
     "b200gru_last_cuda_error": (ctypes.c_char_p, []),
@@ -102,6 +104,31 @@ def load() -> ctypes.CDLL:
                 fn.restype, fn.argtypes = res, args
             _lib = lib
     return _lib
+
+
+class DeviceWaitTimeout(RuntimeError):
+    """A bounded in-kernel wait gave up: the results of the launches since the last check are invalid."""
+
+
+def check_device_status(reset: bool = True) -> None:
+    """Synchronise the current device and raise :class:`DeviceWaitTimeout` if any kernel of the
+    library reported that one of its bounded waits ran out (``b200gru_device_status``)."""
+    st = load().b200gru_device_status(1 if reset else 0)
+    if st > 0:
+        raise DeviceWaitTimeout("a bounded wait inside a b200gru kernel gave up (peer CTA, bulk copy or tensor-core "
+                                "pipeline never delivered); results since the last check are invalid")
+    if st < 0:
+        raise RuntimeError("b200gru_device_status: CUDA error " + load().b200gru_last_cuda_error().decode())
+
+
+# B200GRU_CHECK_STATUS=1: check the health word after every scan call (synchronises: a debugging aid).
+# Without it the word is checked where the wrappers synchronise anyway (GRULayer.calibrate) and on demand.
+_EAGER_STATUS = os.environ.get("B200GRU_CHECK_STATUS", "0") not in ("", "0")
+
+
+def _after_call() -> None:
+    if _EAGER_STATUS:
+        check_device_status()
 
 
 def _cquant(q: Quant) -> CQuant:
@@ -196,6 +223,7 @@ def scan_forward(kind: str, gi, h0, W, bh, h_in_quant: Quant, h_out_quant: Quant
                                           0 if ws is None else ws.numel(), ctypes.c_void_p(stream))
     if rc:
         _raise(rc, f"{kind} scan forward")
+    _after_call()
     return out, save
 
 
@@ -226,4 +254,5 @@ def scan_backward(kind: str, gi, h0, W, bh, out, dout, save, h_in_quant: Quant, 
                                            0 if ws is None else ws.numel(), ctypes.c_void_p(stream))
     if rc:
         _raise(rc, f"{kind} scan backward")
+    _after_call()
     return dgi, dh0, dW, dbh

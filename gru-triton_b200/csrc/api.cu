@@ -20,6 +20,9 @@ int diag_backward(const float* gi, const float* h0, const float* W, const float*
                   int B, int H, Quant qi, Quant qo, cudaStream_t st);
 
 static std::atomic<unsigned long long> g_launches{0};
+static std::atomic<int> g_test_choice[2] = {{0}, {0}};
+
+int test_kernel_choice(int slot) { return (slot >= 0 && slot < 2) ? g_test_choice[slot].load(std::memory_order_relaxed) : 0; }
 static thread_local char g_last_error[256] = {0};
 
 void note_launch(int n) { g_launches.fetch_add((unsigned long long)n, std::memory_order_relaxed); }
@@ -412,6 +415,11 @@ int b200gru_dense_q8_backward(const float* gi, const float* h0, const float* Wq,
   const b200gru_shape s = mk_shape(B200GRU_DENSE, T, B, H, 1, 0);
   return scan_backward_impl(&s, gi, h0, Wq, codes, scales, bh_cat, out, dout, save, q_in, q_out, dgi, dh0, dWq, dbh,
                             workspace, workspace_bytes_, stream);
+}
+
+void b200gru_test_select_kernels(int butterfly_register_kernels, int diagonal_register_ring) {
+  g_test_choice[0].store(butterfly_register_kernels, std::memory_order_relaxed);
+  g_test_choice[1].store(diagonal_register_ring, std::memory_order_relaxed);
 }
 
 unsigned long long b200gru_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }

@@ -15,15 +15,16 @@
 //   a warp owns 4 output units x 3 gates; its lanes split the contraction index k, each
 //   lane reading one float4 of weights per gate and the BT hidden values of its k; a
 //   halving shuffle reduction leaves lane (b, unit) with the three gate sums of its
-//   element, which then does the gate math in place.  Each CTA publishes its slice of
-//   fq_in(h_t) into the shared memory of all C peers (DSMEM float4 stores); one hardware
-//   cluster barrier ends the step.
+//   element, which then does the gate math in place and publishes fq_in(h_t) into the shared
+//   memory of all C peers with st.async, which also counts the bytes on the consumer's mbarrier;
+//   a consumer starts step t+1 when the bytes of step t have arrived.  No cluster barrier inside
+//   the time loop (two per launch: start and end).
 //
 // Backward step ("reduce-scatter"), only dh_via = dgh . W is on the dependence chain:
 //   gate gradients of the owned elements -> local partial products against the SAME
 //   weight rows, for all Hb input positions -> each CTA sends the part that belongs to
-//   peer r into r's receive buffer (DSMEM) -> cluster barrier -> the owner adds the C
-//   partials in rank order.
+//   peer r into r's receive buffer (st.async + the receiver's mbarrier) -> the owner waits for
+//   the bytes and adds the C partials in rank order.
 //
 // The gate recompute for the backward (one big GEMM over all t, since every h_t is
 // known) and the weight-gradient GEMM are off the chain and live in block_gemm.cu.

@@ -168,6 +168,11 @@ int tc_read_status(int reset);       // tensor-core GEMM core (tc_gemm.cu)
 int tc_step_read_status(int reset);  // fused tensor-core step (tc_step.cu)
 }  // namespace tc
 
+// Test hook (b200gru_test_select_kernels): slot 0 != 0 -> butterfly launches use the register /
+// global-twiddle kernels on every shape; slot 1 != 0 -> the diagonal forward uses the register-ring
+// kernel on every shape.  Defaults 0: the dispatch is by shape only.
+int test_kernel_choice(int slot);
+
 // Launch bookkeeping shared by all translation units (defined in api.cu).
 void note_launch(int n = 1);
 int check_launch(const char* what);

@@ -395,10 +395,6 @@ diag_bwd_kernel(const float* __restrict__ gi, const float* __restrict__ h0,
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 static int pick_vec(int B, int H, bool ptr_ok) {
-  if (const char* e = getenv("B200GRU_DIAG_VEC")) {          // tuning override
-    const int v = atoi(e);
-    if ((v == 1) || (v == 2 && ptr_ok && H % 2 == 0) || (v == 4 && ptr_ok && H % 4 == 0)) return v;
-  }
   // Prefer the widest vector that still leaves enough threads to fill the machine.
   const long long chains = (long long)B * H;
   const long long want_threads = 148LL * 512;
@@ -429,7 +425,7 @@ static void launch_fwd(const float* gi, const float* h0, const float* W, const f
 int diag_forward(const float* gi, const float* h0, const float* W, const float* bh, float* out,
                  int T, int B, int H, Quant qi, Quant qo, cudaStream_t st) {
   const bool ok = aligned16(gi) && aligned16(h0) && aligned16(W) && aligned16(bh) && aligned16(out);
-  static const bool no_tma = getenv("B200GRU_DIAG_NO_TMA") != nullptr;       // tuning override
+  const bool no_tma = test_kernel_choice(1) != 0;       // test hook: register-ring kernel on every shape
   if (!no_tma && ok && H % 4 == 0 && T >= DT_STAGES && (long long)B * H >= 65536 && B <= 65535) {
     // 128 threads x 2 units: the best of the (units per thread, threads) shapes measured on B200
     constexpr int V = 2, N = 128;
@@ -470,6 +466,7 @@ int diag_backward(const float* gi, const float* h0, const float* W, const float*
                   const float* out, const float* dout, float* dgi, float* dh0, float* dW, float* dbh,
                   void* workspace, int T, int B, int H, Quant qi, Quant qo, cudaStream_t st) {
   float* partial = static_cast<float*>(workspace);
+  if (cdiv(B, DIAG_BY) > 65535) return B200GRU_UNSUPPORTED;        // grid.y of the backward kernel
   const bool ok = aligned16(gi) && aligned16(h0) && aligned16(W) && aligned16(bh) && aligned16(out) &&
                   aligned16(dout) && aligned16(dgi) && aligned16(dh0) && aligned16(partial);
   const int vec = pick_vec(B, H, ok);
@@ -507,7 +504,11 @@ static int noalloc_scratch_address(float** out) {
   std::lock_guard<std::mutex> lk(mu);
   if (table[dev] == nullptr) {
     void* p = nullptr;
-    if (cudaGetSymbolAddress(&p, g_noalloc_scratch) != cudaSuccess || p == nullptr) return check_launch("cudaGetSymbolAddress");
+    if (cudaGetSymbolAddress(&p, g_noalloc_scratch) != cudaSuccess) {
+      check_launch("cudaGetSymbolAddress");                 // records the CUDA error text
+      return B200GRU_LAUNCH_FAILURE;
+    }
+    if (p == nullptr) return B200GRU_LAUNCH_FAILURE;
     table[dev] = static_cast<float*>(p);
   }
   *out = table[dev];
@@ -528,6 +529,7 @@ extern "C" int b200gru_diagonal_backward_noalloc(const float* gi, const float* h
   if (q_in && q_in->enabled && !(q_in->scale > 0.f)) return B200GRU_INVALID_ARGUMENT;
   if (q_out && q_out->enabled && !(q_out->scale > 0.f)) return B200GRU_INVALID_ARGUMENT;
   if (diag_bwd_workspace_bytes(T, B, H) > (size_t)B200GRU_NOALLOC_SCRATCH_BYTES) return B200GRU_SCRATCH_EXCEEDED;
+  if (cdiv(B, DIAG_BY) > 65535) return B200GRU_UNSUPPORTED;        // grid.y of the backward kernel
   float* scratch = nullptr;
   const int rc = noalloc_scratch_address(&scratch);
   if (rc) return rc;

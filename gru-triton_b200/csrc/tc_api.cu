@@ -53,4 +53,8 @@ int b200gru_split_bf16(const float* src, void* dst, size_t n, size_t plane_strid
                                  static_cast<cudaStream_t>(stream));
 }
 
+int b200gru_test_wait_timeout(void* stream) {
+  return tc::launch_wait_timeout_probe(static_cast<cudaStream_t>(stream));
+}
+
 }  // extern "C"

@@ -278,6 +278,23 @@ split_planes_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ d
   }
 }
 
+// Test probe of the bounded waits: one CTA arms an mbarrier for bytes that nothing ever sends and
+// waits on it with a budget of about a millisecond; the wait gives up, sets the health word and
+// the kernel returns normally.
+__global__ void wait_timeout_probe_kernel(long long budget_cycles) {
+  __shared__ __align__(8) unsigned long long bar;
+  if (threadIdx.x != 0) return;
+  mbar_init(smem_u32(&bar), 1);
+  mbar_fence_init();
+  mbar_expect_tx(smem_u32(&bar), 16);
+  const long long start = clock64();
+  bool ok = false;
+  while (clock64() - start < budget_cycles) {
+    if (mbar_try_wait(smem_u32(&bar), 0)) { ok = true; break; }
+  }
+  if (!ok) atomicExch(&g_tc_status, 1);
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -354,6 +371,12 @@ int make_tensor_map_3d(CUtensorMap* map, CUtensorMapDataType dtype, const void* 
                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? B200GRU_OK : B200GRU_INVALID_ARGUMENT;
+}
+
+int launch_wait_timeout_probe(cudaStream_t st) {
+  wait_timeout_probe_kernel<<<1, 32, 0, st>>>(1ll << 21);
+  note_launch();
+  return check_launch("wait_timeout_probe_kernel");
 }
 
 int tc_read_status(int reset) {

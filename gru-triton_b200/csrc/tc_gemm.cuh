@@ -48,6 +48,9 @@ int tc_gemm_splits(const TcGemm& g, int want);
 int tc_gemm_tile_n(const TcGemm& g);
 int launch_tc_gemm(const TcGemm& g, cudaStream_t st);
 
+// Launches the bounded-wait probe (a wait that must run out); sets the tensor-core health word.
+int launch_wait_timeout_probe(cudaStream_t st);
+
 // dst[pl][i] (bf16, planes `plane_stride` elements apart) = pl-th term of src[i] * col_scale[i % ncols];
 // n % 4 == 0; col_scale may be NULL.
 int launch_split_planes(const float* src, void* dst, size_t n, size_t plane_stride, int planes,

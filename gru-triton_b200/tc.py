@@ -165,9 +165,11 @@ class _LinearFunction(torch.autograd.Function):
         dWq = None
         if need_w:
             chunk_rows = min(R, ROW_CHUNK)
-            # enough K slices to cover the GPU with (N/128) x (I/256) tiles
+            # K slices: about two waves of (N/128) x (I/256) tiles over the 148 SMs when the contraction
+            # is long, one wave when each slice would otherwise be only a few k-blocks
             tiles = -(-N // 128) * -(-I // 256)
-            splits = gemm_splits(N, I, chunk_rows, 1 if tiles >= 120 else -(-280 // tiles))
+            want = 1 if tiles >= 120 else -(-(280 if chunk_rows >= 16384 else 140) // tiles)
+            splits = gemm_splits(N, I, chunk_rows, max(1, min(want, chunk_rows // 512)))
             dWq = torch.zeros((splits, N, I), device=x.device, dtype=torch.float32)
         for r0 in range(0, R, ROW_CHUNK):
             r1 = min(R, r0 + ROW_CHUNK)

@@ -270,6 +270,17 @@ unsigned long long b200gru_launch_count(void);
  * (scan.py:202-205). */
 int b200gru_device_status(int reset);
 
+/* ---- test hooks (no reference counterpart; not for production callers) ------------------------
+ * b200gru_test_select_kernels: the library keeps two kernels for some problems and picks by
+ * shape; a non-zero argument makes the butterfly launches use the register / global-twiddle
+ * kernels, resp. the diagonal forward use its register-ring kernel, on every shape, so that the
+ * tests can hold both to the same parity bar.  Process-wide; (0, 0) restores the normal dispatch.
+ * b200gru_test_wait_timeout: launches one tiny kernel whose bounded wait must run out (it waits
+ * about a millisecond for bytes nothing sends), which sets the flag b200gru_device_status
+ * reports; the kernel returns normally and the device stays usable. */
+void b200gru_test_select_kernels(int butterfly_register_kernels, int diagonal_register_ring);
+int b200gru_test_wait_timeout(void* stream);
+
 /* Human-readable text for a b200gru_status; plus the text of the last CUDA error
  * seen by a launch in this thread (empty string if none). */
 const char* b200gru_strerror(int status);

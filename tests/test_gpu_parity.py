@@ -117,19 +117,42 @@ def test_scan_parity(kind, T, B, H, quant):
 @pytest.mark.parametrize("quant", [None, Q8], ids=["fp32", "q8"])
 @pytest.mark.parametrize("T,B,H,extra", [(8, 4, 32, {}), (16, 32, 512, {}), (5, 3, 48, {"butterfly_nblocks": 2}),
                                          (3, 2, 1024, {})])
-def test_butterfly_alternate_kernels(monkeypatch, T, B, H, extra, quant):
+def test_butterfly_alternate_kernels(T, B, H, extra, quant):
     """The library keeps two butterfly kernels per direction (staged twiddles, the default, and the
-    older register/global-twiddle one for unaligned problems); the variable, read at every call,
-    selects the older pair so that it keeps parity coverage on aligned shapes too."""
-    monkeypatch.setenv("B200GRU_BFLY_LEGACY", "1")
+    register / global-twiddle one for unaligned problems); the test hook selects the latter on
+    aligned shapes too, so that it keeps parity coverage there."""
+    from gru_triton_b200 import _lib
     fwd, bwd, _ = _mods()["butterfly"]
     gi, h0, W, bh, dout = orc.make_problem("butterfly", T, B, H, seed=7 + T + H, **extra)
     kw = dict(h_in_quant=quant[0], h_out_quant=quant[1]) if quant else {}
     d = _cuda(gi, h0, W, bh, dout)
-    out = fwd(*d[:4], **kw)
+    _lib.load().b200gru_test_select_kernels(1, 0)
+    try:
+        out = fwd(*d[:4], **kw)
+        grads = bwd(*d[:4], out, d[4], **kw)
+    finally:
+        _lib.load().b200gru_test_select_kernels(0, 0)
     check_forward("butterfly", out, gi, h0, W, bh, quant)
-    grads = bwd(*d[:4], out, d[4], **kw)
     check_backward("butterfly", grads, gi, h0, W, bh, out, dout, quant)
+
+
+@pytest.mark.parametrize("quant", [None, Q8, Q8_ASYM], ids=["fp32", "q8", "q8asym"])
+@pytest.mark.parametrize("T,B,H", [(16, 64, 1024), (9, 300, 256)])
+def test_diagonal_register_ring_forward_on_aligned_shapes(T, B, H, quant):
+    """Shapes that normally take the bulk-copy forward kernel, forced onto the register-ring one."""
+    from gru_triton_b200 import _lib
+    fwd, _, _ = _mods()["diagonal"]
+    gi, h0, W, bh, dout = orc.make_problem("diagonal", T, B, H, seed=T + H)
+    kw = dict(h_in_quant=quant[0], h_out_quant=quant[1]) if quant else {}
+    d = _cuda(gi, h0, W, bh)
+    default = fwd(*d, **kw)
+    _lib.load().b200gru_test_select_kernels(0, 1)
+    try:
+        ring = fwd(*d, **kw)
+    finally:
+        _lib.load().b200gru_test_select_kernels(0, 0)
+    assert torch.equal(ring, default)
+    check_forward("diagonal", ring[:, :8], gi[:, :8], h0[:8], W, bh, quant)
 
 
 @pytest.mark.parametrize("quant", [None, Q8, Q8_ASYM], ids=["fp32", "q8", "q8asym"])

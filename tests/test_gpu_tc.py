@@ -216,3 +216,22 @@ def test_dense_layer_dispatch_matches_per_step_path(wbits, hbits, T, B, H):
         assert bool(((o - ref.detach()).abs() <= FWD_TOL + FWD_TOL * ref.detach().abs()).all())
         for (n, p), (_, q) in zip(lay.named_parameters(), gl.named_parameters()):
             assert rel_err(q.grad.cpu(), p.grad) <= GRAD_TOL, n
+
+
+def test_zz_bounded_wait_gives_up_and_is_reported():
+    """The give-up path of the bounded waits, without hanging anything: a probe kernel waits about
+    a millisecond for bytes that nothing sends, sets the health word and returns.  The word is then
+    visible through the C ABI and through the Python check, clears on request, and the library
+    works normally afterwards (a set word makes tensor-core CTAs leave at once, so it MUST clear)."""
+    import ctypes
+    from gru_triton_b200 import _lib
+    lib, tc = _lib.load(), _tc()
+    assert lib.b200gru_device_status(0) == 0
+    assert lib.b200gru_test_wait_timeout(ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)) == 0
+    assert lib.b200gru_device_status(0) == 1
+    with pytest.raises(_lib.DeviceWaitTimeout):
+        _lib.check_device_status(reset=True)
+    assert lib.b200gru_device_status(0) == 0
+    a = torch.randint(-127, 128, (128, 128), device="cuda", dtype=torch.int8)
+    assert torch.equal(tc.gemm(a, a).cpu().double(), a.cpu().double() @ a.cpu().double().T)
+    _lib.check_device_status()

@@ -200,3 +200,29 @@ def test_library_exports_every_declared_symbol():
     # argument errors are reported before any device work
     assert lib.b200gru_scan_forward(ctypes.byref(dense), None, None, None, None, None, None, None, None,
                                     None, 0, None) == 1
+
+
+def test_device_status_check_raises_on_a_reported_timeout(monkeypatch):
+    """The Python side of the health word: a non-zero b200gru_device_status becomes DeviceWaitTimeout,
+    a CUDA error a RuntimeError, zero nothing (driven with a stand-in for the library: no GPU)."""
+    class Fake:
+        def __init__(self, v):
+            self.v, self.resets = v, []
+
+        def b200gru_device_status(self, reset):
+            self.resets.append(reset)
+            return self.v
+
+        def b200gru_last_cuda_error(self):
+            return b"unspecified launch failure"
+
+    for v, exc in ((1, _lib.DeviceWaitTimeout), (-1, RuntimeError)):
+        fake = Fake(v)
+        monkeypatch.setattr(_lib, "load", lambda fake=fake: fake)
+        with pytest.raises(exc):
+            _lib.check_device_status()
+        assert fake.resets == [1]
+    fake = Fake(0)
+    monkeypatch.setattr(_lib, "load", lambda: fake)
+    _lib.check_device_status(reset=False)
+    assert fake.resets == [0]

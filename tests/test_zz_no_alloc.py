@@ -24,7 +24,7 @@ pytestmark = pytest.mark.gpu
 GRAD_TOL = 1e-4
 
 
-def _run_pair(T, B, H, seed, quant):
+def _run_pair(T, B, H, seed, quant, first_call_on_device=False):
     from gru_triton_b200 import _lib
     from gru_triton_b200.scan_diagonal import (gru_scan_diagonal_backward_triton,
                                                gru_scan_diagonal_forward_triton)
@@ -42,13 +42,17 @@ def _run_pair(T, B, H, seed, quant):
     qi = _lib._cquant(quant[0] if quant else None)
     qo = _lib._cquant(quant[1] if quant else None)
     p = lambda t: ctypes.c_void_p(t.data_ptr())  # noqa: E731
+    torch.cuda.synchronize()
     before = torch.cuda.memory_allocated()
+    free_before = torch.cuda.mem_get_info()[0]               # the driver's view: catches a raw cudaMalloc too
     rc = lib.b200gru_diagonal_backward_noalloc(
         p(gi), p(h0), p(W), p(bh), p(out), p(dout), T, B, H, ctypes.byref(qi), ctypes.byref(qo),
         p(dgi), p(dh0), p(dW), p(dbh), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
     assert rc == 0, lib.b200gru_strerror(rc)
     assert torch.cuda.memory_allocated() == before          # nothing came from torch's allocator
     torch.cuda.synchronize()
+    if not first_call_on_device:
+        assert torch.cuda.mem_get_info()[0] >= free_before  # nor from the driver (other tenants may free)
     for name, got, want in zip(("dgi", "dh0", "dW", "dbh"), (dgi, dh0, dW, dbh), ref):
         assert not torch.isnan(got).any(), name
         assert rel_err(got, want) <= GRAD_TOL, name
@@ -56,7 +60,7 @@ def _run_pair(T, B, H, seed, quant):
 
 def test_noalloc_backward_matches_workspace_backward_twice_in_a_row():
     q8 = ((0.02, -127, 127), (0.02, -127, 127))
-    _run_pair(24, 37, 256, seed=1, quant=q8)       # larger first ...
+    _run_pair(24, 37, 256, seed=1, quant=q8, first_call_on_device=True)       # larger first ...
     _run_pair(9, 5, 64, seed=2, quant=None)        # ... then a smaller one over its leftovers
     _run_pair(24, 37, 256, seed=3, quant=None)
 
@@ -71,3 +75,22 @@ def test_noalloc_backward_rejects_oversized_problems():
     rc = lib.b200gru_diagonal_backward_noalloc(p, p, p, p, p, p, 1, 1024, 1024, None, None, p, p, p, p, None)
     assert rc == 5 and b"built-in" in lib.b200gru_strerror(rc)
     assert lib.b200gru_launch_count() == n0
+
+
+def test_noalloc_backward_accepts_exactly_the_built_in_size():
+    """H = 1024: ceil(B/4) * 6 * 1024 * 4 bytes; B = 680 fills the 4 MiB buffer to the byte (170 row
+    groups of 24 KiB + ...), one more row group is refused."""
+    from gru_triton_b200 import _lib
+    lib = _lib.load()
+    H = 1024
+    groups = (4 << 20) // (6 * H * 4)                        # 170 row groups fit
+    for B, want_rc in ((4 * groups, 0), (4 * groups + 1, 5)):
+        gi, h0, W, bh, dout = [t.cuda() for t in orc.make_problem("diagonal", 2, B, H, seed=4)]
+        out = torch.zeros(2, B, H, device="cuda")
+        dgi, dh0, dW, dbh = torch.empty_like(gi), torch.empty_like(h0), torch.empty_like(W), torch.empty_like(bh)
+        p = lambda t: ctypes.c_void_p(t.data_ptr())  # noqa: E731
+        rc = lib.b200gru_diagonal_backward_noalloc(
+            p(gi), p(h0), p(W), p(bh), p(out), p(dout), 2, B, H, None, None, p(dgi), p(dh0), p(dW), p(dbh),
+            ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+        assert rc == want_rc, (B, rc)
+    torch.cuda.synchronize()
