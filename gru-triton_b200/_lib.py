@@ -74,6 +74,8 @@ SIGNATURES = {
     "b200gru_tc_gemm": (_I, [_GP, _P]),
     "b200gru_tc_gemm_splits": (_I, [_GP, _I]),
     "b200gru_split_bf16": (_I, [_P, _P, _Z, _Z, _I, _P, _I, _P]),
+    "b200gru_calibration_workspace_bytes": (_Z, [_SP]),
+    "b200gru_calibration_scan": (_I, [_SP, _P, _P, _P, _P, _I, ctypes.c_double, _P, _P, _I, _P, _P, _I, _P, _P, _Z, _P]),
     "b200gru_device_status": (_I, [_I]),
     "b200gru_test_select_kernels": (None, [_I, _I]),
     "b200gru_test_wait_timeout": (_I, [_P]),
@@ -225,6 +227,31 @@ def scan_forward(kind: str, gi, h0, W, bh, h_in_quant: Quant, h_out_quant: Quant
         _raise(rc, f"{kind} scan forward")
     _after_call()
     return out, save
+
+
+def calibration_scan(kind: str, gi, h0, W, bh, qmax: int, momentum: float, in_stats, out_stats, *,
+                     nblocks: int = 1, log2_hpad: int = 0):
+    """Observing-mode forward scan.  ``in_stats`` / ``out_stats``: ``(min, max, initialized)`` with
+    one-element float32 CUDA tensors that are updated in place.  Returns ``out[T,B,H]``."""
+    lib = load()
+    T, B, _ = gi.shape
+    H = h0.shape[1]
+    shape = make_shape(kind, T, B, H, nblocks, log2_hpad)
+    out = torch.empty((T, B, H), device=gi.device, dtype=torch.float32)
+    n = lib.b200gru_calibration_workspace_bytes(ctypes.byref(shape))
+    if n == ctypes.c_size_t(-1).value:
+        raise RuntimeError("shape not supported by the CUDA scan library")
+    ws = torch.empty(n, dtype=torch.uint8, device=gi.device)
+    with torch.cuda.device(gi.device):
+        stream = torch.cuda.current_stream().cuda_stream
+        rc = lib.b200gru_calibration_scan(ctypes.byref(shape), _ptr(gi), _ptr(h0), _ptr(W), _ptr(bh), int(qmax),
+                                          float(momentum), _ptr(in_stats[0]), _ptr(in_stats[1]), int(in_stats[2]),
+                                          _ptr(out_stats[0]), _ptr(out_stats[1]), int(out_stats[2]), _ptr(out),
+                                          _ptr(ws), ws.numel(), ctypes.c_void_p(stream))
+    if rc:
+        _raise(rc, f"{kind} calibration scan")
+    _after_call()
+    return out
 
 
 def scan_backward(kind: str, gi, h0, W, bh, out, dout, save, h_in_quant: Quant, h_out_quant: Quant, *,

@@ -20,7 +20,7 @@ OBJ_DIR = os.path.join(PKG_DIR, "build")
 LIB_PATH = os.path.join(LIB_DIR, os.environ.get("B200GRU_LIB_NAME", "libb200gru.so"))
 
 SOURCES = ["api.cu", "diag_scan.cu", "block_scan.cu", "block_gemm.cu", "butterfly_scan.cu", "butterfly_scan2.cu",
-           "tc_gemm.cu", "tc_step.cu", "tc_scan.cu", "weight_prep.cu", "tc_api.cu"]
+           "tc_gemm.cu", "tc_step.cu", "tc_scan.cu", "weight_prep.cu", "tc_api.cu", "calib_scan.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

@@ -62,6 +62,7 @@ class GRULayer(nn.Module):
             raise ValueError("pre_batch_input is not supported in structured mode "
                              "(no dense Wi_cat to pre-project).")
         self.hidden_size, self.batch_first, self.pre_batch_input = hidden_size, batch_first, pre_batch_input
+        self._calibrating = False
 
         kind = structure_hidden.kind if structure_hidden is not None else None
         if kind in (None, "dense"):
@@ -103,6 +104,8 @@ class GRULayer(nn.Module):
 
         if self.use_triton and x.is_cuda:
             return self._forward_fast_dispatch(x, h0)
+        if self._calibrating and x.is_cuda and self._device_calibration_ok():
+            return self._forward_calibration_scan(x, h0)
 
         step, h, outs = self._compiled_step, h0, []
         if self.cell.is_structured:
@@ -117,6 +120,58 @@ class GRULayer(nn.Module):
                 outs.append(h)
         out = torch.stack(outs, dim=0)
         return (out.transpose(0, 1) if self.batch_first else out), h
+
+    # ------------------------------------------------------------------
+    def _device_calibration_ok(self) -> bool:
+        """calibrate() can observe on the device when the layer is dispatchable, the two hidden
+        quantizers are the per-tensor symmetric observers and nothing else on the path quantises
+        activations (input, gate and structured-output quantizers are identities)."""
+        cell = self.cell
+        if not self._fast_dispatch_eligible:
+            return False
+        qi, qo = cell.quant_h_in, cell.quant_h_out
+        for q in (qi, qo):
+            if not isinstance(q, FakeQuantizePerTensor) or not q.config.symmetric or q.config.mode != "min_max":
+                return False
+            if q.running_min.numel() != 1 or not q.running_min.is_cuda or q.running_min.dtype != torch.float32:
+                return False
+        if int(qi.qmax) != int(qo.qmax):
+            return False
+        others = [cell.quant_x] + [getattr(cell, f"quant_gate_{g}") for g in "rzn"]
+        others += [m for n, m in cell.named_children() if n.startswith("quant_struct_W")]
+        return all(isinstance(q, Identity) for q in others)
+
+    def _forward_calibration_scan(self, x, h0):
+        """One calibration forward on the device: the scan with both hidden quantizers observing
+        (dynamic scale per call, running range blended with the observers' momentum), the same
+        arithmetic the per-step cell performs in ``min_max`` mode (quantizers.py:95-156)."""
+        from . import _lib
+        from .quantizers import _EMA_MOMENTUM
+        cell = self.cell
+        gi = self._input_projection_fast(x) if cell._input_dense else cell.structured_input_projection(x)
+        kind, kw = self._dispatch_kind, {}
+        if kind == "dense":
+            W = torch.cat([getattr(cell, f"quant_W_h{g}")(getattr(cell, f"W_h{g}")) for g in "rzn"], dim=0)
+            bh = cell._cat_bias("h")
+            bh = gi.new_zeros(3 * self.hidden_size) if bh is None else bh
+        elif kind == "diagonal":
+            from .scan_diagonal import extract_diagonal_factors
+            W, bh = extract_diagonal_factors(cell)
+        elif kind == "monarch":
+            from .scan_monarch import extract_monarch_factors
+            W, bh = extract_monarch_factors(cell)
+            kw["nblocks"] = W.shape[1]
+        else:
+            from .scan_butterfly import extract_butterfly_twiddles
+            W, bh = extract_butterfly_twiddles(cell)
+            kw["nblocks"], kw["log2_hpad"] = W.shape[1], W.shape[2]
+        qi, qo = cell.quant_h_in, cell.quant_h_out
+        out = _lib.calibration_scan(kind, gi.contiguous(), h0.contiguous(), W.detach().contiguous(),
+                                    bh.detach().contiguous(), int(qi.qmax), _EMA_MOMENTUM,
+                                    (qi.running_min, qi.running_max, qi._initialized),
+                                    (qo.running_min, qo.running_max, qo._initialized), **kw)
+        qi._initialized = qo._initialized = True
+        return (out.transpose(0, 1) if self.batch_first else out), out[-1]
 
     def _weight_bits_on_device(self, side: str):
         """Bit width if the three weight quantizers of a side are the per-output-row symmetric
@@ -185,16 +240,22 @@ class GRULayer(nn.Module):
 
     # ------------------------------------------------------------------
     @torch.no_grad()
-    def calibrate(self, loader: Iterable[object], n_batches: int = 64, *, only_activations: bool = True):
-        """Observe activation ranges over ``n_batches`` forwards on the per-step path
-        (the fast path reads scales but never runs the hidden quantizers, so it is
-        switched off for the duration).  Call :meth:`freeze` afterwards."""
+    def calibrate(self, loader: Iterable[object], n_batches: int = 64, *, only_activations: bool = True,
+                  device_scan: bool = True):
+        """Observe activation ranges over ``n_batches`` forwards.  The fast path reads frozen scales
+        but never runs the hidden quantizers, so it is switched off for the duration, as in the
+        reference (gru_layer.py:323-339).  CUDA batches of a dispatchable layer whose only
+        activation quantizers are the two hidden-state observers are observed on the device by
+        the calibration scan; everything else steps the cell in Python.  Call :meth:`freeze`
+        afterwards."""
         from .calibration import calibrate as _calibrate
         saved, self.use_triton = self.use_triton, False
+        self._calibrating = bool(saved) and device_scan
         try:
             return _calibrate(self, loader, n_batches=n_batches, only_activations=only_activations)
         finally:
             self.use_triton = saved
+            self._calibrating = False
 
     def freeze(self) -> None:
         self.cell.freeze_quantizers()

@@ -270,6 +270,24 @@ unsigned long long b200gru_launch_count(void);
  * (scan.py:202-205). */
 int b200gru_device_status(int reset);
 
+/* ---- calibration on the device --------------------------------------------------------------
+ * Forward scan with the two hidden-state quantisers in observing ("min_max") mode, the state
+ * GRULayer.calibrate() puts them in (src/gru_qat/gru_layer.py:308-339, src/gru_qat/calibration.py:
+ * 30-135): at every step quant_h_in sees h_{t-1} and quant_h_out sees h_raw_t; each call
+ * fake-quantises with the dynamic symmetric scale max(|min|, |max|, 1e-8) / qmax of its own
+ * argument and folds (min, max) into the running range -- set by the first call, blended with
+ * `momentum` (0.99 in the reference, src/gru_qat/quantizers.py:136-156) afterwards.  The reference
+ * runs this through its Python per-step cell; here the ranges, scales and running statistics stay
+ * in device memory and nothing synchronises with the host.
+ * in_min/in_max, out_min/out_max: one float each in device memory, the running ranges of the two
+ * quantisers (read when *_initialized != 0, always written).  out[T,B,H] receives the quantised
+ * states.  Every hidden kind; no frozen quantiser is involved, so there are no q_in / q_out. */
+size_t b200gru_calibration_workspace_bytes(const b200gru_shape* shape);
+int b200gru_calibration_scan(const b200gru_shape* shape, const float* gi, const float* h0, const float* W,
+                             const float* bh, int qmax, double momentum, float* in_min, float* in_max,
+                             int in_initialized, float* out_min, float* out_max, int out_initialized,
+                             float* out, void* workspace, size_t workspace_bytes, void* stream);
+
 /* ---- test hooks (no reference counterpart; not for production callers) ------------------------
  * b200gru_test_select_kernels: the library keeps two kernels for some problems and picks by
  * shape; a non-zero argument makes the butterfly launches use the register / global-twiddle

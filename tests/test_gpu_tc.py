@@ -218,6 +218,58 @@ def test_dense_layer_dispatch_matches_per_step_path(wbits, hbits, T, B, H):
             assert rel_err(q.grad.cpu(), p.grad) <= GRAD_TOL, n
 
 
+@pytest.mark.parametrize("kind,H,B", [("diagonal", 64, 6), ("diagonal", 1024, 70), ("dense", 64, 5), ("dense", 576, 130),
+                                      ("monarch", 64, 7), ("butterfly", 64, 4)])
+def test_calibration_on_the_device_matches_the_per_step_path(kind, H, B):
+    """calibrate() observed by the calibration scan (ranges, scales and running statistics stay on
+    the device) against the same layer calibrated by the Python per-step loop, then freeze() and
+    the frozen CUDA scan on both."""
+    from gru_triton_b200 import GRULayer, QuantizerConfig, QuantRecipe, StructureConfig
+    torch.manual_seed(H + B)
+    T = 10
+    recipe = QuantRecipe(weight=QuantizerConfig(bits=32, axis=0, name="W"), input_act=QuantizerConfig(bits=32, name="x"),
+                         hidden=QuantizerConfig(bits=8, mode="dynamic", name="h"))
+    structure = None if kind == "dense" else StructureConfig(kind=kind, nblocks=4)
+    a = GRULayer(H, H, recipe, gate_layout="fused", structure_hidden=structure).cuda()
+    b = copy.deepcopy(a)
+    batches = [torch.randn(T, B, H, device="cuda") for _ in range(3)]
+    sa = a.calibrate(batches, n_batches=3)                       # device scan
+    sb = b.calibrate(batches, n_batches=3, device_scan=False)    # per-step cell
+    assert a.use_triton and sa["cell.quant_h_in"]["initialized"] and sa["cell.quant_h_out"]["initialized"]
+    for q in ("cell.quant_h_in", "cell.quant_h_out"):
+        for k in ("running_min", "running_max"):
+            assert abs(sa[q][k] - sb[q][k]) <= 2e-3 * max(abs(sb[q][k]), 1e-3), (q, k, sa[q][k], sb[q][k])
+    a.freeze(); b.freeze()
+    assert rel_err(a.cell.quant_h_in.scale.cpu(), b.cell.quant_h_in.scale.cpu()) < 2e-3
+    assert rel_err(a.cell.quant_h_out.scale.cpu(), b.cell.quant_h_out.scale.cpu()) < 2e-3
+    out, _ = a(batches[0])
+    assert torch.isfinite(out).all()
+
+
+def test_calibration_on_the_device_against_the_reference_fixture():
+    """The reference's own calibrate() + freeze() on a diagonal layer (CPU), replayed on CUDA."""
+    from gru_triton_b200 import GRULayer, QuantizerConfig, QuantRecipe, StructureConfig
+    g = load_golden("calib_diagonal")
+    H = g["x0"].shape[2]
+    recipe = QuantRecipe(weight=QuantizerConfig(bits=32, axis=0, name="W"), input_act=QuantizerConfig(bits=32, name="x"),
+                         hidden=QuantizerConfig(bits=8, mode="dynamic", name="h"))
+    layer = GRULayer(H, H, recipe, gate_layout="fused", structure_hidden=StructureConfig(kind="diagonal"))
+    with torch.no_grad():
+        for k, v in g.items():
+            if k.startswith("p:"):
+                layer.get_parameter(k[2:]).copy_(v)
+    layer = layer.cuda()
+    summary = layer.calibrate([g["x0"].cuda(), g["x1"].cuda(), g["x2"].cuda()], n_batches=3)
+    layer.freeze()
+    assert abs(summary["cell.quant_h_in"]["running_min"] - float(g["rmin_in"])) < 1e-4
+    assert abs(summary["cell.quant_h_out"]["running_max"] - float(g["rmax_out"])) < 1e-4
+    assert rel_err(layer.cell.quant_h_in.scale.cpu(), g["s_in"]) < 1e-4
+    assert rel_err(layer.cell.quant_h_out.scale.cpu(), g["s_out"]) < 1e-4
+    out, _ = layer(g["x_eval"].cuda())
+    frac = float((out.cpu() != g["out_eval"]).float().mean())
+    assert frac < 5e-3, frac
+
+
 def test_zz_bounded_wait_gives_up_and_is_reported():
     """The give-up path of the bounded waits, without hanging anything: a probe kernel waits about
     a millisecond for bytes that nothing sends, sets the health word and returns.  The word is then
