@@ -105,3 +105,48 @@ GRUScanMonarchFunction = make_scan_function("monarch", _forward_impl, _backward_
 def gru_scan_monarch(gi, h0, Wh_struct, bh_cat, *, h_in_quant: Quant = None, h_out_quant: Quant = None):
     """Differentiable block-diagonal scan (scan_monarch.py:927-952)."""
     return GRUScanMonarchFunction.apply(gi, h0, Wh_struct, bh_cat, h_in_quant, h_out_quant)
+
+
+# ---------------------------------------------------------------------------
+# two-factor Monarch (extension; the reference's API has one factor per gate)
+# ---------------------------------------------------------------------------
+
+def monarch_permutation(nblocks: int, blksz: int, device=None) -> torch.Tensor:
+    """Index vector of the Monarch (stride) permutation P of a length ``nblocks * blksz`` vector read
+    as an ``[nblocks, blksz]`` grid: ``(P v)[j * nblocks + i] = v[i * blksz + j]``."""
+    return torch.arange(nblocks * blksz, device=device).reshape(nblocks, blksz).t().reshape(-1)
+
+
+def monarch2_dense(W1: torch.Tensor, W2: torch.Tensor) -> torch.Tensor:
+    """``Wh_cat[3H, H]`` of the two-factor operator ``M_g = P^T . blockdiag(W2[g]) . P . blockdiag(W1[g])``
+    (``W1``, ``W2``: ``[3, nblocks, blksz, blksz]``); differentiable in both factors."""
+    _, nb, bs, _ = W1.shape
+    perm = monarch_permutation(nb, bs, W1.device)
+    inv = torch.argsort(perm)
+    mats = []
+    for g in range(3):
+        B1 = torch.block_diag(*W1[g])
+        B2 = torch.block_diag(*W2[g])
+        mats.append((B2 @ B1[perm])[inv])
+    return torch.cat(mats, dim=0)
+
+
+def gru_scan_monarch2(gi, h0, W1, W2, bh_cat, *, h_in_quant: Quant = None, h_out_quant: Quant = None):
+    """Differentiable scan with TWO block-diagonal factors per gate separated by the Monarch
+    permutation, ``gh_g = P^T B2_g P B1_g fq_in(h) + bh_g`` -- the operator BASELINE config 3 words
+    literally.  The reference cannot express it (one factor per gate, scan_monarch.py:110-112), so
+    there is no reference parity for this entry point; its checker is a dense materialisation.
+
+    The product couples all hidden units (it is no longer ``nblocks`` independent GRUs), so the scan
+    itself runs on the dense kernels with the materialised ``[3H, H]`` matrix; gradients reach the
+    two factors through the materialisation."""
+    require_cuda(gi=gi, h0=h0, W1=W1, W2=W2, bh_cat=bh_cat)
+    require_f32(gi=gi, h0=h0, W1=W1, W2=W2, bh_cat=bh_cat)
+    T, B, H = common_shapes(gi, h0, bh_cat)
+    if W1.dim() != 4 or W1.shape != W2.shape or W1.shape[0] != 3 or W1.shape[2] != W1.shape[3] \
+            or W1.shape[1] * W1.shape[2] != H:
+        raise ValueError("W1 and W2 must both be [3, nblocks, blksz, blksz] with nblocks * blksz == H; got "
+                         f"{tuple(W1.shape)} and {tuple(W2.shape)} for H={H}")
+    from .scan import gru_scan_persistent
+    return gru_scan_persistent(gi, h0, monarch2_dense(W1, W2), bh_cat, h_in_quant=h_in_quant,
+                               h_out_quant=h_out_quant)

@@ -435,6 +435,44 @@ def layer_train_step(kind: str, x, h0, Wi_cat, bi_cat, W, bh,
 
 
 # ---------------------------------------------------------------------------
+# two-factor Monarch (extension of this build; PARITY UNPINNED: the reference has no such operator)
+# ---------------------------------------------------------------------------
+
+def monarch2_dense_loops(W1: torch.Tensor, W2: torch.Tensor) -> torch.Tensor:
+    """Dense ``[3H, H]`` matrix of ``gh_g = P^T B2_g P B1_g h`` by scalar index loops, where B1 / B2
+    are block-diagonal with blocks ``W1[g, i]`` / ``W2[g, i]`` and P is the Monarch stride
+    permutation ``(P v)[j * nblocks + i] = v[i * blksz + j]`` (BASELINE config 3's wording; the
+    reference itself has one factor per gate, scan_monarch.py:110-112)."""
+    _, nb, bs, _ = W1.shape
+    H = nb * bs
+    out = torch.zeros(3 * H, H, dtype=W1.dtype)
+    for g in range(3):
+        for col in range(H):
+            v = [0.0] * H
+            v[col] = 1.0
+            # B1
+            a = [0.0] * H
+            for i in range(nb):
+                for o in range(bs):
+                    a[i * bs + o] = sum(float(W1[g, i, o, k]) * v[i * bs + k] for k in range(bs) if v[i * bs + k] != 0.0)
+            # P
+            p = [0.0] * H
+            for i in range(nb):
+                for j in range(bs):
+                    p[j * nb + i] = a[i * bs + j]
+            # B2
+            c = [0.0] * H
+            for i in range(nb):
+                for o in range(bs):
+                    c[i * bs + o] = sum(float(W2[g, i, o, k]) * p[i * bs + k] for k in range(bs) if p[i * bs + k] != 0.0)
+            # P^T
+            for i in range(nb):
+                for j in range(bs):
+                    out[g * H + i * bs + j, col] = c[j * nb + i]
+    return out
+
+
+# ---------------------------------------------------------------------------
 # seeded synthetic problems (shared by tests, smoke and bench)
 # ---------------------------------------------------------------------------
 

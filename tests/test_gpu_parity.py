@@ -467,6 +467,34 @@ def test_cluster_exchange_is_race_free(kind, T, B, H, extra):
     check_backward(kind, g0, *[t.cpu() for t in (gi, h0, W, bh)], out0, dout.cpu(), None)
 
 
+@pytest.mark.parametrize("quant", [None, Q8], ids=["fp32", "q8"])
+@pytest.mark.parametrize("T,B,nb,bs", [(8, 4, 4, 8), (16, 32, 8, 64)])
+def test_two_factor_monarch_extension(T, B, nb, bs, quant):
+    """gru_scan_monarch2 (two block-diagonal factors around the Monarch permutation, the operator
+    BASELINE config 3 words) against the oracle's dense scan on the loop-materialised matrix;
+    factor gradients against autograd through that materialisation.  Parity with the reference is
+    not defined for this operator."""
+    from gru_triton_b200 import scan_monarch
+    H = nb * bs
+    gen = torch.Generator().manual_seed(T + H)
+    gi, h0, _, bh, dout = orc.make_problem("dense", T, B, H, seed=H)
+    W1 = torch.randn(3, nb, bs, bs, generator=gen) * bs ** -0.5
+    W2 = torch.randn(3, nb, bs, bs, generator=gen) * bs ** -0.5
+    Md = orc.monarch2_dense_loops(W1, W2) if H <= 64 else scan_monarch.monarch2_dense(W1.double(), W2.double()).float()
+    leaves = [t.cuda().requires_grad_(True) for t in (gi, h0, W1, W2, bh)]
+    kw = dict(h_in_quant=quant[0], h_out_quant=quant[1]) if quant else {}
+    out = scan_monarch.gru_scan_monarch2(*leaves, **kw)
+    check_forward("dense", out.detach(), gi, h0, Md, bh, quant)
+    out.backward(dout.cuda())
+    qi, qo = quant if quant else (None, None)
+    ref = orc.scan_backward("dense", gi, h0, Md, bh, out.detach().cpu(), dout, qi, qo)
+    W1l, W2l = W1.clone().requires_grad_(True), W2.clone().requires_grad_(True)
+    scan_monarch.monarch2_dense(W1l, W2l).backward(ref[2])
+    for nm, a, b in zip(("dgi", "dh0", "dW1", "dW2", "dbh"), [l.grad for l in leaves],
+                        (ref[0], ref[1], W1l.grad, W2l.grad, ref[3])):
+        assert rel_err(a.cpu(), b) <= GRAD_TOL, nm
+
+
 def test_zz_no_bounded_wait_gave_up():
     """Runs after the other tests of this file: none of the in-kernel waits timed out."""
     from gru_triton_b200 import _lib

@@ -226,3 +226,19 @@ def test_device_status_check_raises_on_a_reported_timeout(monkeypatch):
     monkeypatch.setattr(_lib, "load", lambda: fake)
     _lib.check_device_status(reset=False)
     assert fake.resets == [0]
+
+
+@pytest.mark.parametrize("nb,bs", [(2, 2), (3, 4), (4, 2), (8, 8)])
+def test_two_factor_monarch_materialisation(nb, bs):
+    """The vectorised dense form of P^T B2 P B1 against the oracle's index-loop form (the checker of
+    the two-factor extension; parity with the reference is undefined: it has one factor per gate)."""
+    from oracle import gru_scan_oracle as orc
+    gen = torch.Generator().manual_seed(nb * 10 + bs)
+    W1 = torch.randn(3, nb, bs, bs, generator=gen, dtype=torch.float64)
+    W2 = torch.randn(3, nb, bs, bs, generator=gen, dtype=torch.float64)
+    assert (scan_monarch.monarch2_dense(W1, W2) - orc.monarch2_dense_loops(W1, W2)).abs().max() < 1e-12
+    # a single factor is the special case B2 = I with the permutation undone
+    eye = torch.eye(bs, dtype=torch.float64).expand(3, nb, bs, bs).contiguous()
+    single = torch.cat([torch.block_diag(*W1[g]) for g in range(3)], 0)
+    if nb == bs:
+        assert (scan_monarch.monarch2_dense(W1, eye) - single).abs().max() < 1e-12
