@@ -404,12 +404,12 @@ int launch_tc_dense_forward(const float* gi, const float* h0, const TcWeights& w
   if (p.i8) {
     // both operands are integer codes: one fused kernel per step (product + gates + next codes)
     FusedFwd f;
-    rc = f.init(w.codes, reinterpret_cast<signed char*>(op[0]), reinterpret_cast<signed char*>(op[1]), B, H);
+    rc = f.init(w.codes, reinterpret_cast<signed char*>(op[0]), reinterpret_cast<signed char*>(op[1]), gi, h0, out, save,
+                T, B, H);
     if (rc) return rc;
     for (int t = 0; t < T; ++t) {
-      rc = f.step(t, T, t & 1, gi, (t == 0) ? h0 : out + (size_t)(t - 1) * B * H, w.row_scale, bh,
-                  out + (size_t)t * B * H, save,
-                  (t + 1 < T) ? reinterpret_cast<signed char*>(op[(t + 1) & 1]) : nullptr, qin.scale, qin, qout, st);
+      rc = f.step(t, t & 1, w.row_scale, bh, (t + 1 < T) ? reinterpret_cast<signed char*>(op[(t + 1) & 1]) : nullptr,
+                  qin.scale, qin, qout, st);
       if (rc) return rc;
     }
     return check_launch("tc_fwd_step_kernel");

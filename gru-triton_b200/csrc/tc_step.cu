@@ -39,31 +39,40 @@ constexpr int FS_KB = 128;          // int8 elements of K per stage
 constexpr int FS_A_BYTES = FS_BM * FS_KB;            // 16 KB
 constexpr int FS_B_SLAB = FS_UNITS * FS_KB;          // 4 KB per gate
 constexpr int FS_STAGE = FS_A_BYTES + 3 * FS_B_SLAB; // 28 KB
-constexpr int FS_MAX_STAGES = 8;
+constexpr int FS_STAGES = 4;                         // ring; also holds the five 16 KB output tiles afterwards
+constexpr int FS_TILE = FS_BM * FS_UNITS * 4;        // one fp32 [128 rows][32 units] tile: 16 KB
+constexpr int FS_SMEM = FS_STAGES * FS_STAGE + 4 * FS_TILE + 1024;   // ring + gi(3) + h_prev(1) + alignment
 constexpr int FS_EPI_WARPS = 8;
 constexpr int FS_THREADS = 64 + 32 * FS_EPI_WARPS;
+static_assert(FS_STAGES * FS_STAGE >= 5 * FS_TILE, "output staging reuses the operand ring");
 
 struct FusedFwdArgs {
-  const float* gi;       // [T][B][3H]
-  const float* h_prev;   // [B][H]
   const float* col_scale;  // [3H] row scales of the weight codes
   const float* bh;       // [3H]
-  float* out_t;          // [B][H]
-  float* save;           // [4][T][B][H] or NULL
   signed char* codes_next;   // [B][H] or NULL
   int t, T, B, H;
-  int nkb, stages;
+  int nkb;
+  int has_save;
   float alpha;           // scale of the hidden codes
   Quant qin, qout;
 };
 
+// fp32 tile [128 rows][32 floats] written by TMA with the 128-byte swizzle: 16-byte chunk c of row r
+// sits at chunk position c ^ (r & 7).  A thread that owns row r touches chunks without bank conflicts.
+__device__ __forceinline__ float4* tile_chunk(unsigned char* tile, int r, int c) {
+  return reinterpret_cast<float4*>(tile + r * 128 + ((c ^ (r & 7)) << 4));
+}
+
 __global__ void __launch_bounds__(FS_THREADS, 1)
 tc_fwd_step_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                   const __grid_constant__ CUtensorMap tmGi, const __grid_constant__ CUtensorMap tmPrev,
+                   const __grid_constant__ CUtensorMap tmOut, const __grid_constant__ CUtensorMap tmSave,
                    const FusedFwdArgs a) {
   constexpr uint32_t IDESC = umma_idesc(true, false, false, FS_BM, FS_BN);
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  __shared__ __align__(8) unsigned long long bar_full[FS_MAX_STAGES], bar_empty[FS_MAX_STAGES], bar_acc;
+  unsigned char* io = smem + FS_STAGES * FS_STAGE;        // gi_r, gi_z, gi_n, h_prev tiles
+  __shared__ __align__(8) unsigned long long bar_full[FS_STAGES], bar_empty[FS_STAGES], bar_acc, bar_io;
   __shared__ uint32_t tmem_base_slot;
   __shared__ int dead;
   __shared__ float s_scale[FS_BN], s_bias[FS_BN];
@@ -75,14 +84,17 @@ tc_fwd_step_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
 
   if (threadIdx.x == 0) {
     dead = (*reinterpret_cast<volatile int*>(status) != 0) ? 1 : 0;
-    for (int s = 0; s < a.stages; ++s) {
+    for (int s = 0; s < FS_STAGES; ++s) {
       mbar_init(smem_u32(&bar_full[s]), 1);
       mbar_init(smem_u32(&bar_empty[s]), 1);
     }
     mbar_init(smem_u32(&bar_acc), 1);
+    mbar_init(smem_u32(&bar_io), 1);
     mbar_fence_init();
     tma_prefetch_map(&tmA);
     tma_prefetch_map(&tmB);
+    tma_prefetch_map(&tmGi);
+    tma_prefetch_map(&tmPrev);
   }
   if (threadIdx.x >= 64 && threadIdx.x < 64 + FS_BN) {
     const int c = threadIdx.x - 64, g = c / FS_UNITS, j = c - g * FS_UNITS;
@@ -98,8 +110,14 @@ tc_fwd_step_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
 
   if (warp == 0) {
     if (lane == 0 && !*deadp) {
+      // the input tiles of the gate math: gi[t] (three gates) and h_{t-1}
+      const uint32_t iob = smem_u32(&bar_io);
+      mbar_expect_tx(iob, 4 * FS_TILE);
+#pragma unroll
+      for (int g = 0; g < 3; ++g) tma_load_3d(smem_u32(io + g * FS_TILE), &tmGi, g * H + u0, m0, a.t, iob);
+      tma_load_3d(smem_u32(io + 3 * FS_TILE), &tmPrev, u0, m0, a.t > 0 ? a.t - 1 : 0, iob);
       for (int i = 0; i < a.nkb; ++i) {
-        const int s = i % a.stages, round = i / a.stages;
+        const int s = i % FS_STAGES, round = i / FS_STAGES;
         if (round > 0 && !mbar_wait(smem_u32(&bar_empty[s]), (round - 1) & 1, deadp, status)) break;
         const uint32_t full = smem_u32(&bar_full[s]);
         mbar_expect_tx(full, FS_STAGE);
@@ -114,7 +132,7 @@ tc_fwd_step_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     if (lane == 0 && !*deadp) {
       bool alive = true;
       for (int i = 0; i < a.nkb && alive; ++i) {
-        const int s = i % a.stages, round = i / a.stages;
+        const int s = i % FS_STAGES, round = i / FS_STAGES;
         if (!mbar_wait(smem_u32(&bar_full[s]), round & 1, deadp, status)) { alive = false; break; }
         tc_fence_after();
         const uint32_t sa = smem_u32(smem + (size_t)s * FS_STAGE);
@@ -130,26 +148,11 @@ tc_fwd_step_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
   } else {
     // ---- epilogue: thread = (batch row, 16 units)
     const int q = warp & 3, half = (warp - 2) >> 2;
-    const int b = m0 + q * 32 + lane;
+    const int r = q * 32 + lane;                    // row inside the tile
+    const int b = m0 + r;
     const int ub = half * 16;                       // first unit of this thread inside the CTA's 32
-    const bool rowok = b < a.B;
-    const size_t o = (size_t)(rowok ? b : 0) * H + u0 + ub;
-    float gi_r[16], gi_z[16], gi_n[16], hp[16];
-    {
-      const float* g = a.gi + ((size_t)a.t * a.B + (rowok ? b : 0)) * 3 * H + u0 + ub;
-#pragma unroll
-      for (int j = 0; j < 16; j += 4) {
-        const float4 vr = __ldcs(reinterpret_cast<const float4*>(g + j));
-        const float4 vz = __ldcs(reinterpret_cast<const float4*>(g + H + j));
-        const float4 vn = __ldcs(reinterpret_cast<const float4*>(g + 2 * H + j));
-        const float4 vh = *reinterpret_cast<const float4*>(a.h_prev + o + j);
-        gi_r[j] = vr.x; gi_r[j + 1] = vr.y; gi_r[j + 2] = vr.z; gi_r[j + 3] = vr.w;
-        gi_z[j] = vz.x; gi_z[j + 1] = vz.y; gi_z[j + 2] = vz.z; gi_z[j + 3] = vz.w;
-        gi_n[j] = vn.x; gi_n[j + 1] = vn.y; gi_n[j + 2] = vn.z; gi_n[j + 3] = vn.w;
-        hp[j] = vh.x; hp[j + 1] = vh.y; hp[j + 2] = vh.z; hp[j + 3] = vh.w;
-      }
-    }
-    bool ok = mbar_wait(smem_u32(&bar_acc), 0, deadp, status);
+    bool ok = mbar_wait(smem_u32(&bar_io), 0, deadp, status);
+    if (ok) ok = mbar_wait(smem_u32(&bar_acc), 0, deadp, status);
     ok = __all_sync(0xffffffffu, ok);
     tc_fence_after();
     uint32_t ar[16], az[16], an[16];
@@ -163,36 +166,53 @@ tc_fwd_step_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
 #pragma unroll
       for (int j = 0; j < 16; ++j) { ar[j] = 0u; az[j] = 0u; an[j] = 0u; }
     }
-    if (rowok) {
-      const size_t comp = (size_t)a.T * a.B * H, so = (size_t)a.t * a.B * H + o;
-      uint32_t cw[4];
+    // every MMA has completed (bar_acc): the operand ring is free and takes the output tiles
+    unsigned char* stage_out = smem;                // out, r, z, n, gh_n: five 16 KB tiles
+    uint32_t cw[4];
 #pragma unroll
-      for (int j4 = 0; j4 < 16; j4 += 4) {
-        float hn[4], rr[4], zz[4], nn[4], gg[4];
-        uint32_t packed = 0;
+    for (int j4 = 0; j4 < 16; j4 += 4) {
+      const int c = (ub + j4) >> 2;                 // 16-byte chunk of the row
+      const float4 vr = *tile_chunk(io, r, c);
+      const float4 vz = *tile_chunk(io + FS_TILE, r, c);
+      const float4 vn = *tile_chunk(io + 2 * FS_TILE, r, c);
+      const float4 vh = *tile_chunk(io + 3 * FS_TILE, r, c);
+      const float gir[4] = {vr.x, vr.y, vr.z, vr.w}, giz[4] = {vz.x, vz.y, vz.z, vz.w};
+      const float gin[4] = {vn.x, vn.y, vn.z, vn.w}, hp[4] = {vh.x, vh.y, vh.z, vh.w};
+      float hn[4], rr[4], zz[4], nn[4], gg[4];
+      uint32_t packed = 0;
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int j = j4 + e, c = ub + j;
-          const float ghr = (float)(int)ar[j] * s_scale[c] + s_bias[c];
-          const float ghz = (float)(int)az[j] * s_scale[FS_UNITS + c] + s_bias[FS_UNITS + c];
-          const float ghn = (float)(int)an[j] * s_scale[2 * FS_UNITS + c] + s_bias[2 * FS_UNITS + c];
-          const GateOut go = gru_gates(gi_r[j], gi_z[j], gi_n[j], ghr, ghz, ghn, hp[j]);
-          rr[e] = go.r; zz[e] = go.z; nn[e] = go.n; gg[e] = ghn;
-          hn[e] = a.qout.enabled ? fake_quant<true>(go.h_raw, a.qout) : go.h_raw;
-          const float code = fminf(fmaxf(fq_code(hn[e], a.qin), a.qin.qmin), a.qin.qmax);
-          packed |= ((uint32_t)(int)code & 0xffu) << (8 * e);
-        }
-        cw[j4 >> 2] = packed;
-        *reinterpret_cast<float4*>(a.out_t + o + j4) = make_float4(hn[0], hn[1], hn[2], hn[3]);
-        if (a.save != nullptr) {
-          __stcs(reinterpret_cast<float4*>(a.save + so + j4), make_float4(rr[0], rr[1], rr[2], rr[3]));
-          __stcs(reinterpret_cast<float4*>(a.save + comp + so + j4), make_float4(zz[0], zz[1], zz[2], zz[3]));
-          __stcs(reinterpret_cast<float4*>(a.save + 2 * comp + so + j4), make_float4(nn[0], nn[1], nn[2], nn[3]));
-          __stcs(reinterpret_cast<float4*>(a.save + 3 * comp + so + j4), make_float4(gg[0], gg[1], gg[2], gg[3]));
-        }
+      for (int e = 0; e < 4; ++e) {
+        const int j = j4 + e, cc = ub + j;
+        const float ghr = (float)(int)ar[j] * s_scale[cc] + s_bias[cc];
+        const float ghz = (float)(int)az[j] * s_scale[FS_UNITS + cc] + s_bias[FS_UNITS + cc];
+        const float ghn = (float)(int)an[j] * s_scale[2 * FS_UNITS + cc] + s_bias[2 * FS_UNITS + cc];
+        const GateOut go = gru_gates(gir[e], giz[e], gin[e], ghr, ghz, ghn, hp[e]);
+        rr[e] = go.r; zz[e] = go.z; nn[e] = go.n; gg[e] = ghn;
+        hn[e] = a.qout.enabled ? fake_quant<true>(go.h_raw, a.qout) : go.h_raw;
+        const float code = fminf(fmaxf(fq_code(hn[e], a.qin), a.qin.qmin), a.qin.qmax);
+        packed |= ((uint32_t)(int)code & 0xffu) << (8 * e);
       }
-      if (a.codes_next != nullptr)
-        *reinterpret_cast<uint4*>(a.codes_next + o) = make_uint4(cw[0], cw[1], cw[2], cw[3]);
+      cw[j4 >> 2] = packed;
+      *tile_chunk(stage_out, r, c) = make_float4(hn[0], hn[1], hn[2], hn[3]);
+      if (a.has_save) {
+        *tile_chunk(stage_out + FS_TILE, r, c) = make_float4(rr[0], rr[1], rr[2], rr[3]);
+        *tile_chunk(stage_out + 2 * FS_TILE, r, c) = make_float4(zz[0], zz[1], zz[2], zz[3]);
+        *tile_chunk(stage_out + 3 * FS_TILE, r, c) = make_float4(nn[0], nn[1], nn[2], nn[3]);
+        *tile_chunk(stage_out + 4 * FS_TILE, r, c) = make_float4(gg[0], gg[1], gg[2], gg[3]);
+      }
+    }
+    if (a.codes_next != nullptr && b < a.B)
+      *reinterpret_cast<uint4*>(a.codes_next + (size_t)b * H + u0 + ub) = make_uint4(cw[0], cw[1], cw[2], cw[3]);
+    // hand the tiles to the TMA engine: all epilogue threads' writes first, then one thread stores
+    fence_async_smem();
+    asm volatile("bar.sync 1, %0;" ::"n"(32 * FS_EPI_WARPS) : "memory");
+    if (warp == 2 && lane == 0 && ok) {
+      tma_store_3d(&tmOut, u0, m0, a.t, smem_u32(stage_out));
+      if (a.has_save) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) tma_store_3d(&tmSave, u0, m0, k * a.T + a.t, smem_u32(stage_out + (k + 1) * FS_TILE));
+      }
+      tma_store_commit_and_wait();
     }
   }
 
@@ -237,33 +257,40 @@ int tc_step_read_status(int reset) {
   return v;
 }
 
-int FusedFwd::init(const signed char* w_codes, signed char* h_codes0, signed char* h_codes1, int B_, int H_) {
-  B = B_; H = H_;
-  int rc = make_tensor_map_3d(&mapW, CU_TENSOR_MAP_DATA_TYPE_UINT8, w_codes, H, 3ull * H, 1, H, 3ull * H * H, FS_KB,
-                              FS_UNITS);
+int FusedFwd::init(const signed char* w_codes, signed char* h_codes0, signed char* h_codes1, const float* gi,
+                   const float* h0, float* out, float* save, int T_, int B_, int H_) {
+  T = T_; B = B_; H = H_;
+  const unsigned long long uH = H, uB = B, uT = T;
+  int rc = make_tensor_map_3d(&mapW, CU_TENSOR_MAP_DATA_TYPE_UINT8, w_codes, uH, 3 * uH, 1, uH, 3 * uH * uH, FS_KB, FS_UNITS);
   if (rc) return rc;
   signed char* bufs[2] = {h_codes0, h_codes1};
   for (int i = 0; i < 2; ++i) {
-    rc = make_tensor_map_3d(&mapH[i], CU_TENSOR_MAP_DATA_TYPE_UINT8, bufs[i], H, B, 1, H, (unsigned long long)B * H,
-                            FS_KB, FS_BM);
+    rc = make_tensor_map_3d(&mapH[i], CU_TENSOR_MAP_DATA_TYPE_UINT8, bufs[i], uH, uB, 1, uH, uB * uH, FS_KB, FS_BM);
     if (rc) return rc;
   }
+  // fp32 tiles of [128 rows][32 units]: gi[T][B][3H], h0[B][H], out[T][B][H], save[4T][B][H]
+  rc = make_tensor_map_3d(&mapGi, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, gi, 3 * uH, uB, uT, 3 * uH * 4, uB * 3 * uH * 4, FS_UNITS, FS_BM);
+  if (rc) return rc;
+  rc = make_tensor_map_3d(&mapH0, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, h0, uH, uB, 1, uH * 4, uB * uH * 4, FS_UNITS, FS_BM);
+  if (rc) return rc;
+  rc = make_tensor_map_3d(&mapOut, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, out, uH, uB, uT, uH * 4, uB * uH * 4, FS_UNITS, FS_BM);
+  if (rc) return rc;
+  has_save = save != nullptr;
+  rc = make_tensor_map_3d(&mapSave, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, has_save ? save : out, uH, uB, has_save ? 4 * uT : uT,
+                          uH * 4, uB * uH * 4, FS_UNITS, FS_BM);
+  if (rc) return rc;
   nkb = cdiv(H, FS_KB);
-  stages = nkb < 7 ? nkb : 7;
-  smem = stages * FS_STAGE + 1024;
-  return prepare_once(reinterpret_cast<const void*>(tc_fwd_step_kernel), FS_MAX_STAGES * FS_STAGE + 1024);
+  return prepare_once(reinterpret_cast<const void*>(tc_fwd_step_kernel), FS_SMEM);
 }
 
-int FusedFwd::step(int t, int T, int src, const float* gi, const float* h_prev, const float* col_scale,
-                   const float* bh, float* out_t, float* save, signed char* codes_next, float alpha, Quant qin,
-                   Quant qout, cudaStream_t st) const {
+int FusedFwd::step(int t, int src, const float* col_scale, const float* bh, signed char* codes_next, float alpha,
+                   Quant qin, Quant qout, cudaStream_t st) const {
   FusedFwdArgs a;
   memset(&a, 0, sizeof(a));
-  a.gi = gi; a.h_prev = h_prev; a.col_scale = col_scale; a.bh = bh; a.out_t = out_t; a.save = save;
-  a.codes_next = codes_next; a.t = t; a.T = T; a.B = B; a.H = H; a.nkb = nkb; a.stages = stages;
-  a.alpha = alpha; a.qin = qin; a.qout = qout;
+  a.col_scale = col_scale; a.bh = bh; a.codes_next = codes_next; a.t = t; a.T = T; a.B = B; a.H = H; a.nkb = nkb;
+  a.has_save = has_save ? 1 : 0; a.alpha = alpha; a.qin = qin; a.qout = qout;
   const dim3 grid(H / FS_UNITS, cdiv(B, FS_BM));
-  tc_fwd_step_kernel<<<grid, FS_THREADS, smem, st>>>(mapH[src], mapW, a);
+  tc_fwd_step_kernel<<<grid, FS_THREADS, FS_SMEM, st>>>(mapH[src], mapW, mapGi, t == 0 ? mapH0 : mapOut, mapOut, mapSave, a);
   note_launch();
   return B200GRU_OK;
 }
