@@ -158,9 +158,10 @@ class DeviceWorkload:
         self.x, self.h0 = x.to(dev), h0.to(dev)
         del x, h0
         self.bucket = GradBucket(list(self.layer.parameters())) if (world > 1 and cfg["train"]) else None
-        # small problems are launch-bound: capture the whole step (forward, loss, backward) once
+        # up to about a thousand batch rows per GPU the step is bound by launch and per-step latency
+        # (thousands of small dependent kernels): capture the whole step (forward, loss, backward) once
         self.graphed = None
-        if graph and self.T * self.B <= 16384:
+        if graph and (self.B <= 1024 or graph == "all"):
             from gru_triton_b200 import _lib
             from gru_triton_b200.graphed import GraphedStep
             n0 = _lib.launch_count()
@@ -666,6 +667,8 @@ def main():
     ap.add_argument("--no-kinds", dest="kinds", action="store_false")
     ap.add_argument("--no-c5", dest="c5", action="store_false", help="skip the config-5 record of the default run")
     ap.add_argument("--no-graph", dest="graph", action="store_false", help="issue the kernels of a step one by one")
+    ap.add_argument("--graph-all", dest="graph", action="store_const", const="all",
+                    help="capture the step in a CUDA graph whatever its size (default: small problems only)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     if args.impl == "reference":
