@@ -160,12 +160,24 @@ class DeviceWorkload:
         self.bucket = GradBucket(list(self.layer.parameters())) if (world > 1 and cfg["train"]) else None
         # up to about a thousand batch rows per GPU the step is bound by launch and per-step latency
         # (thousands of small dependent kernels): capture the whole step (forward, loss, backward) once
-        self.graphed = None
+        self.graphed, self.collective_in_graph = None, False
         if graph and (self.B <= 1024 or graph == "all"):
             from gru_triton_b200 import _lib
             from gru_triton_b200.graphed import GraphedStep
             n0 = _lib.launch_count()
-            self.graphed = GraphedStep(self._body, [self.x, self.h0], warmup=3)
+            if self.bucket is not None:
+                # the gradient all-reduce is a stream operation like the rest: capture it with the step
+                try:
+                    self.collective_in_graph = True
+                    self.graphed = GraphedStep(self._body, [self.x, self.h0], warmup=3)
+                except Exception as e:                      # pragma: no cover - depends on the NCCL build
+                    print(f"[bench] capturing the all-reduce failed ({type(e).__name__}: {e}); it runs eagerly",
+                          file=sys.stderr)
+                    self.collective_in_graph = False
+                    torch.cuda.synchronize()
+                    n0 = _lib.launch_count()
+            if self.graphed is None:
+                self.graphed = GraphedStep(self._body, [self.x, self.h0], warmup=3)
             self.graph_launches = (_lib.launch_count() - n0) / 4      # 3 warm-up passes + the captured one
 
     # -- one pass of the hot path through the public API -----------------------
@@ -177,12 +189,14 @@ class DeviceWorkload:
         out, _ = self.layer(x, h0)
         loss = out.sum()
         loss.backward()
+        if self.bucket is not None and self.collective_in_graph:
+            self.bucket.all_reduce()              # one flat NCCL all-reduce, gradients written back
         return loss
 
     def step(self, x, h0):
         r = self.graphed(x, h0) if self.graphed is not None else self._body(x, h0)
-        if self.bucket is not None:
-            self.bucket.all_reduce()              # one flat NCCL all-reduce, gradients written back
+        if self.bucket is not None and not self.collective_in_graph:
+            self.bucket.all_reduce()
         return r
 
     def scan_only_forward(self):
@@ -331,6 +345,21 @@ def run_c5_record(dev, rank, world, flush, sync_all, max_over_ranks, peaks):
     return rec
 
 
+def shutdown(world):
+    """Leave a multi-rank run: captured graphs that contain a collective must be gone, and every rank
+    past its last collective, before the process group is torn down."""
+    import torch.distributed as dist
+    if world > 1:
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        # A destroyed process group can wait for ever on a communicator that a captured graph still
+        # references; all results are printed, so leave without running destructors.
+        os._exit(0)
+
+
 def run_device(args):
     import torch.distributed as dist
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -417,8 +446,7 @@ def run_device(args):
         scan_bytes, Tm, Bm, Hm = wl.scan_fwd_bytes(), wl.T, wl.B, wl.H
 
     if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
+        shutdown(world)
         return
 
     peak_gbs = float(peaks.get("hbm_gbs", 6650.0))
@@ -471,8 +499,7 @@ def run_device(args):
     if args.kinds and world == 1 and args.config == "c1":
         line["kinds"] = kinds_table(dev, flush, sync_all)
     print(json.dumps(line))
-    if world > 1:
-        dist.destroy_process_group()
+    shutdown(world)
 
 
 def config_dict(name, cfg, B_per_gpu, world, override):
