@@ -50,10 +50,14 @@ CONFIGS = {
 # summarised under profiles/ (the same bench command under ncu; c2 captured at --T 128 and scaled by
 # T, since the kernel streams gi/out once per time step).  None where no capture exists.
 ROOFLINE_TRAFFIC = {
-    "c1": dict(bytes=15.85e6, T=64),
-    "c2": dict(bytes=514.3e6, T=128),
-    "c4": dict(bytes=215.0e6, T=128),
+    "c1": dict(bytes=15.86e6, T=64),
+    "c2": dict(bytes=512.6e6, T=128),
+    "c3": dict(bytes=13.11e6, T=64),
+    "c4": dict(bytes=212.7e6, T=128),
 }
+# config 5: one launch of the fused forward step at B = 512 rows per GPU (profiles/): 3.15 MB of weight
+# codes (independent of B) + 8.98 MB that scale with the rows (gi[t], h_{t-1}, hidden codes)
+C5_STEP_TRAFFIC = dict(fixed=3.15e6, per_512_rows=8.98e6)
 
 
 # ---------------------------------------------------------------------------
@@ -302,10 +306,11 @@ def tensor_roofline(wl, k_ms, scan_launches, peaks):
     flops = 2.0 * wl.T * wl.B * wl.H * 3 * wl.H
     peak_tf = float(peaks.get("bf16_tflops_sustained", 1400.0))
     ach = flops / (k_ms * 1e-3) / 1e12
-    return {"kernel": "tc_gemm_kernel (+ gate_fwd_kernel), one pair per time step", "bound": "tensor",
+    return {"kernel": "tc_fwd_step_kernel, one launch per time step", "bound": "tensor",
             "achieved": ach, "peak": peak_tf, "unit": "TFLOP/s", "frac": ach / peak_tf,
             "peak_source": "measured (sustained bf16)" if peaks else "fallback",
-            "traffic": None, "launch_ms": k_ms / max(scan_launches, 1), "per_step_us": k_ms * 1e3 / wl.T,
+            "traffic": C5_STEP_TRAFFIC["fixed"] + C5_STEP_TRAFFIC["per_512_rows"] * wl.B / 512.0,
+            "launch_ms": k_ms / max(scan_launches, 1), "per_step_us": k_ms * 1e3 / wl.T,
             "launches_per_call": scan_launches, "algorithmic_flops_per_launch": flops / wl.T,
             "note": "each step is a small product (B x 3H x H) on the serial chain: the fraction of the tensor "
                     "peak is bounded by per-step latency, reported as per_step_us"}
