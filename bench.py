@@ -306,10 +306,12 @@ def tensor_roofline(wl, k_ms, scan_launches, peaks):
     flops = 2.0 * wl.T * wl.B * wl.H * 3 * wl.H
     peak_tf = float(peaks.get("bf16_tflops_sustained", 1400.0))
     ach = flops / (k_ms * 1e-3) / 1e12
-    return {"kernel": "tc_fwd_step_kernel, one launch per time step", "bound": "tensor",
+    fused = getattr(wl, "cfg", {}).get("wbits", 32) <= 8 and getattr(wl, "cfg", {}).get("quant", False)
+    return {"kernel": ("tc_fwd_step_kernel, one launch per time step" if fused
+                       else "tc_gemm_kernel + gate_fwd_kernel, one pair per time step"), "bound": "tensor",
             "achieved": ach, "peak": peak_tf, "unit": "TFLOP/s", "frac": ach / peak_tf,
             "peak_source": "measured (sustained bf16)" if peaks else "fallback",
-            "traffic": C5_STEP_TRAFFIC["fixed"] + C5_STEP_TRAFFIC["per_512_rows"] * wl.B / 512.0,
+            "traffic": (C5_STEP_TRAFFIC["fixed"] + C5_STEP_TRAFFIC["per_512_rows"] * wl.B / 512.0) if fused else None,
             "launch_ms": k_ms / max(scan_launches, 1), "per_step_us": k_ms * 1e3 / wl.T,
             "launches_per_call": scan_launches, "algorithmic_flops_per_launch": flops / wl.T,
             "note": "each step is a small product (B x 3H x H) on the serial chain: the fraction of the tensor "
@@ -458,7 +460,7 @@ def run_device(args):
     achieved = scan_bytes / (k_ms * 1e-3) / 1e9
     if tensor_main:
         class _W:
-            T, B, H = Tm, Bm, Hm
+            T, B, H, cfg = Tm, Bm, Hm, dict(CONFIGS[args.config])
         roofline = tensor_roofline(_W, k_ms, scan_launches, peaks)
     else:
         latency_bound = cfg["kind"] != "diagonal"
