@@ -291,17 +291,26 @@ def scan_forward(kind: str, gi: torch.Tensor, h0: torch.Tensor, W: torch.Tensor,
 
 
 def scan_forward_teacher_forced(kind: str, gi, h_prev_all, W, bh,
-                                h_in_quant: Quant = None):
+                                h_in_quant: Quant = None, wide: bool = False):
     """One step from every given predecessor state: h_raw[t] from h_prev_all[t].
 
     Used by the int8 tie protocol: feeding the device's own ``h_{t-1}`` makes every
     step an independent comparison, so a single rounding tie cannot cascade.
+
+    ``wide``: the input fake-quant runs in the inputs' own precision (its codes are part of the
+    reference semantics), everything after it -- hidden product, gates, blend -- in float64, so the
+    returned h_raw carries no summation-order noise of its own (an fp32 CPU product of H terms
+    differs between BLAS builds and thread counts by more than a tie window of 1e-4 code units).
     """
     T, B, _ = gi.shape
-    raw = torch.empty_like(h_prev_all)
+    raw = torch.empty_like(h_prev_all, dtype=torch.float64 if wide else h_prev_all.dtype)
+    Ww, bw = (W.double(), bh.double()) if wide else (W, bh)
     for t in range(T):
         hq, _ = fake_quant(h_prev_all[t], h_in_quant)
-        raw[t] = gate_math(gi[t], hidden_op(kind, hq, W), bh, h_prev_all[t])[4]
+        if wide:
+            raw[t] = gate_math(gi[t].double(), hidden_op(kind, hq.double(), Ww), bw, h_prev_all[t].double())[4]
+        else:
+            raw[t] = gate_math(gi[t], hidden_op(kind, hq, W), bh, h_prev_all[t])[4]
     return raw
 
 
