@@ -2,6 +2,9 @@
 // Nothing here allocates or synchronises; all work is enqueued on the caller's stream.
 
 #include <atomic>
+#include <map>
+#include <mutex>
+#include <utility>
 #include <cstdio>
 #include <cstring>
 
@@ -32,6 +35,29 @@ int check_launch(const char* what) {
   if (e == cudaSuccess) return B200GRU_OK;
   snprintf(g_last_error, sizeof(g_last_error), "%s: %s", what, cudaGetErrorString(e));
   return B200GRU_LAUNCH_FAILURE;
+}
+
+int allow_dynamic_smem(const void* kernel, size_t bytes) {
+  static std::mutex mu;
+  static std::map<std::pair<int, const void*>, int> limit;      // opt-in bytes granted, -1 = failed
+  int dev = 0;
+  cudaGetDevice(&dev);
+  std::lock_guard<std::mutex> lk(mu);
+  auto key = std::make_pair(dev, kernel);
+  auto it = limit.find(key);
+  if (it == limit.end()) {
+    int optin = 0;
+    cudaFuncAttributes fa;
+    cudaError_t e = cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+    if (e == cudaSuccess) e = cudaFuncGetAttributes(&fa, kernel);
+    if (e == cudaSuccess) {
+      optin -= (int)fa.sharedSizeBytes;               // the opt-in limit covers static + dynamic
+      e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, optin);
+    }
+    if (e != cudaSuccess) { cudaGetLastError(); optin = -1; }
+    it = limit.emplace(key, optin).first;
+  }
+  return (it->second >= 0 && bytes <= (size_t)it->second) ? B200GRU_OK : B200GRU_UNSUPPORTED;
 }
 
 __global__ void reduce_partials_kernel(const float* __restrict__ src, int nparts, size_t row_stride, size_t n,
@@ -114,10 +140,11 @@ static size_t workspace_bytes(const Dims& d, int backward) {
     case B200GRU_DIAGONAL:
       return backward ? diag_bwd_workspace_bytes(d.T, d.B, d.H) : 0;
     case B200GRU_BUTTERFLY: {
-      if (!backward) return 0;
-      const size_t w = bfly_wgrad_scratch_bytes(d.T, d.B, d.Hpad, d.nstages);
+      const size_t twp = align_up(d.w_elems * sizeof(float), 256);      // twiddles in pass order
+      if (!backward) return twp;
+      const size_t w = bfly_wgrad_scratch_bytes(d.T, d.B, d.H, d.Hpad, d.nstages);
       if (w == (size_t)-1) return (size_t)-1;
-      return s_need + w + bias_grads_scratch_bytes(d.T, d.B, d.H);
+      return s_need + w + align_up(bias_grads_scratch_bytes(d.T, d.B, d.H), 256) + twp;
     }
   }
   return (size_t)-1;
@@ -197,6 +224,10 @@ static int scan_forward_impl(const b200gru_shape* shape, const float* gi, const 
       if (rc) return rc;
       a.gi = gi; a.h0 = h0; a.h0_tail = h0; a.tw = W; a.bh = bh; a.out = out; a.save = save;
       a.qin = qi; a.qout = qo;
+      float* twp = static_cast<float*>(workspace);
+      rc = bfly2_permute_twiddles(a, twp, st);
+      if (rc) return rc;
+      a.twp = twp;
       return bfly_launch_forward(a, st);
     }
   }
@@ -271,13 +302,17 @@ static int scan_backward_impl(const b200gru_shape* shape, const float* gi, const
     }
     case B200GRU_BUTTERFLY: {
       float* S_ws = reinterpret_cast<float*>(ws);
-      const size_t wg = bfly_wgrad_scratch_bytes(d.T, d.B, d.Hpad, d.nstages);
+      const size_t wg = bfly_wgrad_scratch_bytes(d.T, d.B, d.H, d.Hpad, d.nstages);
       float* part_w = reinterpret_cast<float*>(ws + s_off);
       float* part_b = reinterpret_cast<float*>(ws + s_off + wg);
+      float* twp = reinterpret_cast<float*>(ws + s_off + wg + align_up(bias_grads_scratch_bytes(d.T, d.B, d.H), 256));
       BflyArgs a;
       int rc = fill_bfly(d, &a);
       if (rc) return rc;
       a.tw = W; a.bh = bh; a.qin = qi; a.qout = qo;
+      rc = bfly2_permute_twiddles(a, twp, st);
+      if (rc) return rc;
+      a.twp = twp;
       const float* S = save;
       if (S == nullptr) {
         // gate recompute: the forward kernel, teacher-forced over all T*B rows (T = 1)

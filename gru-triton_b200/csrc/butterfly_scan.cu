@@ -472,8 +472,7 @@ static size_t bwd_smem(int BT, int H, int Hpad, size_t tw_bytes) {
 
 template <typename K>
 static int set_smem(K kernel, size_t bytes) {
-  return cudaFuncSetAttribute((const void*)kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes) ==
-                 cudaSuccess ? 0 : B200GRU_UNSUPPORTED;
+  return allow_dynamic_smem((const void*)kernel, bytes);
 }
 
 int bfly_launch_forward(BflyArgs a, cudaStream_t st) {
@@ -552,13 +551,19 @@ static bool wgrad_geometry(int T, int B, int Hpad, int ns, int* RT, int* spg, in
   return false;
 }
 
-size_t bfly_wgrad_scratch_bytes(int T, int B, int Hpad, int ns) {
+size_t bfly_wgrad_scratch_bytes(int T, int B, int H, int Hpad, int ns) {
   int RT, spg, ng, nsplit, rps; size_t smem;
   if (!wgrad_geometry(T, B, Hpad, ns, &RT, &spg, &ng, &nsplit, &rps, &smem)) return (size_t)-1;
-  return align_up((size_t)nsplit * 3 * ns * (Hpad / 2) * 16, 256);
+  const size_t general = align_up((size_t)nsplit * 3 * ns * (Hpad / 2) * 16, 256);
+  const size_t staged = bfly2_wgrad_scratch_bytes(T, B, H, Hpad, ns);
+  return staged > general ? staged : general;
 }
 
 int bfly_launch_wgrad(BflyArgs a, float* partial, float* dtw, cudaStream_t st) {
+  if (test_kernel_choice(0) == 0) {
+    const int rc2 = bfly2_launch_wgrad(a, partial, dtw, st);
+    if (rc2 >= 0) return rc2;
+  }
   int RT, spg, ng, nsplit, rps; size_t smem;
   if (!wgrad_geometry(a.T, a.B, a.Hpad, a.nstages, &RT, &spg, &ng, &nsplit, &rps, &smem)) return B200GRU_UNSUPPORTED;
   dim3 grid(nsplit, 3, ng);

@@ -20,6 +20,7 @@ struct BflyArgs {
   const float* h0;        // rows [0, h0_rows)
   const float* h0_tail;   // rows [h0_rows, B): previous hidden states taken from `out` (gate recompute)
   const float* tw;        // [3][nstages][Hpad/2][2][2]
+  const float* twp;       // staged kernels: the same twiddles in pass order (bfly2_permute_twiddles), or NULL
   const float* bh;
   float* out;             // may be NULL (gate recompute)
   float* save;            // [4][T][B][H] or NULL
@@ -42,11 +43,14 @@ struct BflyArgs {
 int build_bfly_passes(int logn, int nblocks, BflyPass* passes, int max_passes);
 int bfly_launch_forward(BflyArgs a, cudaStream_t st);
 // butterfly_scan2.cu: staged variants; return -1 when they do not apply to the problem
+int bfly2_permute_twiddles(const BflyArgs& a, float* twp, cudaStream_t st);
 int bfly2_launch_forward(BflyArgs a, int want_bt, cudaStream_t st);
 int bfly2_launch_backward(BflyArgs a, int want_bt, cudaStream_t st);
+size_t bfly2_wgrad_scratch_bytes(int T, int B, int H, int Hpad, int nstages);   // 0: does not apply
+int bfly2_launch_wgrad(BflyArgs a, float* partial, float* dtw, cudaStream_t st);
 int bfly_read_status(int reset);
 int bfly_launch_backward(BflyArgs a, cudaStream_t st);
-size_t bfly_wgrad_scratch_bytes(int T, int B, int Hpad, int nstages);
+size_t bfly_wgrad_scratch_bytes(int T, int B, int H, int Hpad, int nstages);
 int bfly_launch_wgrad(BflyArgs a, float* partial, float* dtw, cudaStream_t st);
 
 // block_gemm.cu: bias gradient (shared by dense, block-diagonal and butterfly)

@@ -82,6 +82,43 @@ __device__ __forceinline__ void stage_dispatch(float (&v)[BT][1 << R], const flo
   else stage_regs<R, 0, BT, TRANSPOSE>(v, tw);
 }
 
+// Twiddle order used by the staged kernels.  Within one stage the reference order is by pair
+// index; a thread of a radix-2^R pass needs pairs pair0(q) + (idx << lb), idx < 2^(R-1), which are
+// 2^(R-1) * 16 bytes (or more) apart between neighbouring lanes: a 4-way bank conflict on every
+// float4 load.  The staged kernels therefore read a copy in which every stage is stored in the
+// order its pass consumes it, position idx * G + q (G items per gate), so that a warp reads 32
+// consecutive float4.  tw_source_index maps such a position back to the pair index.
+__host__ __device__ inline int tw_source_index(const BflyPass& pd, int logn, int half, int k) {
+  if (pd.r >= 2) {
+    const int R = pd.r, lb = pd.lb;
+    const int G = half >> (R - 1);
+    const int idx = k / G, q = k - idx * G;
+    const int low = q & ((1 << lb) - 1), high = q >> lb;
+    return ((high << (lb + R - 1)) | low) + (idx << lb);
+  }
+  if (pd.nst == 1 && pd.lb >= 2 && logn >= 3) {      // the 4-pairs-per-thread single-stage pass
+    const int G4 = half >> 2;
+    const int j = k / G4, q = k - j * G4;
+    return 4 * q + j;
+  }
+  return k;
+}
+
+// dst[g][l][k] = src[g][l][tw_source_index(pass of l, k)]
+__global__ void __launch_bounds__(256)
+bfly_permute_twiddles_kernel(const float4* __restrict__ src, float4* __restrict__ dst, const BflyArgs a) {
+  const int half = a.Hpad >> 1;
+  const int total = 3 * a.nstages * half;
+  const int i = blockIdx.x * 256 + threadIdx.x;
+  if (i >= total) return;
+  const int k = i % half;
+  const int gl = i / half;
+  const int l = gl % a.nstages;
+  int p = 0;
+  while (p + 1 < a.npasses && l >= a.passes[p].l0 + a.passes[p].nst) ++p;
+  dst[i] = src[(size_t)gl * half + tw_source_index(a.passes[p], a.logn, half, k)];
+}
+
 // A float4 of twiddles from shared memory (by 32-bit shared address) or from global memory.
 template <bool TW_SMEM>
 __device__ __forceinline__ float4 tw_load(const float4* p) {
@@ -99,21 +136,21 @@ __device__ __forceinline__ float4 tw_load(const float4* p) {
 template <int R, int BT, bool TRANSPOSE, bool TW_SMEM>
 __device__ __forceinline__ void run_pass2_r(const BflyPass pd, const float* src, int src_gate, float* dst,
                                             int dst_gate, const float4* twp, int tw_gate, int tw_l0, int Hpad,
-                                            int RSZ, int logn) {
+                                            int RSZ, int logn, int ngates = 3, int nthr = NT) {
   constexpr int E = 1 << R;
   const int lb = pd.lb;
   const int pb0 = pd.pb[0], pb1 = pd.pb[1], pb2 = pd.pb[2];
   const int lgG = logn - R;                             // log2 of the groups per gate
   const int G = 1 << lgG;
   const int half = Hpad >> 1;
-  for (int item = threadIdx.x; item < 3 * G; item += NT) {
+  for (int item = threadIdx.x; item < ngates * G; item += nthr) {
     const int g = item >> lgG, q = item & (G - 1);
     const int low = q & ((1 << lb) - 1), high = q >> lb;
     const int base = (high << (lb + R)) | low;
 
-    // The idx-th pair of this group has the same twiddle index at every stage of the pass:
-    // removing the stage's own bit from the position leaves (high, idx, low).
-    const int pair0 = (high << (lb + R - 1)) | low;
+    // The idx-th pair of this group has the same twiddle index at every stage of the pass
+    // (removing the stage's own bit from the position leaves (high, idx, low)); in the permuted
+    // copy it sits at idx * G + q.
     float4 t[3][E / 2];
     int pbit[3];
 #pragma unroll
@@ -122,9 +159,9 @@ __device__ __forceinline__ void run_pass2_r(const BflyPass pd, const float* src,
       if (s < pd.nst) {
         const int so = TRANSPOSE ? (pd.nst - 1 - s) : s;          // stage offset inside the pass
         pbit[s] = so == 0 ? pb0 : (so == 1 ? pb1 : pb2);
-        const float4* tl = twp + (g * tw_gate + (pd.l0 + so - tw_l0) * half + pair0);
+        const float4* tl = twp + (g * tw_gate + (pd.l0 + so - tw_l0) * half + q);
 #pragma unroll
-        for (int idx = 0; idx < E / 2; ++idx) t[s][idx] = tw_load<TW_SMEM>(tl + (idx << lb));
+        for (int idx = 0; idx < E / 2; ++idx) t[s][idx] = tw_load<TW_SMEM>(tl + (idx << lgG));
       }
     }
 
@@ -199,21 +236,21 @@ __device__ __forceinline__ void run_pass2_r(const BflyPass pd, const float* src,
 template <int BT, bool TRANSPOSE, bool TW_SMEM>
 __device__ __forceinline__ void run_pass2_r1w4(const BflyPass pd, const float* src, int src_gate, float* dst,
                                                int dst_gate, const float4* twp, int tw_gate, int tw_l0, int Hpad,
-                                               int RSZ, int logn) {
+                                               int RSZ, int logn, int ngates = 3, int nthr = NT) {
   const int lb = pd.lb;
   const int lgG = logn - 3;                             // groups of 4 pairs per gate
   const int G = 1 << lgG;
   const int half = Hpad >> 1;
   const int S = 1 << lb;
-  for (int item = threadIdx.x; item < 3 * G; item += NT) {
+  for (int item = threadIdx.x; item < ngates * G; item += nthr) {
     const int g = item >> lgG, q = item & (G - 1);
     const int pair = q << 2;                            // first of 4 adjacent pairs
     const int low = pair & (S - 1), high = pair >> lb;
     const int i0 = (high << (lb + 1)) | low;
-    const float4* tl = twp + (g * tw_gate + (pd.l0 - tw_l0) * half + pair);
+    const float4* tl = twp + (g * tw_gate + (pd.l0 - tw_l0) * half + q);
     float4 t[4];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) t[j] = tw_load<TW_SMEM>(tl + j);
+    for (int j = 0; j < 4; ++j) t[j] = tw_load<TW_SMEM>(tl + (j << lgG));
     const int p0 = sw(i0), p1 = sw(i0 + S);
     const float* sp = src + (size_t)g * src_gate;
     float* dp = dst + (size_t)g * dst_gate;
@@ -242,12 +279,12 @@ __device__ __forceinline__ void run_pass2_r1w4(const BflyPass pd, const float* s
 template <int BT, bool TRANSPOSE, bool TW_SMEM>
 __device__ __forceinline__ void run_pass2_s(const BflyPass pd, const float* src, int src_gate, float* dst,
                                             int dst_gate, const float4* twp, int tw_gate, int tw_l0, int Hpad,
-                                            int RSZ, int logn) {
-  if (pd.r == 3) run_pass2_r<3, BT, TRANSPOSE, TW_SMEM>(pd, src, src_gate, dst, dst_gate, twp, tw_gate, tw_l0, Hpad, RSZ, logn);
-  else if (pd.r == 2) run_pass2_r<2, BT, TRANSPOSE, TW_SMEM>(pd, src, src_gate, dst, dst_gate, twp, tw_gate, tw_l0, Hpad, RSZ, logn);
+                                            int RSZ, int logn, int ngates = 3, int nthr = NT) {
+  if (pd.r == 3) run_pass2_r<3, BT, TRANSPOSE, TW_SMEM>(pd, src, src_gate, dst, dst_gate, twp, tw_gate, tw_l0, Hpad, RSZ, logn, ngates, nthr);
+  else if (pd.r == 2) run_pass2_r<2, BT, TRANSPOSE, TW_SMEM>(pd, src, src_gate, dst, dst_gate, twp, tw_gate, tw_l0, Hpad, RSZ, logn, ngates, nthr);
   else if (pd.nst == 1 && pd.lb >= 2 && logn >= 3)
-    run_pass2_r1w4<BT, TRANSPOSE, TW_SMEM>(pd, src, src_gate, dst, dst_gate, twp, tw_gate, tw_l0, Hpad, RSZ, logn);
-  else run_pass2_r<1, BT, TRANSPOSE, TW_SMEM>(pd, src, src_gate, dst, dst_gate, twp, tw_gate, tw_l0, Hpad, RSZ, logn);
+    run_pass2_r1w4<BT, TRANSPOSE, TW_SMEM>(pd, src, src_gate, dst, dst_gate, twp, tw_gate, tw_l0, Hpad, RSZ, logn, ngates, nthr);
+  else run_pass2_r<1, BT, TRANSPOSE, TW_SMEM>(pd, src, src_gate, dst, dst_gate, twp, tw_gate, tw_l0, Hpad, RSZ, logn, ngates, nthr);
 }
 
 // Twiddle supply shared by the forward and the backward kernel.
@@ -313,7 +350,7 @@ bfly_fwd2_kernel(const BflyArgs a) {
   const unsigned gbar = bar0 + 16;
 
   TwiddleFeed feed;
-  feed.gtw = reinterpret_cast<const float4*>(a.tw);
+  feed.gtw = reinterpret_cast<const float4*>(a.twp);
   feed.buf = twbuf; feed.bar0 = bar0; feed.mode = a.tw_mode; feed.half = half; feed.nstages = a.nstages;
   feed.npasses = a.npasses;
   const unsigned total_passes = (unsigned)a.T * (unsigned)a.npasses;
@@ -466,7 +503,7 @@ bfly_bwd2_kernel(const BflyArgs a) {
   const unsigned pbar = bar0 + 16;
 
   TwiddleFeed feed;
-  feed.gtw = reinterpret_cast<const float4*>(a.tw);
+  feed.gtw = reinterpret_cast<const float4*>(a.twp);
   feed.buf = twbuf; feed.bar0 = bar0; feed.mode = a.tw_mode; feed.half = half; feed.nstages = a.nstages;
   feed.npasses = a.npasses;
   const unsigned total_passes = (unsigned)a.T * (unsigned)a.npasses;
@@ -603,6 +640,198 @@ bfly_bwd2_kernel(const BflyArgs a) {
   }
 }
 
+
+// ---------------------------------------------------------------------------
+// twiddle gradients: dt[g][l][pair][m_new][m_old] = sum over rows (t, b) of d_new[m_new] * old[m_old]
+// ---------------------------------------------------------------------------
+// Rows are independent here (every h_{t-1} and every dgh_t is known), so the grid is
+// (row splits, 3 gates).  A CTA keeps its gate's twiddles and one accumulator per twiddle in shared
+// memory.  Per batch of RB rows it runs the forward passes, keeping the input vector of every pass,
+// then walks the passes backwards: a thread re-runs the stages of its item in registers (so the
+// inputs of the inner stages never touch memory), forms the four products of each of its pairs,
+// sums them over the rows of the batch in registers and adds them to the shared accumulators once
+// per batch, and pushes d through the transposed stages.  Every (stage, pair) belongs to exactly
+// one thread, and the split partials are added in a fixed order afterwards: no atomics.
+constexpr int WG_NT = 128;
+
+template <int R, int P>
+__device__ __forceinline__ void wgrad_stage(float (&d)[1 << R], const float (&in)[1 << R],
+                                            const float4 (&tw)[(1 << R) / 2], float4 (&g)[(1 << R) / 2]) {
+  int idx = 0;
+#pragma unroll
+  for (int e = 0; e < (1 << R); ++e) {
+    if (e & (1 << P)) continue;
+    const float4 t = tw[idx];
+    const float d0 = d[e], d1 = d[e | (1 << P)];
+    const float o0 = in[e], o1 = in[e | (1 << P)];
+    g[idx].x = fmaf(d0, o0, g[idx].x); g[idx].y = fmaf(d0, o1, g[idx].y);
+    g[idx].z = fmaf(d1, o0, g[idx].z); g[idx].w = fmaf(d1, o1, g[idx].w);
+    d[e] = fmaf(t.z, d1, t.x * d0);
+    d[e | (1 << P)] = fmaf(t.y, d0, t.w * d1);
+    ++idx;
+  }
+}
+
+template <int R>
+__device__ __forceinline__ void wgrad_stage_dispatch(float (&d)[1 << R], const float (&in)[1 << R],
+                                                     const float4 (&tw)[(1 << R) / 2], float4 (&g)[(1 << R) / 2], int p) {
+  if (R >= 3 && p == 2) wgrad_stage<R, (R >= 3 ? 2 : 0)>(d, in, tw, g);
+  else if (R >= 2 && p == 1) wgrad_stage<R, (R >= 2 ? 1 : 0)>(d, in, tw, g);
+  else wgrad_stage<R, 0>(d, in, tw, g);
+}
+
+// One pass (NST stages spanning R adjacent stride bits) of the backward walk for the rows
+// [0, nrows) of the batch.  xin: the pass's input vectors [RB][RSZ]; dv: gradient w.r.t. the pass's
+// output on entry, w.r.t. its input on return.
+template <int R, int NST>
+__device__ __forceinline__ void wgrad_pass_r(const BflyPass pd, const float* xin, float* dv, int nrows,
+                                             const float4* twsm, float4* acc, int Hpad, int RSZ, int logn) {
+  constexpr int E = 1 << R;
+  const int lb = pd.lb;
+  const int lgG = logn - R;
+  const int G = 1 << lgG;
+  const int half = Hpad >> 1;
+  const int pb0 = pd.pb[0], pb1 = pd.pb[1], pb2 = pd.pb[2];
+  const bool w4 = pd.r < 2 && pd.nst == 1 && pd.lb >= 2 && logn >= 3;
+  const bool uniform = (lb + R <= 6) || (lb >= 6);
+  const int estride = (lb >= 6) ? ((1 << lb) + (8 << (lb - 6))) : (1 << lb);
+  for (int q = threadIdx.x; q < G; q += WG_NT) {
+    const int low = q & ((1 << lb) - 1), high = q >> lb;
+    const int base = (high << (lb + R)) | low;
+    float4 t[NST][E / 2], g[NST][E / 2];            // twiddles and accumulators in the permuted order
+    // a lone stage at stride >= 4 is stored for the 4-pairs-per-thread forward pass: pair p sits at
+    // (p & 3) * (half / 4) + (p >> 2)
+    const int tpos = (R == 1 && w4) ? ((q & 3) * (half >> 2) + (q >> 2)) : q;
+#pragma unroll
+    for (int s = 0; s < NST; ++s) {
+      const float4* tl = twsm + ((pd.l0 + s) * half + tpos);
+#pragma unroll
+      for (int idx = 0; idx < E / 2; ++idx) {
+        t[s][idx] = tl[idx << lgG];
+        g[s][idx] = make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+    }
+    const int pbase = sw(base);
+    int off[E];
+#pragma unroll
+    for (int e = 0; e < E; ++e) off[e] = uniform ? pbase + e * estride : sw(base + (e << lb));
+
+#pragma unroll 1
+    for (int b = 0; b < nrows; ++b) {
+      float v[1][E], d[E], in[NST][E];
+#pragma unroll
+      for (int e = 0; e < E; ++e) { v[0][e] = xin[b * RSZ + off[e]]; d[e] = dv[b * RSZ + off[e]]; }
+#pragma unroll
+      for (int s = 0; s < NST; ++s) {
+#pragma unroll
+        for (int e = 0; e < E; ++e) in[s][e] = v[0][e];
+        if (s + 1 < NST) stage_dispatch<R, 1, false>(v, t[s], s == 0 ? pb0 : pb1);
+      }
+      if (NST >= 3) wgrad_stage_dispatch<R>(d, in[NST >= 3 ? 2 : 0], t[NST >= 3 ? 2 : 0], g[NST >= 3 ? 2 : 0], pb2);
+      if (NST >= 2) wgrad_stage_dispatch<R>(d, in[NST >= 2 ? 1 : 0], t[NST >= 2 ? 1 : 0], g[NST >= 2 ? 1 : 0], pb1);
+      wgrad_stage_dispatch<R>(d, in[0], t[0], g[0], pb0);
+#pragma unroll
+      for (int e = 0; e < E; ++e) dv[b * RSZ + off[e]] = d[e];
+    }
+#pragma unroll
+    for (int s = 0; s < NST; ++s) {
+      float4* al = acc + ((pd.l0 + s) * half + tpos);
+#pragma unroll
+      for (int idx = 0; idx < E / 2; ++idx) {
+        float4 c = al[idx << lgG];
+        c.x += g[s][idx].x; c.y += g[s][idx].y; c.z += g[s][idx].z; c.w += g[s][idx].w;
+        al[idx << lgG] = c;
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void wgrad_pass(const BflyPass pd, const float* xin, float* dv, int nrows,
+                                           const float4* twsm, float4* acc, int Hpad, int RSZ, int logn) {
+  // a pass of span r has at least r stages (the stride moves by at most one bit per stage)
+  if (pd.r == 3) wgrad_pass_r<3, 3>(pd, xin, dv, nrows, twsm, acc, Hpad, RSZ, logn);
+  else if (pd.r == 2 && pd.nst == 3) wgrad_pass_r<2, 3>(pd, xin, dv, nrows, twsm, acc, Hpad, RSZ, logn);
+  else if (pd.r == 2) wgrad_pass_r<2, 2>(pd, xin, dv, nrows, twsm, acc, Hpad, RSZ, logn);
+  else if (pd.nst == 3) wgrad_pass_r<1, 3>(pd, xin, dv, nrows, twsm, acc, Hpad, RSZ, logn);
+  else if (pd.nst == 2) wgrad_pass_r<1, 2>(pd, xin, dv, nrows, twsm, acc, Hpad, RSZ, logn);
+  else wgrad_pass_r<1, 1>(pd, xin, dv, nrows, twsm, acc, Hpad, RSZ, logn);
+}
+
+// shared memory: twiddles [ns][half] float4 | accumulators [ns][half] float4 |
+//                pass inputs [npasses][RB][RSZ] | d [RB][RSZ]
+template <int RB>
+__global__ void __launch_bounds__(WG_NT)
+bfly_wgrad2_kernel(const BflyArgs a, float* __restrict__ partial, int rows_per_split) {
+  extern __shared__ __align__(128) float smem[];
+  __shared__ BflyPass spass[BFLY_MAX_PASSES];
+  if (threadIdx.x == 0) {
+#pragma unroll
+    for (int i = 0; i < BFLY_MAX_PASSES; ++i) spass[i] = a.passes[i];
+  }
+  const int H = a.H, Hpad = a.Hpad, half = Hpad >> 1, ns = a.nstages, RSZ = a.RSZ, P4 = Hpad >> 2;
+  const int TB = a.T * a.B;
+  const int g = blockIdx.y;
+  const int r_begin = blockIdx.x * rows_per_split;
+  const int r_end = min(TB, r_begin + rows_per_split);
+  const int tid = threadIdx.x;
+  const int nacc = ns * half;
+
+  float4* twsm = reinterpret_cast<float4*>(smem);
+  float4* acc = twsm + nacc;
+  float* bnd = reinterpret_cast<float*>(acc + nacc);
+  float* dvec = bnd + (size_t)a.npasses * RB * RSZ;
+  const float4* twg = reinterpret_cast<const float4*>(a.twp) + (size_t)g * nacc;
+  for (int i = tid; i < nacc; i += WG_NT) {
+    twsm[i] = twg[i];
+    acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  for (int i = tid; i < (a.npasses + 1) * RB * RSZ; i += WG_NT) bnd[i] = 0.f;     // includes dvec
+  __syncthreads();
+
+  for (int r0 = r_begin; r0 < r_end; r0 += RB) {
+    const int nrows = min(RB, r_end - r0);
+    for (int idx = tid; idx < RB * P4; idx += WG_NT) {
+      const int b = idx / P4, i = (idx - b * P4) << 2;
+      const int tb = r0 + b;
+      float4 hv = make_float4(0.f, 0.f, 0.f, 0.f), dv = hv;
+      if (b < nrows && i < H) {
+        hv = (tb < a.B) ? *reinterpret_cast<const float4*>(a.h0 + (size_t)tb * H + i)
+                        : *reinterpret_cast<const float4*>(a.out_c + (size_t)(tb - a.B) * H + i);
+        if (a.qin.enabled) {
+          hv.x = fake_quant<true>(hv.x, a.qin); hv.y = fake_quant<true>(hv.y, a.qin);
+          hv.z = fake_quant<true>(hv.z, a.qin); hv.w = fake_quant<true>(hv.w, a.qin);
+        }
+        dv = __ldcs(reinterpret_cast<const float4*>(a.dgi_c + (size_t)tb * 3 * H + (size_t)g * H + i));
+        if (g == 2) {                                             // dgh_n = dgi_n * r
+          const float4 r = __ldcs(reinterpret_cast<const float4*>(a.S + (size_t)tb * H + i));
+          dv.x *= r.x; dv.y *= r.y; dv.z *= r.z; dv.w *= r.w;
+        }
+      }
+      *reinterpret_cast<float4*>(bnd + b * RSZ + sw(i)) = hv;
+      *reinterpret_cast<float4*>(dvec + b * RSZ + sw(i)) = dv;
+    }
+    __syncthreads();
+    for (int p = 0; p + 1 < a.npasses; ++p) {
+      run_pass2_s<RB, false, true>(spass[p], bnd + (size_t)p * RB * RSZ, 0, bnd + (size_t)(p + 1) * RB * RSZ, 0, twsm, 0, 0,
+                                   Hpad, RSZ, a.logn, 1, WG_NT);
+      __syncthreads();
+    }
+    for (int p = a.npasses - 1; p >= 0; --p) {
+      wgrad_pass(spass[p], bnd + (size_t)p * RB * RSZ, dvec, nrows, twsm, acc, Hpad, RSZ, a.logn);
+      __syncthreads();
+    }
+  }
+  // partial sums leave in the reference's pair order
+  float4* dst = reinterpret_cast<float4*>(partial) + ((size_t)blockIdx.x * 3 + g) * nacc;
+  for (int p = 0; p < a.npasses; ++p) {
+    const BflyPass pd = spass[p];
+    for (int i = tid; i < pd.nst * half; i += WG_NT) {
+      const int s = i / half, k = i - s * half;
+      dst[(pd.l0 + s) * half + tw_source_index(pd, a.logn, half, k)] = acc[(pd.l0 + s) * half + k];
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------
@@ -644,14 +873,23 @@ static bool plan2(bool fwd, const BflyArgs& a, int want_bt, int* BT, int* mode, 
 
 template <typename K>
 static int set_smem2(K kernel, size_t bytes) {
-  return cudaFuncSetAttribute((const void*)kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes) ==
-                 cudaSuccess ? 0 : B200GRU_UNSUPPORTED;
+  return allow_dynamic_smem((const void*)kernel, bytes);
+}
+
+// Writes the copy of the twiddles the staged kernels read (see tw_source_index) into `twp`.
+int bfly2_permute_twiddles(const BflyArgs& a, float* twp, cudaStream_t st) {
+  if (!aligned16(a.tw) || !aligned16(twp)) return B200GRU_INVALID_ARGUMENT;
+  const int total = 3 * a.nstages * (a.Hpad / 2);
+  bfly_permute_twiddles_kernel<<<cdiv(total, 256), 256, 0, st>>>(reinterpret_cast<const float4*>(a.tw),
+                                                                  reinterpret_cast<float4*>(twp), a);
+  note_launch();
+  return check_launch("bfly_permute_twiddles_kernel");
 }
 
 // returns -1 if the staged variant does not apply (caller falls back), else a status
 int bfly2_launch_forward(BflyArgs a, int want_bt, cudaStream_t st) {
-  if (!(aligned16(a.gi) && aligned16(a.h0) && aligned16(a.tw) && aligned16(a.out) && aligned16(a.save) &&
-        aligned16(a.h0_tail) && aligned16(a.bh))) return -1;
+  if (a.twp == nullptr || !(aligned16(a.gi) && aligned16(a.h0) && aligned16(a.twp) && aligned16(a.out) &&
+                            aligned16(a.save) && aligned16(a.h0_tail) && aligned16(a.bh))) return -1;
   int BT, mode; size_t smem;
   if (!plan2(true, a, want_bt, &BT, &mode, &smem)) return -1;
   a.tw_mode = mode; a.RSZ = rsz_of(a.Hpad);
@@ -673,8 +911,8 @@ int bfly2_launch_forward(BflyArgs a, int want_bt, cudaStream_t st) {
 }
 
 int bfly2_launch_backward(BflyArgs a, int want_bt, cudaStream_t st) {
-  if (!(aligned16(a.gi) && aligned16(a.h0) && aligned16(a.tw) && aligned16(a.out_c) && aligned16(a.S) &&
-        aligned16(a.dout) && aligned16(a.dgi) && aligned16(a.dh0))) return -1;
+  if (a.twp == nullptr || !(aligned16(a.gi) && aligned16(a.h0) && aligned16(a.twp) && aligned16(a.out_c) &&
+                            aligned16(a.S) && aligned16(a.dout) && aligned16(a.dgi) && aligned16(a.dh0))) return -1;
   int BT, mode; size_t smem;
   if (!plan2(false, a, want_bt, &BT, &mode, &smem)) return -1;
   a.tw_mode = mode; a.RSZ = rsz_of(a.Hpad);
@@ -693,6 +931,64 @@ int bfly2_launch_backward(BflyArgs a, int want_bt, cudaStream_t st) {
   if (rc) return rc;
   note_launch();
   return check_launch("bfly_bwd2_kernel");
+}
+
+
+// Geometry of the staged twiddle-gradient kernel; false if it does not apply (twiddles and
+// accumulators of one gate must fit shared memory next to two rows of pass inputs).
+static bool wgrad2_geometry(int T, int B, int H, int Hpad, int ns, int npasses, int* RB, int* nsplit,
+                            int* rows_per_split, size_t* smem) {
+  if (H % 4 != 0 || Hpad < 8 || npasses < 1) return false;
+  const size_t lim = optin_smem2() - 1024;             // static: the pass table
+  const size_t fixed = (size_t)2 * ns * (Hpad / 2) * 16;
+  const size_t per_row = (size_t)(npasses + 1) * rsz_of(Hpad) * sizeof(float);
+  int rb = 0;
+  if (fixed + 4 * per_row <= lim) rb = 4;
+  else if (fixed + 2 * per_row <= lim) rb = 2;
+  if (rb == 0) return false;
+  *RB = rb;
+  *smem = fixed + rb * per_row;
+  const int per_sm = (int)((lim + 1024) / (*smem + 1024)) > 0 ? (int)((lim + 1024) / (*smem + 1024)) : 1;
+  const int TB = T * B;
+  int want = (148 * per_sm) / 3;
+  const int max_by_rows = cdiv(TB, 4 * rb);
+  if (want > max_by_rows) want = max_by_rows;
+  if (want < 1) want = 1;
+  const int rps = cdiv(cdiv(TB, want), rb) * rb;
+  *rows_per_split = rps;
+  *nsplit = cdiv(TB, rps);
+  return true;
+}
+
+size_t bfly2_wgrad_scratch_bytes(int T, int B, int H, int Hpad, int ns) {
+  BflyPass tmp[BFLY_MAX_PASSES];
+  int logn = 0;
+  while ((1 << logn) < Hpad) ++logn;
+  const int np = build_bfly_passes(logn, ns / (logn > 0 ? logn : 1), tmp, BFLY_MAX_PASSES);
+  int RB, nsplit, rps; size_t smem;
+  if (np < 1 || !wgrad2_geometry(T, B, H, Hpad, ns, np, &RB, &nsplit, &rps, &smem)) return 0;
+  return align_up((size_t)nsplit * 3 * ns * (Hpad / 2) * 16, 256);
+}
+
+// returns -1 if the staged variant does not apply (caller falls back), else a status
+int bfly2_launch_wgrad(BflyArgs a, float* partial, float* dtw, cudaStream_t st) {
+  if (a.twp == nullptr || !(aligned16(a.h0) && aligned16(a.twp) && aligned16(a.out_c) && aligned16(a.S) &&
+                            aligned16(a.dgi_c) && aligned16(partial)))
+    return -1;
+  int RB, nsplit, rps; size_t smem;
+  if (!wgrad2_geometry(a.T, a.B, a.H, a.Hpad, a.nstages, a.npasses, &RB, &nsplit, &rps, &smem)) return -1;
+  a.RSZ = rsz_of(a.Hpad);
+  dim3 grid(nsplit, 3);
+  int rc;
+  if (RB == 4) { rc = set_smem2(bfly_wgrad2_kernel<4>, smem); if (!rc) bfly_wgrad2_kernel<4><<<grid, WG_NT, smem, st>>>(a, partial, rps); }
+  else         { rc = set_smem2(bfly_wgrad2_kernel<2>, smem); if (!rc) bfly_wgrad2_kernel<2><<<grid, WG_NT, smem, st>>>(a, partial, rps); }
+  if (rc) return rc;
+  note_launch();
+  rc = check_launch("bfly_wgrad2_kernel");
+  if (rc) return rc;
+  const size_t n = (size_t)3 * a.nstages * (a.Hpad / 2) * 4;
+  launch_reduce_partials(partial, nsplit, n, n, dtw, st);
+  return check_launch("reduce_partials");
 }
 
 int bfly_read_status(int reset) {

@@ -176,6 +176,10 @@ int test_kernel_choice(int slot);
 // Launch bookkeeping shared by all translation units (defined in api.cu).
 void note_launch(int n = 1);
 int check_launch(const char* what);
+// Once per (device, kernel): raise the kernel's dynamic shared-memory limit to the device's opt-in
+// maximum (less the kernel's static shared memory).  Returns 0, or B200GRU_UNSUPPORTED when `bytes`
+// exceeds that (or the call failed).
+int allow_dynamic_smem(const void* kernel, size_t bytes);
 
 // Deterministic reduction of `nparts` partial vectors of length n, `row_stride` floats apart:
 // dst[i] = src[0*row_stride + i] + src[1*row_stride + i] + ... (fixed order).
