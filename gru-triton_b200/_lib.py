@@ -74,6 +74,7 @@ SIGNATURES = {
     "b200gru_tc_gemm": (_I, [_GP, _P]),
     "b200gru_tc_gemm_splits": (_I, [_GP, _I]),
     "b200gru_split_bf16": (_I, [_P, _P, _Z, _Z, _I, _P, _I, _P]),
+    "b200gru_split_f16": (_I, [_P, _P, _I, _I, _Z, _P, _P]),
     "b200gru_calibration_workspace_bytes": (_Z, [_SP]),
     "b200gru_calibration_scan": (_I, [_SP, _P, _P, _P, _P, _I, ctypes.c_double, _P, _P, _I, _P, _P, _I, _P, _P, _Z, _P]),
     "b200gru_device_status": (_I, [_I]),

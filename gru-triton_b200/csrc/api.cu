@@ -123,6 +123,10 @@ static size_t wt_bytes(const Dims& d) {
 }
 static size_t tc_max(size_t a, size_t b) { return a > b ? a : b; }
 static bool step_path(const Dims& d) { return d.kind == B200GRU_DENSE && tc::tc_dense_path(d.B, d.H); }
+// dense problems on the cluster kernels whose weight gradient is one tensor-core product
+static bool tc_wgrad_path(const Dims& d) {
+  return d.kind == B200GRU_DENSE && !step_path(d) && tc::tc_weight_grads_applies(d.T, d.B, d.H);
+}
 
 // backward: 0 forward, 1 backward that recomputes the gates, 2 backward that is given `save`
 static size_t workspace_bytes(const Dims& d, int backward) {
@@ -136,6 +140,10 @@ static size_t workspace_bytes(const Dims& d, int backward) {
                         : tc_max(tc::tc_dense_fwd_scratch_bytes(d.T, d.B, d.H, false),
                                  tc::tc_dense_fwd_scratch_bytes(d.T, d.B, d.H, true));
       if (!backward) return wt_bytes(d);
+      if (tc_wgrad_path(d))
+        return s_need + align_up(bias_grads_scratch_bytes(d.T, d.B, d.H), 256) +
+               tc_max(tc::tc_weight_grads_scratch_bytes(d.T, d.B, d.H, false),
+                      tc::tc_weight_grads_scratch_bytes(d.T, d.B, d.H, true));
       return s_need + weight_grads_scratch_bytes(d.T, d.B, d.H, d.nb, d.Hb);
     case B200GRU_DIAGONAL:
       return backward ? diag_bwd_workspace_bytes(d.T, d.B, d.H) : 0;
@@ -297,6 +305,14 @@ static int scan_backward_impl(const b200gru_shape* shape, const float* gi, const
       a.qin = qi; a.qout = qo;
       int rc = launch_block_scan(false, cfg, a, d.nb, st);
       if (rc) return rc;
+      if (tc_wgrad_path(d)) {
+        // off-chain products on the tensor cores: bias sums first (their scratch leads), then dW
+        char* sc = ws + s_off;
+        rc = launch_bias_grads(dgi, S, reinterpret_cast<float*>(sc), dbh, d.T, d.B, d.H, st);
+        if (rc) return rc;
+        sc += align_up(bias_grads_scratch_bytes(d.T, d.B, d.H), 256);
+        return tc::launch_tc_weight_grads(dgi, S, h0, out, qi, dW, sc, d.T, d.B, d.H, st);
+      }
       g.S = const_cast<float*>(S);
       return launch_weight_grads(g, st);
     }

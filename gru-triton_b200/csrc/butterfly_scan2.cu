@@ -719,8 +719,19 @@ __device__ __forceinline__ void wgrad_pass_r(const BflyPass pd, const float* xin
 #pragma unroll 1
     for (int b = 0; b < nrows; ++b) {
       float v[1][E], d[E], in[NST][E];
+      if (E == 8 && lb == 0) {                     // 8 adjacent positions: two float4 per vector
+        const float4 x0 = *reinterpret_cast<const float4*>(xin + b * RSZ + pbase);
+        const float4 x1 = *reinterpret_cast<const float4*>(xin + b * RSZ + pbase + 4);
+        const float4 d0 = *reinterpret_cast<const float4*>(dv + b * RSZ + pbase);
+        const float4 d1 = *reinterpret_cast<const float4*>(dv + b * RSZ + pbase + 4);
+        const float xs[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+        const float ds[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
 #pragma unroll
-      for (int e = 0; e < E; ++e) { v[0][e] = xin[b * RSZ + off[e]]; d[e] = dv[b * RSZ + off[e]]; }
+        for (int e = 0; e < E; ++e) { v[0][e] = xs[e & 7]; d[e] = ds[e & 7]; }
+      } else {
+#pragma unroll
+        for (int e = 0; e < E; ++e) { v[0][e] = xin[b * RSZ + off[e]]; d[e] = dv[b * RSZ + off[e]]; }
+      }
 #pragma unroll
       for (int s = 0; s < NST; ++s) {
 #pragma unroll
@@ -730,8 +741,13 @@ __device__ __forceinline__ void wgrad_pass_r(const BflyPass pd, const float* xin
       if (NST >= 3) wgrad_stage_dispatch<R>(d, in[NST >= 3 ? 2 : 0], t[NST >= 3 ? 2 : 0], g[NST >= 3 ? 2 : 0], pb2);
       if (NST >= 2) wgrad_stage_dispatch<R>(d, in[NST >= 2 ? 1 : 0], t[NST >= 2 ? 1 : 0], g[NST >= 2 ? 1 : 0], pb1);
       wgrad_stage_dispatch<R>(d, in[0], t[0], g[0], pb0);
+      if (E == 8 && lb == 0) {
+        *reinterpret_cast<float4*>(dv + b * RSZ + pbase) = make_float4(d[0], d[1], d[2 % E], d[3 % E]);
+        *reinterpret_cast<float4*>(dv + b * RSZ + pbase + 4) = make_float4(d[4 % E], d[5 % E], d[6 % E], d[7 % E]);
+      } else {
 #pragma unroll
-      for (int e = 0; e < E; ++e) dv[b * RSZ + off[e]] = d[e];
+        for (int e = 0; e < E; ++e) dv[b * RSZ + off[e]] = d[e];
+      }
     }
 #pragma unroll
     for (int s = 0; s < NST; ++s) {
@@ -790,6 +806,7 @@ bfly_wgrad2_kernel(const BflyArgs a, float* __restrict__ partial, int rows_per_s
 
   for (int r0 = r_begin; r0 < r_end; r0 += RB) {
     const int nrows = min(RB, r_end - r0);
+#pragma unroll 4
     for (int idx = tid; idx < RB * P4; idx += WG_NT) {
       const int b = idx / P4, i = (idx - b * P4) << 2;
       const int tb = r0 + b;

@@ -12,8 +12,8 @@ bool to_internal(const b200gru_gemm_args* a, tc::TcGemm* g) {
   if (a == nullptr) return false;
   if (a->npairs < 1 || a->npairs > tc::TC_MAX_PAIRS) return false;
   memset(g, 0, sizeof(*g));
-  g->kind = a->dtype == 1 ? tc::TC_KIND_I8 : tc::TC_KIND_BF16;
-  if (a->dtype != 0 && a->dtype != 1) return false;
+  if (a->dtype < 0 || a->dtype > 2) return false;
+  g->kind = a->dtype == 1 ? tc::TC_KIND_I8 : (a->dtype == 2 ? tc::TC_KIND_F16 : tc::TC_KIND_BF16);
   g->M = a->M; g->N = a->N; g->K = a->K;
   g->A = a->A; g->B = a->B;
   g->a_planes = a->a_planes; g->b_planes = a->b_planes;
@@ -51,6 +51,11 @@ int b200gru_split_bf16(const float* src, void* dst, size_t n, size_t plane_strid
                        const float* col_scale, int ncols, void* stream) {
   return tc::launch_split_planes(src, dst, n, plane_stride, planes, col_scale, ncols,
                                  static_cast<cudaStream_t>(stream));
+}
+
+int b200gru_split_f16(const float* src, void* dst, int rows, int cols, size_t plane_stride, float* inv_scale,
+                      void* stream) {
+  return tc::launch_split_rows_f16(src, dst, rows, cols, plane_stride, inv_scale, static_cast<cudaStream_t>(stream));
 }
 
 int b200gru_test_wait_timeout(void* stream) {

@@ -10,6 +10,7 @@
 
 #include <cuda.h>         // CUtensorMap and its enums (types only; the encoder is looked up at run time)
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 
 #include "common.cuh"
 
@@ -131,11 +132,12 @@ __device__ __forceinline__ uint64_t umma_smem_desc(uint32_t saddr, uint32_t lbo_
 
 // Instruction descriptor of tcgen05.mma (dense, no negate, no saturate):
 //   bits [4,6) accumulator format (1 = F32, 2 = S32)   bits [7,10) A format   bits [10,13) B format
-//   (kind::f16: 1 = BF16; kind::i8: 1 = signed 8 bit)   bit 15 A is MN-major   bit 16 B is MN-major
+//   (kind::f16: 0 = F16, 1 = BF16; kind::i8: 1 = signed 8 bit)   bit 15 A is MN-major   bit 16 B is MN-major
 //   bits [17,23) N >> 3   bits [24,29) M >> 4
-__host__ __device__ constexpr uint32_t umma_idesc(bool is_i8, bool a_mn, bool b_mn, int M, int N) {
-  return ((is_i8 ? 2u : 1u) << 4) | (1u << 7) | (1u << 10) | ((a_mn ? 1u : 0u) << 15) | ((b_mn ? 1u : 0u) << 16) |
-         ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+__host__ __device__ constexpr uint32_t umma_idesc(bool is_i8, bool a_mn, bool b_mn, int M, int N,
+                                                  uint32_t ab_format = 1u) {
+  return ((is_i8 ? 2u : 1u) << 4) | (ab_format << 7) | (ab_format << 10) | ((a_mn ? 1u : 0u) << 15) |
+         ((b_mn ? 1u : 0u) << 16) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
 
 // D[tmem] (+)= A[smem] * B[smem]; issued by one thread.

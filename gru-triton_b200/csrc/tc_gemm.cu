@@ -48,6 +48,7 @@ struct GemmParams {
   int stages;
   int chunk_kb;                              // k-blocks summed in tensor memory before a drain
   int accumulate;
+  unsigned ab_format;                        // kind::f16 operand format: 0 = fp16, 1 = bf16
   float alpha;
   const float* row_scale;
   const float* col_scale;
@@ -67,7 +68,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   constexpr int UMMA_K = 32 / ES;                       // K of one tcgen05.mma
   constexpr int A_PLANE_BYTES = BM * BK * ES;           // 16 KB
   constexpr int B_PLANE_BYTES = BN * BK * ES;
-  constexpr uint32_t IDESC = umma_idesc(I8, A_MN, B_MN, BM, BN);
+  const uint32_t IDESC = umma_idesc(I8, A_MN, B_MN, BM, BN, p.ab_format);
   constexpr int NC = BN / 2;                            // accumulator columns per epilogue thread
   typedef typename std::conditional<I8, int, float>::type AccT;
 
@@ -278,6 +279,56 @@ split_planes_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ d
   }
 }
 
+// Two fp16 planes of every row of src[rows][cols], scaled by a power of two of the row's own:
+// s_r = 2^(15 - e) with max|row| = m * 2^e, m in [0.5, 1), so the largest scaled element lies in
+// [2^14, 2^15).  hi = RN16(x * s), lo = RN16(x * s - hi) (the difference is exact in fp32), and
+// inv_scale[r] = 1 / s_r exactly.  hi + lo carries 22 significant bits of every element that is
+// not below 2^-17 of its row's largest; smaller ones keep an absolute error of 2^-40 of it.
+// One warp per row; the second read of the row hits L1.
+__global__ void __launch_bounds__(256)
+split_rows_f16_kernel(const float* __restrict__ src, __half* __restrict__ dst, int rows, int cols, size_t plane_stride,
+                      float* __restrict__ inv_scale) {
+  const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const float4* s4 = reinterpret_cast<const float4*>(src + (size_t)row * cols);
+  const int c4 = cols >> 2;
+  float mx = 0.f;
+  for (int i = lane; i < c4; i += 32) {
+    const float4 v = s4[i];
+    mx = fmaxf(fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))), mx);
+  }
+#pragma unroll
+  for (int off = 16; off >= 1; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+  int e = 0;
+  float s = 1.0f, inv = 1.0f;
+  if (mx > 0.f && mx < 3.0e38f) {
+    frexpf(mx, &e);
+    e = max(-110, min(110, e));               // both 2^(15-e) and 2^(e-15) stay normal
+    s = ldexpf(1.0f, 15 - e);
+    inv = ldexpf(1.0f, e - 15);
+  }
+  if (lane == 0) inv_scale[row] = inv;
+  __half* d = dst + (size_t)row * cols;
+  for (int i = lane; i < c4; i += 32) {
+    const float4 v = s4[i];
+    const float x[4] = {v.x * s, v.y * s, v.z * s, v.w * s};
+    __half hi[4], lo[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      hi[k] = __float2half_rn(x[k]);
+      lo[k] = __float2half_rn(x[k] - __half2float(hi[k]));
+    }
+    uint2 a, b;
+    a.x = (uint32_t)__half_as_ushort(hi[0]) | ((uint32_t)__half_as_ushort(hi[1]) << 16);
+    a.y = (uint32_t)__half_as_ushort(hi[2]) | ((uint32_t)__half_as_ushort(hi[3]) << 16);
+    b.x = (uint32_t)__half_as_ushort(lo[0]) | ((uint32_t)__half_as_ushort(lo[1]) << 16);
+    b.y = (uint32_t)__half_as_ushort(lo[2]) | ((uint32_t)__half_as_ushort(lo[3]) << 16);
+    *reinterpret_cast<uint2*>(d + i * 4) = a;
+    *reinterpret_cast<uint2*>(d + plane_stride + i * 4) = b;
+  }
+}
+
 // Test probe of the bounded waits: one CTA arms an mbarrier for bytes that nothing ever sends and
 // waits on it with a budget of about a millisecond; the wait gives up, sets the health word and
 // the kernel returns normally.
@@ -441,10 +492,13 @@ int launch_tc_gemm(const TcGemm& g, cudaStream_t st) {
   else if (i8) p.chunk_kb = p.kb_per_split;                   // int32 accumulation is exact
   else p.chunk_kb = (32 / (4 * g.npairs)) > 0 ? 32 / (4 * g.npairs) : 1;   // at most 32 accumulation steps per chunk
   p.accumulate = g.accumulate;
+  p.ab_format = (g.kind == TC_KIND_F16) ? 0u : 1u;
   p.alpha = g.alpha; p.row_scale = g.row_scale; p.col_scale = g.col_scale; p.bias = g.bias;
   p.C = g.C; p.ldc = g.ldc; p.split_stride = g.split_stride;
 
-  const CUtensorMapDataType dt = i8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  const CUtensorMapDataType dt = i8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                    : (g.kind == TC_KIND_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                                             : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16);
   alignas(64) CUtensorMap ta, tb;
   int rc;
   // K-major: dims {K, rows, planes}, box {128 bytes of K, tile rows}.  MN-major: dims {rows(M|N), K, planes},
@@ -491,6 +545,19 @@ int launch_split_planes(const float* src, void* dst, size_t n, size_t plane_stri
                                                                     plane_stride, planes, col_scale, ncols);
   note_launch();
   return check_launch("split_planes_kernel");
+}
+
+int launch_split_rows_f16(const float* src, void* dst, int rows, int cols, size_t plane_stride, float* inv_scale,
+                          cudaStream_t st) {
+  if (src == nullptr || dst == nullptr || inv_scale == nullptr || rows < 0 || cols <= 0 || (cols & 3) ||
+      (plane_stride & 3))
+    return B200GRU_INVALID_ARGUMENT;
+  if (!aligned16(src) || (reinterpret_cast<uintptr_t>(dst) & 7u)) return B200GRU_INVALID_ARGUMENT;
+  if (rows == 0) return B200GRU_OK;
+  split_rows_f16_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(src, static_cast<__half*>(dst), rows, cols,
+                                                                    plane_stride, inv_scale);
+  note_launch();
+  return check_launch("split_rows_f16_kernel");
 }
 
 }  // namespace tc

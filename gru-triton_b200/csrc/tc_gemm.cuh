@@ -10,10 +10,10 @@ constexpr int TC_MAX_PAIRS = 9;
 constexpr int TC_MAX_STAGES = 8;
 constexpr int TC_SMEM_BUDGET = 208 * 1024;    // bytes of the operand ring
 
-enum { TC_KIND_BF16 = 0, TC_KIND_I8 = 1 };
+enum { TC_KIND_BF16 = 0, TC_KIND_I8 = 1, TC_KIND_F16 = 2 };
 
 // C[split][M,N] (fp32, row stride ldc) = alpha * row_scale[m] * col_scale[n] * sum_q A_{pa[q]} . B_{pb[q]}^T + bias[n]
-// over the K slice of each split.  Operand element type: bf16 (kind 0) or int8 (kind 1).
+// over the K slice of each split.  Operand element type: bf16 (kind 0), int8 (kind 1) or fp16 (kind 2).
 //   a_mn == 0: A is [planes][M][lda], K contiguous.   a_mn == 1: A is [planes][K][lda], M contiguous.
 //   b_mn == 0: B is [planes][N][ldb], K contiguous.   b_mn == 1: B is [planes][K][ldb], N contiguous.
 // Strides are in elements; bases 16-byte aligned, byte strides multiples of 16; N % 4 == 0.
@@ -55,6 +55,11 @@ int launch_wait_timeout_probe(cudaStream_t st);
 // n % 4 == 0; col_scale may be NULL.
 int launch_split_planes(const float* src, void* dst, size_t n, size_t plane_stride, int planes,
                         const float* col_scale, int ncols, cudaStream_t st);
+
+// dst[0 | 1][r][c] (fp16, planes `plane_stride` elements apart) = leading / trailing half of
+// src[r][c] * 2^k_r with the power of two chosen per row; inv_scale[r] = 2^-k_r.  cols % 4 == 0.
+int launch_split_rows_f16(const float* src, void* dst, int rows, int cols, size_t plane_stride, float* inv_scale,
+                          cudaStream_t st);
 
 }  // namespace tc
 }  // namespace b200gru

@@ -553,5 +553,119 @@ int launch_tc_dense_backward(const float* h0, const TcWeights& w, const float* o
   return launch_bias_grads(dgi, S, bias_part, dbh, T, B, H, st);
 }
 
+
+// ---- weight gradient of the dense cluster path on the tensor cores ----------------------------------
+// dW[3H,H] = dgh^T[3H, T*B] . fq_in(h_prev)[T*B, H] with every operand known (the serial scan has
+// finished): one pass writes the bf16 operand planes of dgh (dgh_n = dgi_n * r) and of h_{t-1},
+// one GEMM with both operands MN-major contracts over the T*B rows.
+struct WgOperandArgs {
+  const float* dgi;        // [T*B][3H]
+  const float* r;          // [T*B][H]
+  const float* h0;         // [B][H]
+  const float* out;        // [T][B][H]
+  __nv_bfloat16* dgh_op;   // [2 planes][T*B][3H]
+  __nv_bfloat16* h_op;     // [1 plane of codes | 2 planes][T*B][H]
+  size_t rows;             // T*B
+  int B, H, h_codes;
+  Quant qin;
+};
+
+__global__ void __launch_bounds__(256)
+wgrad_operands_kernel(const WgOperandArgs a) {
+  const int H4 = a.H >> 2;
+  const size_t idx = (size_t)blockIdx.x * 256 + threadIdx.x;
+  if (idx >= a.rows * H4) return;
+  const size_t row = idx / H4;
+  const int u = (int)(idx - row * H4) * 4;
+  const int H = a.H;
+  const float* d = a.dgi + row * 3 * H + u;
+  const float4 dr = ld4s(d), dz = ld4s(d + H), dn = ld4s(d + 2 * H);
+  const float4 r4 = ld4s(a.r + row * H + u);
+  const float4 hp = (row < (size_t)a.B) ? ld4(a.h0 + row * H + u) : ld4(a.out + (row - a.B) * H + u);
+  float vr[4] = {dr.x, dr.y, dr.z, dr.w}, vz[4] = {dz.x, dz.y, dz.z, dz.w};
+  float vn[4] = {dn.x * r4.x, dn.y * r4.y, dn.z * r4.z, dn.w * r4.w};
+  const size_t dps = a.rows * 3 * H;
+  __nv_bfloat16* dp = a.dgh_op + row * 3 * H + u;
+  store_planes4(dp, dps, 2, vr);
+  store_planes4(dp + H, dps, 2, vz);
+  store_planes4(dp + 2 * H, dps, 2, vn);
+  const float hv[4] = {hp.x, hp.y, hp.z, hp.w};
+  if (a.h_codes) {
+    store_h_operand(a.h_op, row * H + u, 0, 1, hv, a.qin);
+  } else {
+    float v[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) v[e] = a.qin.enabled ? fake_quant<true>(hv[e], a.qin) : hv[e];
+    store_planes4(a.h_op + row * H + u, a.rows * H, 2, v);
+  }
+}
+
+bool tc_weight_grads_applies(int T, int B, int H) {
+  return H % 8 == 0 && H >= 128 && (size_t)T * B >= 1024 && (size_t)T * B * 3 * H < ((size_t)1 << 31);
+}
+
+static TcGemm wgrad_gemm(int T, int B, int H, bool h_codes) {
+  TcGemm g;
+  memset(&g, 0, sizeof(g));
+  const long long rows = (long long)T * B;
+  g.kind = TC_KIND_BF16;
+  g.M = 3 * H; g.N = H; g.K = (int)rows;
+  g.a_planes = 2; g.b_planes = h_codes ? 1 : 2; g.a_mn = 1; g.b_mn = 1;
+  g.lda = 3 * H; g.ldb = H; g.a_plane_stride = rows * 3 * H; g.b_plane_stride = rows * H;
+  // two leading planes per fp32 operand and the cross products down to 2^-16: about 5e-6 of a term
+  g.npairs = 0;
+  for (int s2 = 0; s2 <= 1; ++s2)
+    for (int i = 0; i <= s2; ++i) {
+      const int j = s2 - i;
+      if (j < g.b_planes) { g.pa[g.npairs] = i; g.pb[g.npairs] = j; ++g.npairs; }
+    }
+  g.tile_n = 128;
+  const int tiles = cdiv(g.M, 128) * cdiv(g.N, 128);
+  // enough K slices to fill the SMs, at least 8 k-blocks each
+  int want = tiles >= 148 ? 1 : cdiv(148, tiles);
+  const int kb = cdiv(g.K, tc_gemm_kblock(g));
+  if (want > kb / 8) want = kb / 8 > 0 ? kb / 8 : 1;
+  g.split_k = tc_gemm_splits(g, want);
+  g.ldc = H; g.split_stride = (long long)3 * H * H;
+  g.alpha = 1.0f;
+  return g;
+}
+
+size_t tc_weight_grads_scratch_bytes(int T, int B, int H, bool h_codes) {
+  const size_t rows = (size_t)T * B;
+  const TcGemm g = wgrad_gemm(T, B, H, h_codes);
+  size_t n = align_up(2 * rows * 3 * H * 2, 256) + align_up((size_t)g.b_planes * rows * H * 2, 256);
+  if (g.split_k > 1) n += align_up((size_t)g.split_k * 3 * H * H * sizeof(float), 256);
+  return n;
+}
+
+int launch_tc_weight_grads(const float* dgi, const float* S, const float* h0, const float* out, Quant qin, float* dW,
+                           void* scratch, int T, int B, int H, cudaStream_t st) {
+  const bool h_codes = codes_fit_int8(qin);
+  const size_t rows = (size_t)T * B;
+  TcGemm g = wgrad_gemm(T, B, H, h_codes);
+  char* ws = static_cast<char*>(scratch);
+  __nv_bfloat16* dgh_op = reinterpret_cast<__nv_bfloat16*>(ws); ws += align_up(2 * rows * 3 * H * 2, 256);
+  __nv_bfloat16* h_op = reinterpret_cast<__nv_bfloat16*>(ws); ws += align_up((size_t)g.b_planes * rows * H * 2, 256);
+  float* part = reinterpret_cast<float*>(ws);
+
+  WgOperandArgs a;
+  memset(&a, 0, sizeof(a));
+  a.dgi = dgi; a.r = S; a.h0 = h0; a.out = out; a.dgh_op = dgh_op; a.h_op = h_op;
+  a.rows = rows; a.B = B; a.H = H; a.h_codes = h_codes ? 1 : 0; a.qin = qin;
+  const size_t n4 = rows * (H / 4);
+  wgrad_operands_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, st>>>(a);
+  note_launch();
+  int rc = check_launch("wgrad_operands_kernel");
+  if (rc) return rc;
+  g.A = dgh_op; g.B = h_op;
+  g.alpha = h_codes ? qin.scale : 1.0f;
+  g.C = g.split_k > 1 ? part : dW;
+  rc = launch_tc_gemm(g, st);
+  if (rc) return rc;
+  if (g.split_k > 1) launch_reduce_partials(part, g.split_k, (size_t)3 * H * H, (size_t)3 * H * H, dW, st);
+  return check_launch("weight gradient product");
+}
+
 }  // namespace tc
 }  // namespace b200gru

@@ -26,6 +26,13 @@ int launch_tc_dense_backward(const float* h0, const TcWeights& w, const float* o
                              float* dgi, float* dh0, float* dW, float* dbh, void* scratch, int T, int B, int H,
                              Quant qin, Quant qout, cudaStream_t st);
 
+// Weight gradient of the dense scan as one tensor-core product over all T*B rows (used after the
+// cluster kernels' serial backward): dW[3H,H] = dgh^T . fq_in(h_prev), S = r activations [T*B][H].
+bool tc_weight_grads_applies(int T, int B, int H);
+size_t tc_weight_grads_scratch_bytes(int T, int B, int H, bool h_codes);
+int launch_tc_weight_grads(const float* dgi, const float* S, const float* h0, const float* out, Quant qin, float* dW,
+                           void* scratch, int T, int B, int H, cudaStream_t st);
+
 // Per-output-row symmetric fake-quant of a weight matrix W[rows, cols] (dynamic scale
 // s_r = max(max|row|, 1e-8) / qmax, qmax = 2^(bits-1) - 1): codes (int8), scales and, optionally,
 // the fake-quantised fp32 values codes * s.  cols % 4 == 0, 2 <= bits <= 8.

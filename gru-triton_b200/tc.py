@@ -1,8 +1,8 @@
 """Tensor-core products of the GRU path (tcgen05 GEMM core of ``libb200gru.so``).
 
-* ``split_bf16`` / ``gemm``: operand preparation and the raw product
-  ``C = alpha * row_scale * col_scale * sum_pairs A_i @ B_j^T + bias`` with fp32 (bf16 planes)
-  or exact int32 (int8 codes) accumulation.
+* ``split_bf16`` / ``split_f16`` / ``gemm``: operand preparation and the raw product
+  ``C = alpha * row_scale * col_scale * sum_pairs A_i @ B_j^T + bias`` with fp32 (bf16 or fp16
+  planes) or exact int32 (int8 codes) accumulation.
 * ``linear``: the input projection ``gi = x @ Wi^T + bi`` of a whole sequence and its gradients,
   row-chunked so that operand planes stay small; with ``weight_bits <= 8`` the weights are
   fake-quantised per output row on the device and multiplied as exact integer codes.
@@ -27,6 +27,8 @@ PAIRS_EXACT_B = {1: [(0, 0)], 2: [(0, 0), (1, 0)], 3: [(0, 0), (1, 0), (2, 0)]}
 PAIRS_EXACT_A = {1: [(0, 0)], 2: [(0, 0), (0, 1)], 3: [(0, 0), (0, 1), (0, 2)]}
 PAIRS_FULL = [(0, 0), (0, 1), (1, 0), (0, 2), (1, 1), (2, 0)]          # error about 2^-24 of |a||b|
 PAIRS_FAST = [(0, 0), (0, 1), (1, 0)]                                  # error about 2^-17 of |a||b|
+# the same three products on two row-scaled fp16 planes per operand (split_f16): about 2^-22
+PAIRS_F16 = PAIRS_FAST
 
 ROW_CHUNK = 32768          # rows of x handled per operand-preparation + GEMM round
 
@@ -55,13 +57,34 @@ def split_bf16(x: torch.Tensor, planes: int = 3, col_scale: Optional[torch.Tenso
     return out
 
 
+def split_f16(x: torch.Tensor, out: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``(planes [2, R, K] float16, inv_scale [R] float32)`` with
+    ``(planes[0] + planes[1]) * inv_scale[:, None] == x`` to 22 significant bits: every row is scaled
+    by a power of two of its own before the split, ``inv_scale`` undoes it as the product's
+    ``row_scale`` (A operand) or ``col_scale`` (B operand)."""
+    if not x.is_cuda or x.dtype != torch.float32 or x.dim() != 2:
+        raise ValueError("split_f16 needs a 2-d CUDA float32 tensor")
+    x = x.contiguous()
+    R, K = x.shape
+    if K % 4:
+        raise ValueError("row length must be a multiple of 4")
+    if out is None:
+        out = torch.empty((2, R, K), device=x.device, dtype=torch.float16)
+    inv = torch.empty((R,), device=x.device, dtype=torch.float32)
+    with torch.cuda.device(x.device):
+        rc = _lib.load().b200gru_split_f16(_lib._ptr(x), _lib._ptr(out), R, K, R * K, _lib._ptr(inv), _stream(x))
+    if rc:
+        _lib._raise(rc, "split_f16")
+    return out, inv
+
+
 def gemm(A: torch.Tensor, B: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
          pairs: Optional[Sequence[Tuple[int, int]]] = None, alpha: float = 1.0,
          row_scale: Optional[torch.Tensor] = None, col_scale: Optional[torch.Tensor] = None,
          bias: Optional[torch.Tensor] = None, split_k: int = 1, tile_n: int = 0, chunk_kblocks: int = 0,
          out: Optional[torch.Tensor] = None, accumulate: bool = False, reduce_splits: bool = True) -> torch.Tensor:
     """``A``: ``[planes, M, K]`` (or ``[planes, K, M]`` with ``a_mn``); ``B``: ``[planes, N, K]``
-    (or ``[planes, K, N]`` with ``b_mn``); bf16 or int8, contiguous.  Returns fp32 ``[M, N]``.
+    (or ``[planes, K, N]`` with ``b_mn``); bf16, fp16 or int8, contiguous.  Returns fp32 ``[M, N]``.
 
     ``split_k > 1`` computes that many partial products over slices of K: they are summed in order
     unless ``reduce_splits`` is False, in which case ``out`` (``[splits, M, N]``) receives (or,
@@ -70,8 +93,8 @@ def gemm(A: torch.Tensor, B: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
         A = A[None]
     if B.dim() == 2:
         B = B[None]
-    if not (A.is_cuda and B.is_cuda) or A.dtype != B.dtype or A.dtype not in (torch.bfloat16, torch.int8):
-        raise ValueError("gemm needs CUDA operands of one dtype, bfloat16 or int8")
+    if not (A.is_cuda and B.is_cuda) or A.dtype != B.dtype or A.dtype not in (torch.bfloat16, torch.float16, torch.int8):
+        raise ValueError("gemm needs CUDA operands of one dtype, bfloat16, float16 or int8")
     A, B = A.contiguous(), B.contiguous()
     pa, (M, K) = A.shape[0], ((A.shape[2], A.shape[1]) if a_mn else (A.shape[1], A.shape[2]))
     pb, (N, Kb) = B.shape[0], ((B.shape[2], B.shape[1]) if b_mn else (B.shape[1], B.shape[2]))
@@ -80,7 +103,7 @@ def gemm(A: torch.Tensor, B: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     if pairs is None:
         pairs = [(i, j) for i in range(pa) for j in range(pb)]
     g = _lib.CGemmArgs()
-    g.dtype = 1 if A.dtype == torch.int8 else 0
+    g.dtype = {torch.bfloat16: 0, torch.int8: 1, torch.float16: 2}[A.dtype]
     g.M, g.N, g.K = M, N, K
     g.A, g.B = A.data_ptr(), B.data_ptr()
     g.a_planes, g.b_planes = pa, pb
@@ -140,15 +163,19 @@ class _LinearFunction(torch.autograd.Function):
     def forward(ctx: Any, x, W, bias, weight_bits: int):
         R, I = x.shape
         N = W.shape[0]
+        # two row-scaled fp16 planes per fp32 operand: 22 significant bits in three cross products
+        # (two when the weights are exact integer codes)
         if weight_bits <= 8:
             codes, scales, _ = _lib.quantize_rows(W, weight_bits)
-            Bop, col_scale, pairs = codes.to(torch.bfloat16)[None], scales, PAIRS_EXACT_B[3]
+            Bop, col_scale, pairs = codes.to(torch.float16)[None], scales, PAIRS_EXACT_B[2]
         else:
-            Bop, col_scale, pairs = split_bf16(W), None, PAIRS_FULL
+            Bop, col_scale = split_f16(W)
+            pairs = PAIRS_F16
         y = torch.empty((R, N), device=x.device, dtype=torch.float32)
         for r0 in range(0, R, ROW_CHUNK):
             r1 = min(R, r0 + ROW_CHUNK)
-            gemm(split_bf16(x[r0:r1]), Bop, pairs=pairs, col_scale=col_scale, bias=bias, out=y[r0:r1])
+            xp, x_inv = split_f16(x[r0:r1])
+            gemm(xp, Bop, pairs=pairs, row_scale=x_inv, col_scale=col_scale, bias=bias, out=y[r0:r1])
         ctx.save_for_backward(x, W)
         ctx.weight_bits, ctx.has_bias = weight_bits, bias is not None
         ctx.col_scale, ctx.Bop = col_scale, Bop
@@ -162,6 +189,9 @@ class _LinearFunction(torch.autograd.Function):
         N = W.shape[0]
         need_x, need_w, need_b = ctx.needs_input_grad[0], ctx.needs_input_grad[1], ctx.needs_input_grad[2] and ctx.has_bias
         dx = torch.empty_like(x) if need_x else None
+        if need_x:
+            # dx contracts over the weight rows: the bf16 form of the weights (codes are exact in it)
+            Bx = ctx.Bop.to(torch.bfloat16) if ctx.weight_bits <= 8 else split_bf16(W)
         dWq = None
         if need_w:
             chunk_rows = min(R, ROW_CHUNK)
@@ -185,9 +215,9 @@ class _LinearFunction(torch.autograd.Function):
                 # dx = dy @ fq(W): W rows are the contraction index (MN-major B)
                 if ctx.weight_bits <= 8:
                     dys = split_bf16(dy[r0:r1], col_scale=ctx.col_scale)
-                    gemm(dys, ctx.Bop, b_mn=True, pairs=PAIRS_EXACT_B[3], out=dx[r0:r1])
+                    gemm(dys, Bx, b_mn=True, pairs=PAIRS_EXACT_B[3], out=dx[r0:r1])
                 else:
-                    gemm(dyp, ctx.Bop, b_mn=True, pairs=PAIRS_FULL, out=dx[r0:r1])
+                    gemm(dyp, Bx, b_mn=True, pairs=PAIRS_FULL, out=dx[r0:r1])
         dW = None
         if need_w:
             dWq = dWq.sum(dim=0) if dWq.shape[0] > 1 else dWq[0]

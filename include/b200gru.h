@@ -191,10 +191,12 @@ int b200gru_dense_q8_backward(const float* gi, const float* h0, const float* Wq,
  *
  *   C[s][M,N] = alpha * row_scale[m] * col_scale[n] * sum_q A_{pair_a[q]} . B_{pair_b[q]}^T + bias[n]
  *
- * Operands are bf16 (dtype 0, fp32 accumulation) or int8 (dtype 1, exact int32 accumulation) and
- * come as 1..3 planes: an fp32 operand is split into bf16 terms hi + mid + lo by
- * b200gru_split_bf16 (three planes are exact), an operand on an int8 grid is one exact plane of
- * codes.  pair_a / pair_b list the plane cross products to accumulate.
+ * Operands are bf16 (dtype 0, fp32 accumulation), int8 (dtype 1, exact int32 accumulation) or
+ * fp16 (dtype 2, fp32 accumulation) and come as 1..3 planes: an fp32 operand is split into bf16
+ * terms hi + mid + lo by b200gru_split_bf16 (three planes are exact) or into two row-scaled fp16
+ * terms by b200gru_split_f16 (22 significant bits; three cross products instead of six), an
+ * operand on an int8 grid is one exact plane of codes.  pair_a / pair_b list the plane cross
+ * products to accumulate.
  *   a_mn_major == 0: A is [planes][M][lda] (K contiguous);  1: A is [planes][K][lda] (M contiguous)
  *   b_mn_major == 0: B is [planes][N][ldb] (K contiguous);  1: B is [planes][K][ldb] (N contiguous)
  * (int8 operands: K contiguous only).  Strides in elements; bases 16-byte aligned; byte strides
@@ -236,6 +238,13 @@ int b200gru_tc_gemm_splits(const b200gru_gemm_args* args, int wanted);
  * feeds fp32 tensors to tl.dot / cuBLAS directly. */
 int b200gru_split_bf16(const float* src, void* dst, size_t n, size_t plane_stride, int planes,
                        const float* col_scale, int ncols, void* stream);
+
+/* dst[0 | 1][r][c] (fp16, planes `plane_stride` elements apart) = leading / trailing fp16 term of
+ * src[r][c] * 2^k_r, with 2^k_r chosen per row so that the row's largest element lands in
+ * [2^14, 2^15); inv_scale[r] = 2^-k_r is the row_scale (A operand) or col_scale (B operand) of the
+ * product.  cols % 4 == 0.  Operand preparation like b200gru_split_bf16. */
+int b200gru_split_f16(const float* src, void* dst, int rows, int cols, size_t plane_stride, float* inv_scale,
+                      void* stream);
 
 /* Diagonal backward for callers that cannot allocate device memory.  It has no counterpart in
  * the reference (whose wrappers always allocate their scratch with torch).  Same inputs, outputs

@@ -85,6 +85,33 @@ def test_split_products_reach_fp32_accuracy():
     assert rel_err(got.cpu(), refl) < 3e-6
 
 
+def test_two_fp16_planes_reach_fp32_accuracy():
+    """Two row-scaled fp16 planes per operand, three cross products: planes * inv_scale reproduce
+    the operand to 2^-21 of each row's largest element, rows of very different magnitude (and a
+    zero row) included, and the product is as close to float64 as the six-product bf16 form."""
+    tc = _tc()
+    torch.manual_seed(1)
+    M, N, K = 384, 512, 1024
+    x = torch.randn(M, K, device="cuda")
+    x[3] *= 1e-20
+    x[5] *= 3e18
+    x[7] = 0.0
+    w = (torch.rand(N, K, device="cuda") * 2 - 1) / 32
+    xp, xi = tc.split_f16(x)
+    wp, wi = tc.split_f16(w)
+    assert bool(torch.isfinite(xp.float()).all())
+    back = (xp[0].double() + xp[1].double()) * xi.double()[:, None]
+    rowmax = x.abs().amax(dim=1).double().clamp(min=1e-300)
+    assert float(((back - x.double()).abs().amax(dim=1) / rowmax).max()) < 2.0 ** -21
+    assert float(back[7].abs().max()) == 0.0
+    # powers of two: the scale round-trips exactly
+    assert bool((torch.frexp(xi)[0] == 0.5).all())
+    ref = x.cpu().double() @ w.cpu().double().T
+    got = tc.gemm(xp, wp, pairs=tc.PAIRS_F16, row_scale=xi, col_scale=wi).cpu().double()
+    err = (got - ref).abs().amax(dim=1) / ref.abs().amax(dim=1).clamp(min=1e-300)     # per row: rows differ by 1e38
+    assert float(err.max()) < 2e-6, float(err.max())
+
+
 @pytest.mark.parametrize("rows,cols,bits", [(48, 16, 8), (96, 1024, 8), (30, 260, 4)])
 def test_weight_prep_matches_autograd(rows, cols, bits):
     """Codes, scales and values of the per-row fake-quant and its straight-through gradient
