@@ -139,6 +139,25 @@ def test_butterfly_alternate_kernels(T, B, H, extra, quant):
 
 
 @pytest.mark.parametrize("quant", [None, Q8, Q8_ASYM], ids=["fp32", "q8", "q8asym"])
+@pytest.mark.parametrize("T,B,H,h0_gain", [(8, 1, 256, 1.0), (20, 16, 256, 1.0), (33, 17, 512, 1.0), (9, 112, 512, 1.0),
+                                           (12, 5, 512, 3.0)])
+def test_dense_small_batch_cluster_shapes(T, B, H, h0_gain, quant):
+    """H = 256 / 512 at small batch (16-CTA clusters, one and several clusters, a ragged last batch
+    tile, |h0| above 1): forward and backward against the oracle; no bounded wait gave up."""
+    from gru_triton_b200 import _lib
+    fwd, bwd, _ = _mods()["dense"]
+    gi, h0, W, bh, dout = orc.make_problem("dense", T, B, H, seed=3 * T + B + H)
+    h0 = h0 * h0_gain
+    kw = dict(h_in_quant=quant[0], h_out_quant=quant[1]) if quant else {}
+    d = _cuda(gi, h0, W, bh, dout)
+    out = fwd(*d[:4], **kw)
+    grads = bwd(*d[:4], out, d[4], **kw)
+    check_forward("dense", out, gi, h0, W, bh, quant)
+    check_backward("dense", grads, gi, h0, W, bh, out, dout, quant)
+    _lib.check_device_status()
+
+
+@pytest.mark.parametrize("quant", [None, Q8, Q8_ASYM], ids=["fp32", "q8", "q8asym"])
 @pytest.mark.parametrize("T,B,H", [(16, 64, 1024), (9, 300, 256)])
 def test_diagonal_register_ring_forward_on_aligned_shapes(T, B, H, quant):
     """Shapes that normally take the bulk-copy forward kernel, forced onto the register-ring one."""
