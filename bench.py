@@ -382,8 +382,9 @@ def run_device(args):
 
     from gru_triton_b200 import _lib
     cfg = CONFIGS[args.config]
-    if args.T or args.B:
-        cfg = CONFIGS[args.config] = dict(cfg, T=args.T or cfg["T"], B=args.B or cfg["B"])
+    if args.T or args.B or args.train:
+        cfg = CONFIGS[args.config] = dict(cfg, T=args.T or cfg["T"], B=args.B or cfg["B"],
+                                          train=cfg["train"] or args.train)
     wl = DeviceWorkload(args.config, cfg, rank, world, dev, graph=args.graph)
     graph_note = ("the step (forward, loss, backward) is captured once by gru_triton_b200.graphed.GraphedStep and "
                   "replayed; gpu_launches counts the kernels of the library inside one replay"
@@ -440,7 +441,7 @@ def run_device(args):
 
     peaks = load_peaks()
     c5 = None
-    if args.c5 and args.config == "c1" and not (args.T or args.B):
+    if args.c5 and args.config == "c1" and not (args.T or args.B or args.train):
         h_bytes = wl.x_host.numel() * 4 + wl.h0_host.numel() * 4
         units_main, tensor_main = wl.units(), wl.tensor_path()
         scan_bytes, Tm, Bm, Hm = wl.scan_fwd_bytes(), wl.T, wl.B, wl.H
@@ -490,7 +491,7 @@ def run_device(args):
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
         "higher_is_better": True, "scaling": "strong" if args.config == "c5" else "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": config_dict(args.config, cfg, Bm, world, bool(args.T or args.B)),
+        "config": config_dict(args.config, cfg, Bm, world, bool(args.T or args.B or args.train)),
         "e2e": {"value": units / (e2e_ms * 1e-3), "unit": "seq-steps/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": h_bytes, "d2h_bytes_per_step": 4},
         "gpu_launches": int(round(launches_per_step * args.steps)),
@@ -515,7 +516,7 @@ def config_dict(name, cfg, B_per_gpu, world, override):
          "train_step": bool(cfg["train"]), "parallelism": f"batch-shard x{world}" if world > 1 else "1 GPU",
          "l2": "256 MiB buffer written between timed steps (outside the timed events)"}
     if override:
-        d["override"] = "T/B changed on the command line: a profiling case, not a result"
+        d["override"] = "T / B / train changed on the command line: a profiling case, not a result"
     return d
 
 
@@ -697,6 +698,8 @@ def main():
     ap.add_argument("--T", type=int, default=0, help="override the sequence length (profiling a smaller case; "
                     "the line then carries config.override and is not a benchmark result)")
     ap.add_argument("--B", type=int, default=0, help="override the batch, as --T")
+    ap.add_argument("--train", action="store_true", help="time forward + backward of a forward-only config "
+                    "(a profiling case like --T / --B)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-kinds", dest="kinds", action="store_false")
     ap.add_argument("--no-c5", dest="c5", action="store_false", help="skip the config-5 record of the default run")

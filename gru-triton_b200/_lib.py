@@ -75,6 +75,8 @@ SIGNATURES = {
     "b200gru_tc_gemm_splits": (_I, [_GP, _I]),
     "b200gru_split_bf16": (_I, [_P, _P, _Z, _Z, _I, _P, _I, _P]),
     "b200gru_split_f16": (_I, [_P, _P, _I, _I, _Z, _P, _P]),
+    "b200gru_column_sums_workspace_bytes": (_Z, [_Z, _I]),
+    "b200gru_column_sums": (_I, [_P, _Z, _I, _P, _P, _Z, _P]),
     "b200gru_calibration_workspace_bytes": (_Z, [_SP]),
     "b200gru_calibration_scan": (_I, [_SP, _P, _P, _P, _P, _I, ctypes.c_double, _P, _P, _I, _P, _P, _I, _P, _P, _Z, _P]),
     "b200gru_device_status": (_I, [_I]),
@@ -197,6 +199,25 @@ def quantize_rows_backward(W: torch.Tensor, dWq: torch.Tensor, bits: int = 8) ->
     if rc:
         _raise(rc, "quantize_rows_backward")
     return dW
+
+
+def column_sums(x: torch.Tensor) -> torch.Tensor:
+    """``x.reshape(-1, x.shape[-1]).sum(0)`` in a fixed summation order (CUDA float32, contiguous)."""
+    lib = load()
+    x = x.contiguous()
+    cols = x.shape[-1]
+    rows = x.numel() // cols if cols else 0
+    out = torch.empty((cols,), device=x.device, dtype=torch.float32)
+    if rows == 0 or cols == 0:
+        return out.zero_()
+    n = lib.b200gru_column_sums_workspace_bytes(rows, cols)
+    ws = torch.empty((max(n, 1),), device=x.device, dtype=torch.uint8)
+    with torch.cuda.device(x.device):
+        stream = torch.cuda.current_stream().cuda_stream
+        rc = lib.b200gru_column_sums(_ptr(x), rows, cols, _ptr(out), _ptr(ws), n, ctypes.c_void_p(stream))
+    if rc:
+        _raise(rc, "column_sums")
+    return out
 
 
 def scan_forward(kind: str, gi, h0, W, bh, h_in_quant: Quant, h_out_quant: Quant, *, nblocks: int = 1,

@@ -447,6 +447,16 @@ int b200gru_quantize_rows_backward(const float* W, const float* dWq, int rows, i
   return tc::launch_quantize_rows_backward(W, dWq, rows, cols, bits, dW, static_cast<cudaStream_t>(stream));
 }
 
+size_t b200gru_column_sums_workspace_bytes(size_t rows, int cols) {
+  return cols > 0 ? tc::column_sums_scratch_bytes(rows, cols) : 0;
+}
+
+int b200gru_column_sums(const float* src, size_t rows, int cols, float* dst, void* workspace, size_t workspace_bytes_,
+                        void* stream) {
+  if (cols <= 0 || workspace_bytes_ < tc::column_sums_scratch_bytes(rows, cols)) return B200GRU_WORKSPACE_TOO_SMALL;
+  return tc::launch_column_sums(src, rows, cols, dst, static_cast<float*>(workspace), static_cast<cudaStream_t>(stream));
+}
+
 int b200gru_dense_q8_forward(const float* gi, const float* h0, const float* Wq, const signed char* codes,
                              const float* scales, const float* bh_cat, int T, int B, int H,
                              const b200gru_quant* q_in, const b200gru_quant* q_out, float* out, float* save,

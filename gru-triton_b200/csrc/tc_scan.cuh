@@ -43,5 +43,9 @@ int launch_quantize_rows(const float* W, int rows, int cols, int bits, signed ch
 int launch_quantize_rows_backward(const float* W, const float* dWq, int rows, int cols, int bits, float* dW,
                                   cudaStream_t st);
 
+// dst[c] = sum over r of src[r][c] (fixed summation order); scratch of column_sums_scratch_bytes.
+size_t column_sums_scratch_bytes(size_t rows, int cols);
+int launch_column_sums(const float* src, size_t rows, int cols, float* dst, float* scratch, cudaStream_t st);
+
 }  // namespace tc
 }  // namespace b200gru

@@ -134,5 +134,103 @@ int launch_quantize_rows_backward(const float* W, const float* dWq, int rows, in
   return check_launch("quantize_rows_bwd_kernel");
 }
 
+// ---- column sums (bias gradient of the input projection) -----------------------------------------
+// partial[s][c] = sum of src[r][c] over the rows of slice s; a CTA takes 64 columns of one slice,
+// four row groups of 64 threads each, combined in a fixed order.  The slices are added in order
+// afterwards: no atomics.
+__global__ void __launch_bounds__(256)
+column_sums_kernel(const float* __restrict__ src, size_t rows, int cols, size_t rows_per_slice,
+                   float* __restrict__ partial) {
+  __shared__ float red[4][64];
+  const int c = blockIdx.x * 64 + (threadIdx.x & 63);
+  const int grp = threadIdx.x >> 6;
+  const size_t r0 = (size_t)blockIdx.y * rows_per_slice;
+  const size_t r1 = r0 + rows_per_slice < rows ? r0 + rows_per_slice : rows;
+  float s = 0.f;
+  if (c < cols)
+    for (size_t r = r0 + grp; r < r1; r += 4) s += __ldcs(src + r * cols + c);
+  red[grp][threadIdx.x & 63] = s;
+  __syncthreads();
+  if (grp == 0 && c < cols)
+    partial[(size_t)blockIdx.y * cols + c] = ((red[0][threadIdx.x] + red[1][threadIdx.x]) + red[2][threadIdx.x]) + red[3][threadIdx.x];
+}
+
+// The same for cols % 4 == 0: a CTA takes 256 columns (float4 per thread), four row groups, four
+// independent partial sums per thread so that the loads overlap.
+__global__ void __launch_bounds__(256)
+column_sums4_kernel(const float* __restrict__ src, size_t rows, int cols, size_t rows_per_slice,
+                    float* __restrict__ partial) {
+  __shared__ float4 red[4][64];
+  const int c = (blockIdx.x * 64 + (threadIdx.x & 63)) * 4;
+  const int grp = threadIdx.x >> 6;
+  const size_t r0 = (size_t)blockIdx.y * rows_per_slice;
+  const size_t r1 = r0 + rows_per_slice < rows ? r0 + rows_per_slice : rows;
+  float4 s[4];
+#pragma unroll
+  for (int u = 0; u < 4; ++u) s[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (c < cols) {
+    size_t r = r0 + grp;
+    for (; r + 12 < r1; r += 16) {
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const float4 v = __ldcs(reinterpret_cast<const float4*>(src + (r + 4 * u) * cols + c));
+        s[u].x += v.x; s[u].y += v.y; s[u].z += v.z; s[u].w += v.w;
+      }
+    }
+    for (; r < r1; r += 4) {
+      const float4 v = __ldcs(reinterpret_cast<const float4*>(src + r * cols + c));
+      s[0].x += v.x; s[0].y += v.y; s[0].z += v.z; s[0].w += v.w;
+    }
+  }
+  float4 t;
+  t.x = (s[0].x + s[1].x) + (s[2].x + s[3].x); t.y = (s[0].y + s[1].y) + (s[2].y + s[3].y);
+  t.z = (s[0].z + s[1].z) + (s[2].z + s[3].z); t.w = (s[0].w + s[1].w) + (s[2].w + s[3].w);
+  red[grp][threadIdx.x & 63] = t;
+  __syncthreads();
+  if (grp == 0 && c < cols) {
+    const int i = threadIdx.x;
+    float4 o;
+    o.x = ((red[0][i].x + red[1][i].x) + red[2][i].x) + red[3][i].x;
+    o.y = ((red[0][i].y + red[1][i].y) + red[2][i].y) + red[3][i].y;
+    o.z = ((red[0][i].z + red[1][i].z) + red[2][i].z) + red[3][i].z;
+    o.w = ((red[0][i].w + red[1][i].w) + red[2][i].w) + red[3][i].w;
+    *reinterpret_cast<float4*>(partial + (size_t)blockIdx.y * cols + c) = o;
+  }
+}
+
+static int column_slices(size_t rows, int cols) {
+  const int col_tiles = cdiv(cols, (cols % 4 == 0) ? 256 : 64);
+  int s = cdiv(2 * 148, col_tiles);
+  const size_t by_rows = (rows + 63) / 64;
+  if ((size_t)s > by_rows) s = (int)by_rows;
+  return s < 1 ? 1 : s;
+}
+
+size_t column_sums_scratch_bytes(size_t rows, int cols) {
+  return align_up((size_t)column_slices(rows, cols) * cols * sizeof(float), 256);
+}
+
+int launch_column_sums(const float* src, size_t rows, int cols, float* dst, float* scratch, cudaStream_t st) {
+  if (src == nullptr || dst == nullptr || scratch == nullptr || cols <= 0) return B200GRU_INVALID_ARGUMENT;
+  if (rows == 0) {
+    cudaMemsetAsync(dst, 0, (size_t)cols * sizeof(float), st);
+    return check_launch("column sums");
+  }
+  if (rows <= 16) {                               // a handful of partial results: one pass, fixed order
+    launch_reduce_partials(src, (int)rows, (size_t)cols, (size_t)cols, dst, st);
+    return check_launch("reduce_partials");
+  }
+  const int slices = column_slices(rows, cols);
+  const size_t rps = (rows + slices - 1) / slices;
+  const int used = (int)((rows + rps - 1) / rps);
+  if (cols % 4 == 0 && (reinterpret_cast<uintptr_t>(src) & 15u) == 0)
+    column_sums4_kernel<<<dim3(cdiv(cols, 256), used), 256, 0, st>>>(src, rows, cols, rps, scratch);
+  else
+    column_sums_kernel<<<dim3(cdiv(cols, 64), used), 256, 0, st>>>(src, rows, cols, rps, scratch);
+  note_launch();
+  launch_reduce_partials(scratch, used, (size_t)cols, (size_t)cols, dst, st);
+  return check_launch("column_sums_kernel");
+}
+
 }  // namespace tc
 }  // namespace b200gru

@@ -135,9 +135,7 @@ def gemm(A: torch.Tensor, B: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     if rc:
         _lib._raise(rc, "tc gemm")
     if splits > 1 and reduce_splits:
-        res = C[0]
-        for s in range(1, splits):
-            res = res + C[s]
+        res = _lib.column_sums(C.reshape(splits, M * N)).reshape(M, N)
         if out is not None:
             out.copy_(res)
             return out
@@ -220,9 +218,9 @@ class _LinearFunction(torch.autograd.Function):
                     gemm(dyp, Bx, b_mn=True, pairs=PAIRS_FULL, out=dx[r0:r1])
         dW = None
         if need_w:
-            dWq = dWq.sum(dim=0) if dWq.shape[0] > 1 else dWq[0]
+            dWq = _lib.column_sums(dWq.reshape(dWq.shape[0], -1)).reshape(N, I) if dWq.shape[0] > 1 else dWq[0]
             dW = _lib.quantize_rows_backward(W, dWq, ctx.weight_bits) if ctx.weight_bits <= 8 else dWq
-        db = dy.sum(dim=0) if need_b else None
+        db = _lib.column_sums(dy) if need_b else None
         return dx, dW, db, None
 
 

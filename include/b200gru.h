@@ -246,6 +246,13 @@ int b200gru_split_bf16(const float* src, void* dst, size_t n, size_t plane_strid
 int b200gru_split_f16(const float* src, void* dst, int rows, int cols, size_t plane_stride, float* inv_scale,
                       void* stream);
 
+/* dst[c] = sum over r of src[r][c] for a contiguous src[rows][cols], in a fixed summation order
+ * (two-level: row slices, then the slices in order).  The bias gradient of the input projection
+ * (autograd of F.linear at src/gru_qat/gru_layer.py:251-253) and the sum of split-K partials. */
+size_t b200gru_column_sums_workspace_bytes(size_t rows, int cols);
+int b200gru_column_sums(const float* src, size_t rows, int cols, float* dst, void* workspace,
+                        size_t workspace_bytes, void* stream);
+
 /* Diagonal backward for callers that cannot allocate device memory.  It has no counterpart in
  * the reference (whose wrappers always allocate their scratch with torch).  Same inputs, outputs
  * and results as b200gru_diagonal_backward, but no workspace argument: the partial sums go into a

@@ -133,6 +133,20 @@ def test_weight_prep_matches_autograd(rows, cols, bits):
     assert rel_err(dW.cpu(), Wl.grad) < 1e-5
 
 
+@pytest.mark.parametrize("rows,cols", [(1, 4), (77, 130), (2048, 1536), (40000, 96), (0, 8)])
+def test_column_sums_fixed_order(rows, cols):
+    """The bias-gradient reduction: equal to the float64 column sums to fp32 rounding, and bitwise
+    reproducible run to run."""
+    from gru_triton_b200 import _lib
+    torch.manual_seed(rows + cols)
+    x = torch.randn(rows, cols, device="cuda")
+    a = _lib.column_sums(x)
+    b = _lib.column_sums(x)
+    assert torch.equal(a, b)
+    ref = x.double().sum(0)
+    assert float((a.double() - ref).abs().max()) <= 1e-6 * max(1.0, float(x.abs().sum(0).max())) if rows else float(a.abs().max()) == 0.0
+
+
 @pytest.mark.parametrize("bits", [32, 8])
 @pytest.mark.parametrize("R,I,N", [(60, 64, 192), (1000, 520, 136), (40000, 128, 384)])
 def test_input_projection_forward_and_gradients(R, I, N, bits):
