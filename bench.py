@@ -7,8 +7,9 @@ Every workload is a ``GRULayer`` of this package built from BASELINE.json's desc
 through its public API: ``out, h_T = layer(x, h0)``, ``out.sum().backward()`` -- input projection
 on the tensor-core GEMM core, the CUDA scan, the weight gradients.  Default (every N): config 1,
 dense fp32 train step at T=64, B=32 per GPU, I=H=512; with N > 1 each rank runs its own batch
-(weak scaling) and the weight gradients are all-reduced once per step over NCCL through
-``data_parallel.GradBucket``.  Metric: sequence-steps/s = T*B*N / step time.  Each line also
+(weak scaling) and the weight gradients are all-reduced over NCCL through
+``data_parallel.OverlappedReducer`` (hidden-path bucket, then input-path bucket, each on a side
+stream as soon as the backward pass has produced it; ``--no-overlap``: one ``GradBucket`` at the end).  Metric: sequence-steps/s = T*B*N / step time.  Each line also
 carries a ``c5`` record: config 5 (dense int8 QAT, T=512, H=1024, B=4096 split over the N GPUs),
 three timed steps.
 
@@ -141,9 +142,9 @@ def build_layer(pkg, cfg, params, scale, use_triton):
 # ---------------------------------------------------------------------------
 
 class DeviceWorkload:
-    def __init__(self, name, cfg, rank, world, dev, pinned=True, graph=True):
+    def __init__(self, name, cfg, rank, world, dev, pinned=True, graph=True, overlap=True):
         import gru_triton_b200 as pkg
-        from gru_triton_b200.data_parallel import GradBucket
+        from gru_triton_b200.data_parallel import GradBucket, OverlappedReducer, hidden_then_input_buckets
         self.cfg, self.name, self.rank, self.world, self.dev = cfg, name, rank, world, dev
         self.T, self.H = cfg["T"], cfg["H"]
         self.B = cfg["B"] // world if name == "c5" else cfg["B"]
@@ -161,7 +162,15 @@ class DeviceWorkload:
         self.h0_host = h0.pin_memory() if pinned else None
         self.x, self.h0 = x.to(dev), h0.to(dev)
         del x, h0
-        self.bucket = GradBucket(list(self.layer.parameters())) if (world > 1 and cfg["train"]) else None
+        # N > 1: the gradients are summed over the ranks.  Default: two buckets (hidden path, input path),
+        # each all-reduced on a side stream as soon as the backward pass has produced it; --no-overlap:
+        # one bucket after the backward pass.
+        self.bucket = self.reducer = None
+        if world > 1 and cfg["train"]:
+            if overlap:
+                self.reducer = OverlappedReducer(hidden_then_input_buckets(self.layer))
+            else:
+                self.bucket = GradBucket(list(self.layer.parameters()))
         # up to about a thousand batch rows per GPU the step is bound by launch and per-step latency
         # (thousands of small dependent kernels): capture the whole step (forward, loss, backward) once
         self.graphed, self.collective_in_graph = None, False
@@ -169,7 +178,7 @@ class DeviceWorkload:
             from gru_triton_b200 import _lib
             from gru_triton_b200.graphed import GraphedStep
             n0 = _lib.launch_count()
-            if self.bucket is not None:
+            if self.bucket is not None or self.reducer is not None:
                 # the gradient all-reduce is a stream operation like the rest: capture it with the step
                 try:
                     self.collective_in_graph = True
@@ -178,6 +187,10 @@ class DeviceWorkload:
                     print(f"[bench] capturing the all-reduce failed ({type(e).__name__}: {e}); it runs eagerly",
                           file=sys.stderr)
                     self.collective_in_graph = False
+                    if self.reducer is not None:            # fall back to one bucket reduced after the replay
+                        self.reducer.remove()
+                        self.reducer = None
+                        self.bucket = GradBucket(list(self.layer.parameters()))
                     torch.cuda.synchronize()
                     n0 = _lib.launch_count()
             if self.graphed is None:
@@ -193,7 +206,9 @@ class DeviceWorkload:
         out, _ = self.layer(x, h0)
         loss = out.sum()
         loss.backward()
-        if self.bucket is not None and self.collective_in_graph:
+        if self.reducer is not None:
+            self.reducer.finish()                 # buckets already in flight on the side stream: join them
+        elif self.bucket is not None and self.collective_in_graph:
             self.bucket.all_reduce()              # one flat NCCL all-reduce, gradients written back
         return loss
 
@@ -332,10 +347,16 @@ def run_c5_record(dev, rank, world, flush, sync_all, max_over_ranks, peaks):
         rec["gpu_launches_per_step"] = (_lib.launch_count() - n0) / 4
         rec["ms_per_step"] = sum(ms) / len(ms)
         rec["seq_steps_per_s"] = cfg["T"] * cfg["B"] / (rec["ms_per_step"] * 1e-3)
-        if wl.bucket is not None:
-            ar = max_over_ranks(timed_loop(lambda: dist.all_reduce(wl.bucket.flat), 5, 2, flush, sync_all))
+        flats = ([wl.bucket.flat] if wl.bucket is not None else
+                 [b.flat for b in wl.reducer.buckets] if wl.reducer is not None else [])
+        if flats and all(f is not None for f in flats):
+            # the collective alone (both buckets back to back when the step overlaps them with the backward)
+            ar = max_over_ranks(timed_loop(lambda: [dist.all_reduce(f) for f in flats], 5, 2, flush, sync_all))
             rec["allreduce_ms"] = statistics.median(ar)
-            rec["allreduce_bytes"] = wl.bucket.flat.numel() * 4
+            rec["allreduce_bytes"] = sum(f.numel() for f in flats) * 4
+            rec["allreduce_overlapped_with_backward"] = wl.reducer is not None
+        if wl.reducer is not None:
+            wl.reducer.remove()
         wl.layer.zero_grad(set_to_none=True)
         torch.cuda.empty_cache()
         n1 = _lib.launch_count()
@@ -385,7 +406,7 @@ def run_device(args):
     if args.T or args.B or args.train:
         cfg = CONFIGS[args.config] = dict(cfg, T=args.T or cfg["T"], B=args.B or cfg["B"],
                                           train=cfg["train"] or args.train)
-    wl = DeviceWorkload(args.config, cfg, rank, world, dev, graph=args.graph)
+    wl = DeviceWorkload(args.config, cfg, rank, world, dev, graph=args.graph, overlap=args.overlap)
     graph_note = ("the step (forward, loss, backward) is captured once by gru_triton_b200.graphed.GraphedStep and "
                   "replayed; gpu_launches counts the kernels of the library inside one replay"
                   if wl.graphed is not None else "not used")
@@ -704,6 +725,8 @@ def main():
     ap.add_argument("--no-kinds", dest="kinds", action="store_false")
     ap.add_argument("--no-c5", dest="c5", action="store_false", help="skip the config-5 record of the default run")
     ap.add_argument("--no-graph", dest="graph", action="store_false", help="issue the kernels of a step one by one")
+    ap.add_argument("--no-overlap", dest="overlap", action="store_false",
+                    help="N > 1: one gradient bucket reduced after the backward pass instead of two overlapped ones")
     ap.add_argument("--graph-all", dest="graph", action="store_const", const="all",
                     help="capture the step in a CUDA graph whatever its size (default: small problems only)")
     args = ap.parse_args()

@@ -2,8 +2,11 @@
 
 Sequences are independent, so the scan itself needs no communication: each rank
 runs the same weights on its own slice of the batch.  The only collective of a
-training step is one all-reduce (sum) of the weight gradients, moved as a single
-flat fp32 bucket so that one NCCL launch covers {dWh, dWi, dbh, dbi}.
+training step is the all-reduce (sum) of the weight gradients, moved as flat fp32
+buckets: one bucket over {dWh, dWi, dbh, dbi} (``GradBucket``), or one bucket per group of
+parameters reduced on a side stream as soon as the backward pass has produced the group's
+gradients (``OverlappedReducer``: the hidden-path gradients travel while the input projection's
+backward still runs).
 """
 
 from __future__ import annotations
@@ -81,6 +84,75 @@ class GradBucket:
     def scatter(self) -> None:
         """Write the reduced bucket back into ``.grad`` (after an async reduce completes)."""
         self.unpack()
+
+
+class OverlappedReducer:
+    """All-reduce of several gradient buckets, each started the moment its last gradient exists.
+
+    ``buckets``: lists of parameters, in the order the backward pass completes them.  A
+    post-accumulate hook on every parameter counts a bucket's finished gradients; the last one
+    launches pack -> all-reduce -> unpack of that bucket on a side CUDA stream that first waits for
+    the producing stream, so the collective overlaps whatever the backward pass still has to do.
+    ``finish()`` reduces the buckets whose hooks never fired (parameters without a gradient), makes
+    the current stream wait for the side stream and re-arms the counters.  Everything is a stream
+    operation: a step using it can be captured in a CUDA graph (the side stream becomes a parallel
+    branch of the graph).  On CPU tensors (gloo) the reductions run in place, in the same order."""
+
+    def __init__(self, buckets: Sequence[Sequence[torch.Tensor]], group=None):
+        self.group = group
+        self.buckets = [GradBucket(list(ps)) for ps in buckets if len(ps)]
+        self._done = [0] * len(self.buckets)
+        self._launched = [False] * len(self.buckets)
+        self._stream: Optional[torch.cuda.Stream] = None
+        self._handles = []
+        for bi, b in enumerate(self.buckets):
+            for p in b.params:
+                self._handles.append(p.register_post_accumulate_grad_hook(self._make_hook(bi)))
+
+    def _make_hook(self, bi: int):
+        def hook(_param):
+            self._done[bi] += 1
+            if self._done[bi] == len(self.buckets[bi].params) and not self._launched[bi]:
+                self._launch(bi)
+        return hook
+
+    def _launch(self, bi: int) -> None:
+        self._launched[bi] = True
+        b = self.buckets[bi]
+        if b.params[0].is_cuda:
+            if self._stream is None:
+                self._stream = torch.cuda.Stream(device=b.params[0].device)
+            self._stream.wait_stream(torch.cuda.current_stream(b.params[0].device))
+            with torch.cuda.stream(self._stream):
+                b.all_reduce(group=self.group)
+        else:
+            b.all_reduce(group=self.group)
+
+    def finish(self) -> None:
+        """Call after ``backward()``: every bucket reduced, gradients visible to the current stream."""
+        for bi in range(len(self.buckets)):
+            if not self._launched[bi]:
+                self._launch(bi)
+        if self._stream is not None:
+            torch.cuda.current_stream(self.buckets[0].params[0].device).wait_stream(self._stream)
+        self._done = [0] * len(self.buckets)
+        self._launched = [False] * len(self.buckets)
+
+    def remove(self) -> None:
+        for h in self._handles:
+            h.remove()
+        self._handles = []
+
+
+def hidden_then_input_buckets(module: torch.nn.Module):
+    """Two parameter groups of a ``GRULayer`` in the order its backward pass finishes them: the
+    hidden path (scan backward: W_h*, b_h*, structured hidden factors), then everything else (the
+    input projection's weights and biases)."""
+    hidden, rest = [], []
+    for name, p in module.named_parameters():
+        leaf = name.rsplit(".", 1)[-1]
+        (hidden if ("W_h" in name or "b_h" in leaf or "struct_Wh" in name) else rest).append(p)
+    return [hidden, rest]
 
 
 def all_reduce_gradients(params: Iterable[torch.Tensor], group=None) -> None:

@@ -35,7 +35,8 @@ def _worker(rank, world, port, out_path):
     sys.path.insert(0, REPO)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
-    from gru_triton_b200.data_parallel import GradBucket, shard_batch
+    from gru_triton_b200.data_parallel import (GradBucket, OverlappedReducer, hidden_then_input_buckets,
+                                               shard_batch)
     layer = _make_layer()
     gen = torch.Generator().manual_seed(0)
     x = torch.randn(6, 5, 12, generator=gen)            # B = 5: uneven shards (3 + 2)
@@ -44,8 +45,21 @@ def _worker(rank, world, port, out_path):
     out.sum().backward()
     params = [p for p in layer.parameters()]
     GradBucket(params).all_reduce()
+    one_bucket = [p.grad.clone() for p in params]
+    # the same step with two buckets, each reduced from the hook of its last gradient
+    buckets = hidden_then_input_buckets(layer)
+    assert len(buckets[0]) and len(buckets[1]) and len(buckets[0]) + len(buckets[1]) == len(params)
+    red = OverlappedReducer(buckets)
+    for _ in range(2):                                  # twice: the counters re-arm
+        layer.zero_grad(set_to_none=True)
+        out, _ = layer(shard_batch(x, rank, world, 1), shard_batch(h0, rank, world, 0))
+        out.sum().backward()
+        red.finish()
+        for a, p in zip(one_bucket, params):
+            assert torch.equal(a, p.grad)
+    red.remove()
     if rank == 0:
-        torch.save([p.grad.clone() for p in params], out_path)
+        torch.save(one_bucket, out_path)
     dist.barrier()
     dist.destroy_process_group()
 
