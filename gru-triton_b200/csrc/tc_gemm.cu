@@ -87,6 +87,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const int nchunks = (nkb + p.chunk_kb - 1) / p.chunk_kb;
   const int stage_bytes = p.a_planes * A_PLANE_BYTES + p.b_planes * B_PLANE_BYTES;
   int* status = &g_tc_status;
+  pdl_launch_dependents();
 
   if (threadIdx.x == 0) {
     dead = (*reinterpret_cast<volatile int*>(status) != 0) ? 1 : 0;
@@ -108,6 +109,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   tc_fence_after();
   const uint32_t tmem_acc = tmem_base_slot;
   volatile int* deadp = &dead;
+  pdl_wait();          // the operands (and, when accumulating, C) may come from the previous kernel of the stream
 
   if (warp == 0) {
     if (lane == 0 && !*deadp) {
@@ -389,7 +391,7 @@ int launch_variant(const TcGemm& g, const CUtensorMap& ta, const CUtensorMap& tb
   auto kernel = tc_gemm_kernel<I8, A_MN, B_MN, BN>;
   int rc = prepare(reinterpret_cast<const void*>(kernel));
   if (rc) return rc;
-  kernel<<<grid, GEMM_THREADS, smem, st>>>(ta, tb, p);
+  launch_pdl(kernel, grid, dim3(GEMM_THREADS), (size_t)smem, st, ta, tb, p);
   note_launch();
   return check_launch("tc_gemm_kernel");
 }

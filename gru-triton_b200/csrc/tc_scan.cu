@@ -27,6 +27,7 @@
 
 #include "block_scan.cuh"
 #include "butterfly_scan.cuh"
+#include "tc_common.cuh"
 #include "tc_gemm.cuh"
 #include "tc_scan.cuh"
 #include "tc_step.cuh"
@@ -185,6 +186,13 @@ gate_bwd_kernel(const BwdStepArgs a) {
   const size_t o = (size_t)b * H + u;
   const size_t step = (size_t)B * H, comp = (size_t)a.T * step, so = (size_t)t * step + o;
 
+  // inputs no kernel of the backward chain writes go in flight before the wait for the previous one
+  pdl_launch_dependents();
+  const float4 d4 = ld4s(a.dout + so);
+  const float4 r4 = ld4s(a.S + so), z4 = ld4s(a.S + comp + so), n4 = ld4s(a.S + 2 * comp + so), g4 = ld4s(a.S + 3 * comp + so);
+  const float4 h4 = ld4(a.h_prev + o);
+  pdl_wait();
+
   float carry[4] = {0.f, 0.f, 0.f, 0.f};
   if (a.via != nullptr) {
     float4 s = ld4s(a.via + o);
@@ -201,9 +209,6 @@ gate_bwd_kernel(const BwdStepArgs a) {
       carry[e] = dv[e] + sv[e] * mk;
     }
   }
-  const float4 d4 = ld4s(a.dout + so);
-  const float4 r4 = ld4s(a.S + so), z4 = ld4s(a.S + comp + so), n4 = ld4s(a.S + 2 * comp + so), g4 = ld4s(a.S + 3 * comp + so);
-  const float4 h4 = ld4(a.h_prev + o);
   const float dv[4] = {d4.x, d4.y, d4.z, d4.w}, rv[4] = {r4.x, r4.y, r4.z, r4.w}, zv[4] = {z4.x, z4.y, z4.z, z4.w};
   const float nv[4] = {n4.x, n4.y, n4.z, n4.w}, gv[4] = {g4.x, g4.y, g4.z, g4.w}, hv[4] = {h4.x, h4.y, h4.z, h4.w};
   float dgr[4], dgz[4], dgn[4], dghn[4], dir[4];
@@ -524,7 +529,7 @@ int launch_tc_dense_backward(const float* h0, const TcWeights& w, const float* o
     a.via = (t == T - 1) ? nullptr : via;
     a.h_t = out + (size_t)t * B * H;
     a.h_prev = (t == 0) ? h0 : out + (size_t)(t - 1) * B * H;
-    gate_bwd_kernel<<<cdiv(n4, 256), 256, 0, st>>>(a);
+    launch_pdl(gate_bwd_kernel, dim3(cdiv(n4, 256)), dim3(256), 0, st, a);
     note_launch();
     gv.A = dgh_op + (size_t)slot * B * 3 * H;
     rc = launch_tc_gemm(gv, st);

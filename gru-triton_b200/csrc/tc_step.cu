@@ -81,6 +81,7 @@ tc_fwd_step_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
   const int u0 = blockIdx.x * FS_UNITS, m0 = blockIdx.y * FS_BM;
   const int H = a.H;
   int* status = &g_tc_step_status;
+  pdl_launch_dependents();
 
   if (threadIdx.x == 0) {
     dead = (*reinterpret_cast<volatile int*>(status) != 0) ? 1 : 0;
@@ -110,13 +111,27 @@ tc_fwd_step_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
 
   if (warp == 0) {
     if (lane == 0 && !*deadp) {
-      // the input tiles of the gate math: gi[t] (three gates) and h_{t-1}
+      // Nothing the previous step's kernel writes: gi[t] and the weight slabs of the first ring
+      // round go in flight before the wait for that kernel.
       const uint32_t iob = smem_u32(&bar_io);
       mbar_expect_tx(iob, 4 * FS_TILE);
 #pragma unroll
       for (int g = 0; g < 3; ++g) tma_load_3d(smem_u32(io + g * FS_TILE), &tmGi, g * H + u0, m0, a.t, iob);
+      const int first = a.nkb < FS_STAGES ? a.nkb : FS_STAGES;
+      for (int i = 0; i < first; ++i) {
+        const uint32_t full = smem_u32(&bar_full[i]);
+        mbar_expect_tx(full, FS_STAGE);
+        unsigned char* st = smem + (size_t)i * FS_STAGE;
+#pragma unroll
+        for (int g = 0; g < 3; ++g)
+          tma_load_3d(smem_u32(st + FS_A_BYTES + g * FS_B_SLAB), &tmB, i * FS_KB, g * H + u0, 0, full);
+      }
+      pdl_wait();
+      // h_{t-1} and its integer codes come from the previous step
       tma_load_3d(smem_u32(io + 3 * FS_TILE), &tmPrev, u0, m0, a.t > 0 ? a.t - 1 : 0, iob);
-      for (int i = 0; i < a.nkb; ++i) {
+      for (int i = 0; i < first; ++i)
+        tma_load_3d(smem_u32(smem + (size_t)i * FS_STAGE), &tmA, i * FS_KB, m0, 0, smem_u32(&bar_full[i]));
+      for (int i = first; i < a.nkb; ++i) {
         const int s = i % FS_STAGES, round = i / FS_STAGES;
         if (round > 0 && !mbar_wait(smem_u32(&bar_empty[s]), (round - 1) & 1, deadp, status)) break;
         const uint32_t full = smem_u32(&bar_full[s]);
@@ -127,8 +142,11 @@ tc_fwd_step_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
           tma_load_3d(smem_u32(st + FS_A_BYTES + g * FS_B_SLAB), &tmB, i * FS_KB, g * H + u0, 0, full);
         tma_load_3d(smem_u32(st), &tmA, i * FS_KB, m0, 0, full);
       }
+    } else {
+      pdl_wait();
     }
   } else if (warp == 1) {
+    pdl_wait();
     if (lane == 0 && !*deadp) {
       bool alive = true;
       for (int i = 0; i < a.nkb && alive; ++i) {
@@ -146,6 +164,7 @@ tc_fwd_step_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
       if (alive) umma_commit(smem_u32(&bar_acc));
     }
   } else {
+    pdl_wait();
     // ---- epilogue: thread = (batch row, 16 units)
     const int q = warp & 3, half = (warp - 2) >> 2;
     const int r = q * 32 + lane;                    // row inside the tile
@@ -290,7 +309,8 @@ int FusedFwd::step(int t, int src, const float* col_scale, const float* bh, sign
   a.col_scale = col_scale; a.bh = bh; a.codes_next = codes_next; a.t = t; a.T = T; a.B = B; a.H = H; a.nkb = nkb;
   a.has_save = has_save ? 1 : 0; a.alpha = alpha; a.qin = qin; a.qout = qout;
   const dim3 grid(H / FS_UNITS, cdiv(B, FS_BM));
-  tc_fwd_step_kernel<<<grid, FS_THREADS, FS_SMEM, st>>>(mapH[src], mapW, mapGi, t == 0 ? mapH0 : mapOut, mapOut, mapSave, a);
+  launch_pdl(tc_fwd_step_kernel, grid, dim3(FS_THREADS), (size_t)FS_SMEM, st, mapH[src], mapW, mapGi,
+             t == 0 ? mapH0 : mapOut, mapOut, mapSave, a);
   note_launch();
   return B200GRU_OK;
 }
