@@ -441,8 +441,14 @@ def run_device(args):
 
     # ---- (2) end to end: pinned host -> device copy in, loss (or last h) read back -----
     def e2e_step():
-        x = wl.x_host.to(dev, non_blocking=True)
-        h0 = wl.h0_host.to(dev, non_blocking=True)
+        if wl.graphed is not None:
+            # straight into the captured step's input buffers: no staging tensor, no device-to-device copy
+            x, h0 = wl.graphed.static_inputs
+            x.copy_(wl.x_host, non_blocking=True)
+            h0.copy_(wl.h0_host, non_blocking=True)
+        else:
+            x = wl.x_host.to(dev, non_blocking=True)
+            h0 = wl.h0_host.to(dev, non_blocking=True)
         r = wl.step(x, h0)
         return (r if r.dim() == 0 else r[-1, 0, 0]).item()
 

@@ -49,6 +49,7 @@ struct GemmParams {
   int chunk_kb;                              // k-blocks summed in tensor memory before a drain
   int accumulate;
   unsigned ab_format;                        // kind::f16 operand format: 0 = fp16, 1 = bf16
+  int staged_store;                          // the result tile leaves through the operand ring, whole rows per warp
   float alpha;
   const float* row_scale;
   const float* col_scale;
@@ -88,6 +89,13 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const int stage_bytes = p.a_planes * A_PLANE_BYTES + p.b_planes * B_PLANE_BYTES;
   int* status = &g_tc_status;
   pdl_launch_dependents();
+#ifdef B200GRU_PHASE_TIMING
+  const long long gm_t0 = clock64();
+#define GM_MARK(cond, slot) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (cond)) \
+    atomicAdd(&g_phase_cycles[slot], (unsigned long long)(clock64() - gm_t0)); } while (0)
+#else
+#define GM_MARK(cond, slot)
+#endif
 
   if (threadIdx.x == 0) {
     dead = (*reinterpret_cast<volatile int*>(status) != 0) ? 1 : 0;
@@ -110,6 +118,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const uint32_t tmem_acc = tmem_base_slot;
   volatile int* deadp = &dead;
   pdl_wait();          // the operands (and, when accumulating, C) may come from the previous kernel of the stream
+  GM_MARK(threadIdx.x == 0, 0);      // prologue done
 
   if (warp == 0) {
     if (lane == 0 && !*deadp) {
@@ -161,6 +170,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           const int s = i % p.stages, round = i / p.stages;
           if (!mbar_wait(smem_u32(&bar_full[s]), round & 1, deadp, status)) { alive = false; break; }
           tc_fence_after();
+          GM_MARK(i == 0, 1);          // first stage landed
+          GM_MARK(i == nkb - 1, 2);    // last stage landed
           const uint32_t sa = smem_u32(smem + (size_t)s * stage_bytes);
           const uint32_t sb = sa + p.a_planes * A_PLANE_BYTES;
           for (int q = 0; q < p.npairs; ++q) {
@@ -212,7 +223,73 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&bar_acc_empty[buf]));
     }
-    if (m < p.M) {
+    GM_MARK(threadIdx.x == 64, 3);    // all chunks drained
+    if (p.staged_store) {
+      // Coalesced stores.  A thread holds one row of the tile, so its own stores would scatter 16
+      // bytes into each of 32 rows per instruction (a quarter of a cache line each: the LSU queues
+      // them for longer than the whole main loop of a short product).  The operand ring is free
+      // once the last chunk has been committed: the tile goes through it, row-major with a
+      // 4-float pad, and every warp then writes whole rows, 512 contiguous bytes per instruction.
+      constexpr int LDS = BN + 4;
+      float* tile = reinterpret_cast<float*>(smem);
+      const int r = q * 32 + lane;
+      if (ok) {
+#pragma unroll
+        for (int j = 0; j < NC; j += 4)
+          *reinterpret_cast<float4*>(tile + r * LDS + cbase + j) =
+              make_float4((float)acc[j], (float)acc[j + 1], (float)acc[j + 2], (float)acc[j + 3]);
+      }
+      asm volatile("bar.sync 1, %0;" ::"n"(32 * EPI_WARPS) : "memory");
+      const int ew = warp - 2;                                   // 0..7
+      constexpr int NH = BN >= 128 ? BN / 128 : 1;               // 128-column spans of the tile
+      float cs[NH][4], bs[NH][4];
+#pragma unroll
+      for (int h = 0; h < NH; ++h) {
+        const int n = n0 + h * 128 + lane * 4;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          cs[h][e] = (p.col_scale != nullptr && n + e < p.N) ? __ldg(p.col_scale + n + e) : 1.0f;
+          bs[h][e] = (p.bias != nullptr && n + e < p.N) ? __ldg(p.bias + n + e) : 0.0f;
+        }
+      }
+      if (ok) {
+        constexpr int RPW = BM / EPI_WARPS;                        // rows per warp
+        float rsv[RPW];
+#pragma unroll
+        for (int i = 0; i < RPW; ++i) {                            // all row scales in flight at once
+          const int mm = m0 + ew + i * EPI_WARPS;
+          rsv[i] = p.alpha * ((p.row_scale != nullptr && mm < p.M) ? __ldg(p.row_scale + mm) : 1.0f);
+        }
+#pragma unroll 4
+        for (int i = 0; i < RPW; ++i) {
+          const int rr = ew + i * EPI_WARPS;
+          const int mm = m0 + rr;
+          if (mm < p.M) {
+            const float rs = rsv[i];
+            float* crow = p.C + (size_t)blockIdx.z * p.split_stride + (size_t)mm * p.ldc;
+#pragma unroll
+            for (int h = 0; h < NH; ++h) {
+              const int c = h * 128 + lane * 4;
+              const int n = n0 + c;
+              if (c < BN && n < p.N) {
+                const float4 v = *reinterpret_cast<const float4*>(tile + rr * LDS + c);
+                float o[4] = {v.x * rs, v.y * rs, v.z * rs, v.w * rs};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  if (p.col_scale != nullptr) o[e] = o[e] * cs[h][e];
+                  if (p.bias != nullptr) o[e] = o[e] + bs[h][e];
+                }
+                if (p.accumulate) {
+                  const float4 old = *reinterpret_cast<const float4*>(crow + n);
+                  o[0] += old.x; o[1] += old.y; o[2] += old.z; o[3] += old.w;
+                }
+                *reinterpret_cast<float4*>(crow + n) = make_float4(o[0], o[1], o[2], o[3]);
+              }
+            }
+          }
+        }
+      }
+    } else if (m < p.M) {
       const float rs = p.alpha * (p.row_scale != nullptr ? p.row_scale[m] : 1.0f);
       float* crow = p.C + (size_t)blockIdx.z * p.split_stride + (size_t)m * p.ldc;
 #pragma unroll
@@ -243,8 +320,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     while (clock64() - start < (1ll << 18)) {
     }
   }
+  GM_MARK(threadIdx.x == 64, 4);      // stores issued
   tc_fence_before();
   __syncthreads();
+  GM_MARK(threadIdx.x == 0, 5);       // all warps done
   if (warp == 1) {
     __syncwarp();
     tc_fence_after();
@@ -495,6 +574,7 @@ int launch_tc_gemm(const TcGemm& g, cudaStream_t st) {
   else p.chunk_kb = (32 / (4 * g.npairs)) > 0 ? 32 / (4 * g.npairs) : 1;   // at most 32 accumulation steps per chunk
   p.accumulate = g.accumulate;
   p.ab_format = (g.kind == TC_KIND_F16) ? 0u : 1u;
+  p.staged_store = ((size_t)p.stages * stage >= (size_t)BM * (bn + 4) * sizeof(float)) ? 1 : 0;
   p.alpha = g.alpha; p.row_scale = g.row_scale; p.col_scale = g.col_scale; p.bias = g.bias;
   p.C = g.C; p.ldc = g.ldc; p.split_stride = g.split_stride;
 
@@ -564,3 +644,5 @@ int launch_split_rows_f16(const float* src, void* dst, int rows, int cols, size_
 
 }  // namespace tc
 }  // namespace b200gru
+
+B200GRU_DEFINE_PHASE_READER(b200gru_debug_phase_cycles_gemm)
