@@ -624,8 +624,10 @@ static TcGemm wgrad_gemm(int T, int B, int H, bool h_codes) {
       const int j = s2 - i;
       if (j < g.b_planes) { g.pa[g.npairs] = i; g.pb[g.npairs] = j; ++g.npairs; }
     }
-  g.tile_n = 128;
-  const int tiles = cdiv(g.M, 128) * cdiv(g.N, 128);
+  // wide tiles: one k-block of the two A planes then feeds 256 columns (measured at c1: 31 K cycles
+  // per CTA with 256-wide tiles and 4 K slices against 42 K with 128-wide ones)
+  g.tile_n = g.N >= 256 ? 256 : 128;
+  const int tiles = cdiv(g.M, 128) * cdiv(g.N, g.tile_n);
   // enough K slices to fill the SMs, at least 8 k-blocks each
   int want = tiles >= 148 ? 1 : cdiv(148, tiles);
   const int kb = cdiv(g.K, tc_gemm_kblock(g));
