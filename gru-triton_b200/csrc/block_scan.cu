@@ -280,14 +280,23 @@ block_fwd_kernel(const BlockScanArgs a) {
     kstride = a.RS;
     gstride = Hc4;
     const float* Wn = a.W + (size_t)n * a.w_block_stride;
-    const int total = 3 * Hc4 * Hb;
+    // Transposing fill: a thread takes one k and four adjacent units, so the four global loads are
+    // coalesced across the warp (consecutive k) and the one float4 store is conflict-free (row
+    // stride = 4 mod 8 floats); several items in flight per thread hide the load latency.
+    const int nq = 3 * (Hc4 >> 2);
+    const int total = nq * Hb;
+#pragma unroll 4
     for (int idx = tid; idx < total; idx += NT) {
       const int k = idx % Hb;
-      const int gj = idx / Hb;
-      const int g = gj / Hc4, j = gj - g * Hc4;
-      float v = 0.f;
-      if (j < nown) v = Wn[(size_t)g * a.w_gate_stride + (size_t)(u0 + j) * Hb + k];
-      wsm[k * kstride + g * Hc4 + j] = v;
+      const int q = idx / Hb;
+      const int g = q / (Hc4 >> 2), j0 = (q - g * (Hc4 >> 2)) << 2;
+      const float* src = Wn + (size_t)g * a.w_gate_stride + (size_t)(u0 + j0) * Hb + k;
+      float4 v;
+      v.x = (j0 + 0 < nown) ? __ldg(src) : 0.f;
+      v.y = (j0 + 1 < nown) ? __ldg(src + Hb) : 0.f;
+      v.z = (j0 + 2 < nown) ? __ldg(src + 2 * Hb) : 0.f;
+      v.w = (j0 + 3 < nown) ? __ldg(src + 3 * Hb) : 0.f;
+      *reinterpret_cast<float4*>(wsm + k * kstride + g * Hc4 + j0) = v;
     }
     wbase = wsm;
   } else {
@@ -514,13 +523,30 @@ block_bwd_kernel(const BlockScanArgs a) {
     rstride = Hb4;
     const float* Wn = a.W + (size_t)n * a.w_block_stride;
     const int total = 3 * Hc4 * Hb4;
-    for (int idx = tid; idx < total; idx += NT) {
-      const int k = idx % Hb4;
-      const int gj = idx / Hb4;
-      const int g = gj / Hc4, j = gj - g * Hc4;
-      float v = 0.f;
-      if (j < nown && k < Hb) v = Wn[(size_t)g * a.w_gate_stride + (size_t)(u0 + j) * Hb + k];
-      wsm[idx] = v;
+    const bool vec4 = (Hb % 4 == 0) && (a.w_gate_stride % 4 == 0) && (a.w_block_stride % 4 == 0) &&
+                      ((reinterpret_cast<uintptr_t>(a.W) & 15u) == 0);
+    if (vec4) {
+      // rows are copied as they lie (k contiguous on both sides): float4s, several in flight per thread
+      const int kq = Hb4 >> 2;
+#pragma unroll 4
+      for (int idx = tid; idx < 3 * Hc4 * kq; idx += NT) {
+        const int k4 = idx % kq;
+        const int gj = idx / kq;
+        const int g = gj / Hc4, j = gj - g * Hc4;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (j < nown && 4 * k4 < Hb)                  // the padding beyond Hb stays zero
+          v = __ldg(reinterpret_cast<const float4*>(Wn + (size_t)g * a.w_gate_stride + (size_t)(u0 + j) * Hb) + k4);
+        reinterpret_cast<float4*>(wsm)[idx] = v;
+      }
+    } else {
+      for (int idx = tid; idx < total; idx += NT) {
+        const int k = idx % Hb4;
+        const int gj = idx / Hb4;
+        const int g = gj / Hc4, j = gj - g * Hc4;
+        float v = 0.f;
+        if (j < nown && k < Hb) v = Wn[(size_t)g * a.w_gate_stride + (size_t)(u0 + j) * Hb + k];
+        wsm[idx] = v;
+      }
     }
     wbase = wsm;
   } else {
