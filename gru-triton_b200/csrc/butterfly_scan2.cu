@@ -15,6 +15,8 @@
 // Every wait is a bounded poll of an mbarrier; a wait that gives up sets a device flag and the
 // kernel runs to its end (results invalid, flag visible through b200gru_device_status).
 
+#include <type_traits>
+
 #include "butterfly_scan.cuh"
 
 namespace b200gru {
@@ -52,6 +54,28 @@ __device__ __forceinline__ void mbar_wait(unsigned bar, unsigned parity, bool& d
 }
 
 __device__ __forceinline__ int sw(int i) { return i + ((i >> 6) << 3); }
+
+// V (2 or 4) adjacent floats as one vector access; STREAM: evict-first store
+template <int V>
+__device__ __forceinline__ void ldv(const float* p, float (&x)[V]) {
+  if constexpr (V == 4) {
+    const float4 v = *reinterpret_cast<const float4*>(p);
+    x[0] = v.x; x[1] = v.y; x[2] = v.z; x[3] = v.w;
+  } else {
+    const float2 v = *reinterpret_cast<const float2*>(p);
+    x[0] = v.x; x[1] = v.y;
+  }
+}
+template <int V, bool STREAM>
+__device__ __forceinline__ void stv(float* p, const float (&x)[V]) {
+  if constexpr (V == 4) {
+    if (STREAM) __stcs(reinterpret_cast<float4*>(p), make_float4(x[0], x[1], x[2], x[3]));
+    else *reinterpret_cast<float4*>(p) = make_float4(x[0], x[1], x[2], x[3]);
+  } else {
+    if (STREAM) __stcs(reinterpret_cast<float2*>(p), make_float2(x[0], x[1]));
+    else *reinterpret_cast<float2*>(p) = make_float2(x[0], x[1]);
+  }
+}
 
 template <int R, int P, int BT, bool TRANSPOSE>
 __device__ __forceinline__ void stage_regs(float (&v)[BT][1 << R], const float4 (&tw)[(1 << R) / 2]) {
@@ -429,44 +453,51 @@ bfly_fwd2_kernel(const BflyArgs a) {
     mbar_wait(gbar, (unsigned)t & 1u, dead);
     PHASE_MARK(8);
 
-    for (int idx = tid; idx < nrows * H4g; idx += NT) {
-      const int b = idx / H4g, i = (idx - b * H4g) << 2;
-      const int row = row0 + b;
-      const int ps = b * RSZ + sw(i);
-      const float4 s0 = *reinterpret_cast<const float4*>(st + 0 * BT * RSZ + ps);
-      const float4 s1 = *reinterpret_cast<const float4*>(st + 1 * BT * RSZ + ps);
-      const float4 s2 = *reinterpret_cast<const float4*>(st + 2 * BT * RSZ + ps);
-      const float4 b0 = *reinterpret_cast<const float4*>(bias + i);
-      const float4 b1 = *reinterpret_cast<const float4*>(bias + H + i);
-      const float4 b2 = *reinterpret_cast<const float4*>(bias + 2 * H + i);
-      const float4 g0 = *reinterpret_cast<const float4*>(gbuf + (0 * BT + b) * H + i);
-      const float4 g1 = *reinterpret_cast<const float4*>(gbuf + (1 * BT + b) * H + i);
-      const float4 g2 = *reinterpret_cast<const float4*>(gbuf + (2 * BT + b) * H + i);
-      const float4 hp = *reinterpret_cast<const float4*>(hraw + b * H + i);
-      const float sr[4] = {s0.x + b0.x, s0.y + b0.y, s0.z + b0.z, s0.w + b0.w};
-      const float sz[4] = {s1.x + b1.x, s1.y + b1.y, s1.z + b1.z, s1.w + b1.w};
-      const float sn[4] = {s2.x + b2.x, s2.y + b2.y, s2.z + b2.z, s2.w + b2.w};
-      const float gr[4] = {g0.x, g0.y, g0.z, g0.w}, gz[4] = {g1.x, g1.y, g1.z, g1.w}, gn[4] = {g2.x, g2.y, g2.z, g2.w};
-      const float hv[4] = {hp.x, hp.y, hp.z, hp.w};
-      float hn[4], hqv[4], rr[4], zz[4], nn[4];
+    // gate phase: an item is V adjacent units of one row; narrower items when the row would otherwise
+    // leave most of the threads idle (the phase is a chain of transcendental latencies per element)
+    auto gate_phase = [&](auto vtag) {
+      constexpr int V = decltype(vtag)::value;
+      const int HV = H / V;
+      for (int idx = tid; idx < nrows * HV; idx += NT) {
+        const int b = idx / HV, i = (idx - b * HV) * V;
+        const int row = row0 + b;
+        const int ps = b * RSZ + sw(i);
+        float sr[V], sz[V], sn[V], gr[V], gz[V], gn[V], hv[V], bb[V];
+        ldv<V>(st + 0 * BT * RSZ + ps, sr); ldv<V>(bias + i, bb);
 #pragma unroll
-      for (int v = 0; v < 4; ++v) {
-        const GateOut go = gru_gates(gr[v], gz[v], gn[v], sr[v], sz[v], sn[v], hv[v]);
-        hn[v] = a.qout.enabled ? fake_quant<true>(go.h_raw, a.qout) : go.h_raw;
-        hqv[v] = a.qin.enabled ? fake_quant<true>(hn[v], a.qin) : hn[v];
-        rr[v] = go.r; zz[v] = go.z; nn[v] = go.n;
+        for (int v = 0; v < V; ++v) sr[v] += bb[v];
+        ldv<V>(st + 1 * BT * RSZ + ps, sz); ldv<V>(bias + H + i, bb);
+#pragma unroll
+        for (int v = 0; v < V; ++v) sz[v] += bb[v];
+        ldv<V>(st + 2 * BT * RSZ + ps, sn); ldv<V>(bias + 2 * H + i, bb);
+#pragma unroll
+        for (int v = 0; v < V; ++v) sn[v] += bb[v];
+        ldv<V>(gbuf + (0 * BT + b) * H + i, gr);
+        ldv<V>(gbuf + (1 * BT + b) * H + i, gz);
+        ldv<V>(gbuf + (2 * BT + b) * H + i, gn);
+        ldv<V>(hraw + b * H + i, hv);
+        float hn[V], hqv[V], rr[V], zz[V], nn[V];
+#pragma unroll
+        for (int v = 0; v < V; ++v) {
+          const GateOut go = gru_gates(gr[v], gz[v], gn[v], sr[v], sz[v], sn[v], hv[v]);
+          hn[v] = a.qout.enabled ? fake_quant<true>(go.h_raw, a.qout) : go.h_raw;
+          hqv[v] = a.qin.enabled ? fake_quant<true>(hn[v], a.qin) : hn[v];
+          rr[v] = go.r; zz[v] = go.z; nn[v] = go.n;
+        }
+        const size_t o = (size_t)t * out_step + (size_t)row * H + i;
+        if (a.out != nullptr) stv<V, false>(a.out + o, hn);
+        if (a.save != nullptr) {
+          stv<V, true>(a.save + o, rr);
+          stv<V, true>(a.save + comp + o, zz);
+          stv<V, true>(a.save + 2 * comp + o, nn);
+          stv<V, true>(a.save + 3 * comp + o, sn);
+        }
+        stv<V, false>(hraw + b * H + i, hn);
+        stv<V, false>(hq + ps, hqv);
       }
-      const size_t o = (size_t)t * out_step + (size_t)row * H + i;
-      if (a.out != nullptr) *reinterpret_cast<float4*>(a.out + o) = make_float4(hn[0], hn[1], hn[2], hn[3]);
-      if (a.save != nullptr) {
-        __stcs(reinterpret_cast<float4*>(a.save + o), make_float4(rr[0], rr[1], rr[2], rr[3]));
-        __stcs(reinterpret_cast<float4*>(a.save + comp + o), make_float4(zz[0], zz[1], zz[2], zz[3]));
-        __stcs(reinterpret_cast<float4*>(a.save + 2 * comp + o), make_float4(nn[0], nn[1], nn[2], nn[3]));
-        __stcs(reinterpret_cast<float4*>(a.save + 3 * comp + o), make_float4(sn[0], sn[1], sn[2], sn[3]));
-      }
-      *reinterpret_cast<float4*>(hraw + b * H + i) = make_float4(hn[0], hn[1], hn[2], hn[3]);
-      *reinterpret_cast<float4*>(hq + ps) = make_float4(hqv[0], hqv[1], hqv[2], hqv[3]);
-    }
+    };
+    if (2 * nrows * H4g <= NT) gate_phase(std::integral_constant<int, 2>{});
+    else gate_phase(std::integral_constant<int, 4>{});
     PHASE_MARK(9);
     __syncthreads();
     PHASE_MARK(10);
