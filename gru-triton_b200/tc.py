@@ -198,7 +198,11 @@ class _LinearFunction(torch.autograd.Function):
             tiles = -(-N // 128) * -(-I // 256)
             want = 1 if tiles >= 120 else -(-(280 if chunk_rows >= 16384 else 140) // tiles)
             splits = gemm_splits(N, I, chunk_rows, max(1, min(want, chunk_rows // 512)))
-            dWq = torch.zeros((splits, N, I), device=x.device, dtype=torch.float32)
+            # the first chunk writes the K-slice accumulators, later chunks add to them; a short first chunk
+            # may use fewer slices than the rest, then the buffer starts from zero
+            first_splits = gemm_splits(N, I, min(R, ROW_CHUNK), splits)
+            alloc = torch.empty if first_splits == splits else torch.zeros
+            dWq = alloc((splits, N, I), device=x.device, dtype=torch.float32)
         for r0 in range(0, R, ROW_CHUNK):
             r1 = min(R, r0 + ROW_CHUNK)
             dyp = split_bf16(dy[r0:r1], planes=3 if need_x else 2)
@@ -207,8 +211,8 @@ class _LinearFunction(torch.autograd.Function):
                 # the cross products down to 2^-16 (error about 1e-5 of a term, averaged over the rows)
                 xp = split_bf16(x[r0:r1], planes=2)
                 k_splits = gemm_splits(N, I, r1 - r0, dWq.shape[0])
-                gemm(dyp[:2], xp, a_mn=True, b_mn=True, pairs=PAIRS_FAST, split_k=k_splits, out=dWq, accumulate=True,
-                     reduce_splits=False)
+                gemm(dyp[:2], xp, a_mn=True, b_mn=True, pairs=PAIRS_FAST, split_k=k_splits, out=dWq,
+                     accumulate=(r0 > 0 or first_splits != splits), reduce_splits=False)
             if need_x:
                 # dx = dy @ fq(W): W rows are the contraction index (MN-major B)
                 if ctx.weight_bits <= 8:
