@@ -349,13 +349,20 @@ def run_c5_record(dev, rank, world, flush, sync_all, max_over_ranks, peaks):
         rec["gpu_launches_per_step"] = (_lib.launch_count() - n0) / 4
         rec["ms_per_step"] = sum(ms) / len(ms)
         rec["seq_steps_per_s"] = cfg["T"] * cfg["B"] / (rec["ms_per_step"] * 1e-3)
-        flats = ([wl.bucket.flat] if wl.bucket is not None else
-                 [b.flat for b in wl.reducer.buckets] if wl.reducer is not None else [])
-        if flats and all(f is not None for f in flats):
-            # the collective alone (both buckets back to back when the step overlaps them with the backward)
-            ar = max_over_ranks(timed_loop(lambda: [dist.all_reduce(f) for f in flats], 5, 2, flush, sync_all))
+        # the collective alone (both buckets back to back when the step overlaps them with the backward);
+        # it sums in place, so the gradients are garbage afterwards: they are dropped just below
+        if wl.reducer is not None:
+            bks = wl.reducer.buckets
+            nbytes = sum(p.grad.numel() for b in bks for p in b.params if p.grad is not None) * 4
+            ar = max_over_ranks(timed_loop(lambda: [b.all_reduce_in_place() for b in bks], 5, 2, flush, sync_all))
+        elif wl.bucket is not None:
+            nbytes = wl.bucket.flat.numel() * 4
+            ar = max_over_ranks(timed_loop(lambda: dist.all_reduce(wl.bucket.flat), 5, 2, flush, sync_all))
+        else:
+            ar = None
+        if ar is not None:
             rec["allreduce_ms"] = statistics.median(ar)
-            rec["allreduce_bytes"] = sum(f.numel() for f in flats) * 4
+            rec["allreduce_bytes"] = nbytes
             rec["allreduce_overlapped_with_backward"] = wl.reducer is not None
         if wl.reducer is not None:
             wl.reducer.remove()

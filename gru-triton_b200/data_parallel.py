@@ -85,6 +85,17 @@ class GradBucket:
         """Write the reduced bucket back into ``.grad`` (after an async reduce completes)."""
         self.unpack()
 
+    def all_reduce_in_place(self, group=None) -> None:
+        """Sum the gradients of all ranks where they lie: one coalesced collective over the ``.grad``
+        tensors themselves (the backend groups them into one launch), no flat copy in or out.
+        Every rank must hold a gradient for the same parameters."""
+        grads = [p.grad for p in self.params if p.grad is not None]
+        if not grads:
+            return
+        with dist._coalescing_manager(group=group):
+            for g in grads:
+                dist.all_reduce(g, op=dist.ReduceOp.SUM, group=group)
+
 
 class OverlappedReducer:
     """All-reduce of several gradient buckets, each started the moment its last gradient exists.
@@ -93,13 +104,17 @@ class OverlappedReducer:
     post-accumulate hook on every parameter counts a bucket's finished gradients; the last one
     launches pack -> all-reduce -> unpack of that bucket on a side CUDA stream that first waits for
     the producing stream, so the collective overlaps whatever the backward pass still has to do.
+    By default a bucket is reduced in place (one coalesced collective over its ``.grad`` tensors);
+    with ``in_place=False``, or when a parameter of the bucket has no gradient, through the flat
+    copy of ``GradBucket``.
     ``finish()`` reduces the buckets whose hooks never fired (parameters without a gradient), makes
     the current stream wait for the side stream and re-arms the counters.  Everything is a stream
     operation: a step using it can be captured in a CUDA graph (the side stream becomes a parallel
     branch of the graph).  On CPU tensors (gloo) the reductions run in place, in the same order."""
 
-    def __init__(self, buckets: Sequence[Sequence[torch.Tensor]], group=None):
+    def __init__(self, buckets: Sequence[Sequence[torch.Tensor]], group=None, in_place: bool = True):
         self.group = group
+        self.in_place = in_place          # coalesced all-reduce of the .grad tensors; else flat buckets
         self.buckets = [GradBucket(list(ps)) for ps in buckets if len(ps)]
         self._done = [0] * len(self.buckets)
         self._launched = [False] * len(self.buckets)
@@ -124,7 +139,13 @@ class OverlappedReducer:
                 self._stream = torch.cuda.Stream(device=b.params[0].device)
             self._stream.wait_stream(torch.cuda.current_stream(b.params[0].device))
             with torch.cuda.stream(self._stream):
-                b.all_reduce(group=self.group)
+                self._reduce(b)
+        else:
+            self._reduce(b)
+
+    def _reduce(self, b: GradBucket) -> None:
+        if self.in_place and all(p.grad is not None for p in b.params):
+            b.all_reduce_in_place(group=self.group)
         else:
             b.all_reduce(group=self.group)
 

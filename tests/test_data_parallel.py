@@ -49,15 +49,16 @@ def _worker(rank, world, port, out_path):
     # the same step with two buckets, each reduced from the hook of its last gradient
     buckets = hidden_then_input_buckets(layer)
     assert len(buckets[0]) and len(buckets[1]) and len(buckets[0]) + len(buckets[1]) == len(params)
-    red = OverlappedReducer(buckets)
-    for _ in range(2):                                  # twice: the counters re-arm
-        layer.zero_grad(set_to_none=True)
-        out, _ = layer(shard_batch(x, rank, world, 1), shard_batch(h0, rank, world, 0))
-        out.sum().backward()
-        red.finish()
-        for a, p in zip(one_bucket, params):
-            assert torch.equal(a, p.grad)
-    red.remove()
+    for in_place in (True, False):                      # coalesced in-place collective / flat buckets
+        red = OverlappedReducer(buckets, in_place=in_place)
+        for _ in range(2):                              # twice: the counters re-arm
+            layer.zero_grad(set_to_none=True)
+            out, _ = layer(shard_batch(x, rank, world, 1), shard_batch(h0, rank, world, 0))
+            out.sum().backward()
+            red.finish()
+            for a, p in zip(one_bucket, params):
+                assert torch.equal(a, p.grad)
+        red.remove()
     if rank == 0:
         torch.save(one_bucket, out_path)
     dist.barrier()
