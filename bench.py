@@ -211,13 +211,13 @@ class DeviceWorkload:
         if self.reducer is not None:
             self.reducer.finish()                 # buckets already in flight on the side stream: join them
         elif self.bucket is not None and self.collective_in_graph:
-            self.bucket.all_reduce()              # one flat NCCL all-reduce, gradients written back
+            self.bucket.all_reduce_in_place()     # one coalesced NCCL all-reduce over the .grad tensors
         return loss
 
     def step(self, x, h0):
         r = self.graphed(x, h0) if self.graphed is not None else self._body(x, h0)
         if self.bucket is not None and not self.collective_in_graph:
-            self.bucket.all_reduce()
+            self.bucket.all_reduce_in_place()
         return r
 
     def scan_only_forward(self):
@@ -356,8 +356,8 @@ def run_c5_record(dev, rank, world, flush, sync_all, max_over_ranks, peaks):
             nbytes = sum(p.grad.numel() for b in bks for p in b.params if p.grad is not None) * 4
             ar = max_over_ranks(timed_loop(lambda: [b.all_reduce_in_place() for b in bks], 5, 2, flush, sync_all))
         elif wl.bucket is not None:
-            nbytes = wl.bucket.flat.numel() * 4
-            ar = max_over_ranks(timed_loop(lambda: dist.all_reduce(wl.bucket.flat), 5, 2, flush, sync_all))
+            nbytes = sum(p.grad.numel() for p in wl.bucket.params if p.grad is not None) * 4
+            ar = max_over_ranks(timed_loop(wl.bucket.all_reduce_in_place, 5, 2, flush, sync_all))
         else:
             ar = None
         if ar is not None:
