@@ -943,10 +943,19 @@ bool choose_block_config(bool fwd, int B, int Hb, int nb, BlockScanConfig* out) 
   bool found = false;
   const int bts[7] = {1, 2, 3, 4, 5, 6, 8};
   const int cs[5] = {1, 2, 4, 8, 16};
-  for (int ci = 0; ci < 5; ++ci) {
+  // Every cluster size is tried with the exact slice width ceil(Hb / C) and, when that is no multiple
+  // of 4, with the width rounded up to one (the last ranks then own fewer units or none): the
+  // streamed-weight form and the float4 exchange need Hc % 4 == 0, and widths such as Hb = 520 or
+  // 1000 have no cluster size that gives it exactly.
+  for (int cv = 0; cv < 10; ++cv) {
+    const int ci = cv >> 1;
     const int C = cs[ci];
     if (C > 1 && Hb / C < 8) continue;                 // slices thinner than 8 units: not worth a barrier
-    const int Hc = cdiv(Hb, C);
+    int Hc = cdiv(Hb, C);
+    if (cv & 1) {
+      if (C == 1 || Hc % 4 == 0) continue;             // nothing to round
+      Hc = round_up(Hc, 4);
+    }
     const int Hc4 = round_up(Hc, 4);
     const int HbP = C * Hc;
     const int Hb4 = round_up(HbP, 4);

@@ -42,7 +42,7 @@ struct BlockScanConfig {
 
 // Row length of the transposed weight copy for a block of width Hb (upper bound over all
 // cluster sizes; the forward reads 4 units at a time and may run past the last owned unit).
-inline int transposed_row_bound(int Hb) { return Hb + 24; }
+inline int transposed_row_bound(int Hb) { return Hb + 72; }     // C * round_up(ceil(Hb / C), 4) + 4 + 4, C <= 16
 
 bool choose_block_config(bool fwd, int B, int Hb, int nb, BlockScanConfig* out);
 int launch_block_scan(bool fwd, const BlockScanConfig& c, BlockScanArgs args, int nb, cudaStream_t st);

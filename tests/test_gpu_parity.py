@@ -140,10 +140,12 @@ def test_butterfly_alternate_kernels(T, B, H, extra, quant):
 
 @pytest.mark.parametrize("quant", [None, Q8, Q8_ASYM], ids=["fp32", "q8", "q8asym"])
 @pytest.mark.parametrize("T,B,H,h0_gain", [(8, 1, 256, 1.0), (20, 16, 256, 1.0), (33, 17, 512, 1.0), (9, 112, 512, 1.0),
-                                           (12, 5, 512, 3.0)])
+                                           (12, 5, 512, 3.0), (37, 29, 136, 1.0), (41, 27, 520, 1.0), (6, 3, 1000, 1.0), (5, 9, 200, 1.0)])
 def test_dense_small_batch_cluster_shapes(T, B, H, h0_gain, quant):
-    """H = 256 / 512 at small batch (16-CTA clusters, one and several clusters, a ragged last batch
-    tile, |h0| above 1): forward and backward against the oracle; no bounded wait gave up."""
+    """Small-batch dense shapes of the cluster kernels (one and several clusters, a ragged last batch
+    tile, |h0| above 1) and, in the last two, T*B >= 1024 rows that are no multiple of a k-block with
+    H % 8 == 0: the weight gradient then runs as one tensor-core product with a ragged contraction
+    tail.  Forward and backward against the oracle; no bounded wait gave up."""
     from gru_triton_b200 import _lib
     fwd, bwd, _ = _mods()["dense"]
     gi, h0, W, bh, dout = orc.make_problem("dense", T, B, H, seed=3 * T + B + H)
