@@ -1,5 +1,5 @@
 // Blackwell tensor-core plumbing shared by the tcgen05 kernels (sm_100a): mbarrier, TMA tile
-// loads (no multicast form anywhere), tensor-memory allocation, UMMA descriptors, tcgen05.mma /
+// loads (each CTA fetches its own tiles), tensor-memory allocation, UMMA descriptors, tcgen05.mma /
 // commit / ld wrappers, and bounded waits.
 //
 // Waits: every mbarrier wait polls try_wait against a clock64() budget.  A wait that runs out
