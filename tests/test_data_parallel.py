@@ -87,3 +87,21 @@ def test_two_rank_gloo_sharded_grads_match_full_batch():
     out.sum().backward()
     for g, p in zip(got, layer.parameters()):
         assert (g - p.grad).abs().max().item() < 1e-5
+
+
+def test_bucket_split_follows_the_backward_order():
+    """hidden_then_input_buckets: the hidden path's parameters (finished by the scan backward) first,
+    the input projection's second, for every hidden kind; nothing lost, nothing twice."""
+    from gru_triton_b200 import GRULayer, QuantizerConfig, QuantRecipe, StructureConfig
+    from gru_triton_b200.data_parallel import hidden_then_input_buckets
+    rec = QuantRecipe(weight=QuantizerConfig(bits=32, axis=0), input_act=QuantizerConfig(bits=32),
+                      hidden=QuantizerConfig(bits=32))
+    for st in (None, StructureConfig(kind="diagonal"), StructureConfig(kind="monarch", nblocks=4),
+               StructureConfig(kind="butterfly")):
+        layer = GRULayer(16, 16, rec, gate_layout="fused", structure_hidden=st)
+        names = {id(p): n for n, p in layer.named_parameters()}
+        hidden, rest = hidden_then_input_buckets(layer)
+        assert len(hidden) == 6 and len(rest) == 6
+        assert {id(p) for p in hidden} | {id(p) for p in rest} == set(names)
+        assert all(("_h" in names[id(p)]) or ("struct_Wh" in names[id(p)]) for p in hidden)
+        assert all(("W_i" in names[id(p)]) or ("b_i" in names[id(p)]) for p in rest)
