@@ -62,6 +62,8 @@ int allow_dynamic_smem(const void* kernel, size_t bytes) {
 
 __global__ void reduce_partials_kernel(const float* __restrict__ src, int nparts, size_t row_stride, size_t n,
                                        float* __restrict__ dst) {
+  pdl_launch_dependents();
+  pdl_wait();
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   float s = src[i];
@@ -72,7 +74,7 @@ __global__ void reduce_partials_kernel(const float* __restrict__ src, int nparts
 void launch_reduce_partials(const float* src, int nparts, size_t row_stride, size_t n, float* dst,
                             cudaStream_t st) {
   const unsigned grid = (unsigned)((n + 255) / 256);
-  reduce_partials_kernel<<<grid, 256, 0, st>>>(src, nparts, row_stride, n, dst);
+  launch_pdl(reduce_partials_kernel, dim3(grid), dim3(256), 0, st, src, nparts, row_stride, n, dst);
   note_launch();
 }
 

@@ -314,6 +314,8 @@ __global__ void __launch_bounds__(256)
 bias_grads_kernel(const float* __restrict__ dgi, const float* __restrict__ S, float* __restrict__ dst,
                   int TB, int H, int rows_per_split) {
   __shared__ float red[8][32];
+  pdl_launch_dependents();
+  pdl_wait();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int col = blockIdx.x * 32 + lane;                  // in [0, 3H)
   const int r_begin = blockIdx.y * rows_per_split;
@@ -389,7 +391,7 @@ int launch_bias_grads(const float* dgi, const float* S, float* partial, float* d
   int nsb, rpsb;
   bg_splits(T, B, &nsb, &rpsb);
   dim3 gridb(cdiv(3 * H, 32), nsb);
-  bias_grads_kernel<<<gridb, 256, 0, st>>>(dgi, S, partial, T * B, H, rpsb);
+  launch_pdl(bias_grads_kernel, gridb, dim3(256), 0, st, dgi, S, partial, T * B, H, rpsb);
   note_launch();
   int rc = check_launch("bias_grads_kernel");
   if (rc) return rc;

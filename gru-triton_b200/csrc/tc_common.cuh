@@ -160,36 +160,6 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
-// ---- programmatic dependent launch ---------------------------------------------------------------
-// The per-step kernels of a scan form a chain in one stream; each is launched with the
-// programmatic-stream-serialization attribute, lets its successor be scheduled as soon as every CTA
-// of it has started (launch_dependents) and waits for its predecessor's completion and memory
-// flush (wait) only after its own prologue -- barrier initialisation, tensor-memory allocation and
-// loads of operands no kernel of the chain writes.  Both instructions do nothing in a kernel that
-// was launched without the attribute.
-__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-
-// ---- host side ---------------------------------------------------------------------------------
-#ifndef B200GRU_NO_PDL
-#define B200GRU_PDL_ALLOWED 1
-#else
-#define B200GRU_PDL_ALLOWED 0
-#endif
-// Launch with the programmatic-stream-serialization attribute (the kernel must call pdl_wait()
-// before it touches anything an earlier kernel of the stream produces or still reads).
-template <typename... KArgs, typename... Args>
-inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
-                              Args&&... args) {
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
-  cudaLaunchAttribute at[1];
-  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  at[0].val.programmaticStreamSerializationAllowed = B200GRU_PDL_ALLOWED;
-  cfg.attrs = at; cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
-}
-
 // 3-D tiled tensor map (dims innermost first), 128-byte swizzle, zero fill out of bounds.
 // Returns B200GRU_OK or an error status; looks the driver's encoder up on first use.
 int make_tensor_map_3d(CUtensorMap* map, CUtensorMapDataType dtype, const void* base, unsigned long long d0,

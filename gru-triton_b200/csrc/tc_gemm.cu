@@ -337,6 +337,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 __global__ void __launch_bounds__(256)
 split_planes_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, size_t n4, size_t plane_stride,
                     int planes, const float* __restrict__ col_scale, int ncols) {
+  pdl_launch_dependents();
+  pdl_wait();
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n4) return;
   float4 v = __ldcs(reinterpret_cast<const float4*>(src) + i);
@@ -369,6 +371,8 @@ split_planes_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ d
 __global__ void __launch_bounds__(256)
 split_rows_f16_kernel(const float* __restrict__ src, __half* __restrict__ dst, int rows, int cols, size_t plane_stride,
                       float* __restrict__ inv_scale) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (row >= rows) return;
@@ -623,8 +627,8 @@ int launch_split_planes(const float* src, void* dst, size_t n, size_t plane_stri
   if (!aligned16(src) || (reinterpret_cast<uintptr_t>(dst) & 7u) || (plane_stride & 3)) return B200GRU_INVALID_ARGUMENT;
   const size_t n4 = n / 4;
   if (n4 == 0) return B200GRU_OK;
-  split_planes_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, st>>>(src, static_cast<__nv_bfloat16*>(dst), n4,
-                                                                    plane_stride, planes, col_scale, ncols);
+  launch_pdl(split_planes_kernel, dim3((unsigned)((n4 + 255) / 256)), dim3(256), 0, st, src,
+             static_cast<__nv_bfloat16*>(dst), n4, plane_stride, planes, col_scale, ncols);
   note_launch();
   return check_launch("split_planes_kernel");
 }
@@ -636,8 +640,8 @@ int launch_split_rows_f16(const float* src, void* dst, int rows, int cols, size_
     return B200GRU_INVALID_ARGUMENT;
   if (!aligned16(src) || (reinterpret_cast<uintptr_t>(dst) & 7u)) return B200GRU_INVALID_ARGUMENT;
   if (rows == 0) return B200GRU_OK;
-  split_rows_f16_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(src, static_cast<__half*>(dst), rows, cols,
-                                                                    plane_stride, inv_scale);
+  launch_pdl(split_rows_f16_kernel, dim3((unsigned)((rows + 7) / 8)), dim3(256), 0, st, src, static_cast<__half*>(dst),
+             rows, cols, plane_stride, inv_scale);
   note_launch();
   return check_launch("split_rows_f16_kernel");
 }

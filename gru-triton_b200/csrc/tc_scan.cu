@@ -123,6 +123,8 @@ h0_operand_kernel(const float* __restrict__ h0, void* op, size_t plane_stride, i
 
 __global__ void __launch_bounds__(256)
 gate_fwd_kernel(const FwdStepArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int H4 = a.H >> 2;
   const int idx = blockIdx.x * 256 + threadIdx.x;
   if (idx >= a.B * H4) return;
@@ -449,7 +451,7 @@ int launch_tc_dense_forward(const float* gi, const float* h0, const TcWeights& w
     a.h_prev = (t == 0) ? h0 : out + (size_t)(t - 1) * B * H;
     a.out_t = out + (size_t)t * B * H;
     a.op_next = (t + 1 < T) ? op[(t + 1) & 1] : nullptr;
-    gate_fwd_kernel<<<cdiv(n4, 256), 256, 0, st>>>(a);
+    launch_pdl(gate_fwd_kernel, dim3(cdiv(n4, 256)), dim3(256), 0, st, a);
     note_launch();
   }
   return check_launch("gate_fwd_kernel");
@@ -577,6 +579,8 @@ struct WgOperandArgs {
 
 __global__ void __launch_bounds__(256)
 wgrad_operands_kernel(const WgOperandArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int H4 = a.H >> 2;
   const size_t idx = (size_t)blockIdx.x * 256 + threadIdx.x;
   if (idx >= a.rows * H4) return;
@@ -661,7 +665,7 @@ int launch_tc_weight_grads(const float* dgi, const float* S, const float* h0, co
   a.dgi = dgi; a.r = S; a.h0 = h0; a.out = out; a.dgh_op = dgh_op; a.h_op = h_op;
   a.rows = rows; a.B = B; a.H = H; a.h_codes = h_codes ? 1 : 0; a.qin = qin;
   const size_t n4 = rows * (H / 4);
-  wgrad_operands_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, st>>>(a);
+  launch_pdl(wgrad_operands_kernel, dim3((unsigned)((n4 + 255) / 256)), dim3(256), 0, st, a);
   note_launch();
   int rc = check_launch("wgrad_operands_kernel");
   if (rc) return rc;

@@ -142,6 +142,8 @@ __global__ void __launch_bounds__(256)
 column_sums_kernel(const float* __restrict__ src, size_t rows, int cols, size_t rows_per_slice,
                    float* __restrict__ partial) {
   __shared__ float red[4][64];
+  pdl_launch_dependents();
+  pdl_wait();
   const int c = blockIdx.x * 64 + (threadIdx.x & 63);
   const int grp = threadIdx.x >> 6;
   const size_t r0 = (size_t)blockIdx.y * rows_per_slice;
@@ -161,6 +163,8 @@ __global__ void __launch_bounds__(256)
 column_sums4_kernel(const float* __restrict__ src, size_t rows, int cols, size_t rows_per_slice,
                     float* __restrict__ partial) {
   __shared__ float4 red[4][64];
+  pdl_launch_dependents();
+  pdl_wait();
   const int c = (blockIdx.x * 64 + (threadIdx.x & 63)) * 4;
   const int grp = threadIdx.x >> 6;
   const size_t r0 = (size_t)blockIdx.y * rows_per_slice;
@@ -224,9 +228,9 @@ int launch_column_sums(const float* src, size_t rows, int cols, float* dst, floa
   const size_t rps = (rows + slices - 1) / slices;
   const int used = (int)((rows + rps - 1) / rps);
   if (cols % 4 == 0 && (reinterpret_cast<uintptr_t>(src) & 15u) == 0)
-    column_sums4_kernel<<<dim3(cdiv(cols, 256), used), 256, 0, st>>>(src, rows, cols, rps, scratch);
+    launch_pdl(column_sums4_kernel, dim3(cdiv(cols, 256), used), dim3(256), 0, st, src, rows, cols, rps, scratch);
   else
-    column_sums_kernel<<<dim3(cdiv(cols, 64), used), 256, 0, st>>>(src, rows, cols, rps, scratch);
+    launch_pdl(column_sums_kernel, dim3(cdiv(cols, 64), used), dim3(256), 0, st, src, rows, cols, rps, scratch);
   note_launch();
   launch_reduce_partials(scratch, used, (size_t)cols, (size_t)cols, dst, st);
   return check_launch("column_sums_kernel");
