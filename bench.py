@@ -168,7 +168,7 @@ class DeviceWorkload:
         self.bucket = self.reducer = None
         if world > 1 and cfg["train"]:
             if overlap:
-                self.reducer = OverlappedReducer(hidden_then_input_buckets(self.layer))
+                self.reducer = OverlappedReducer(hidden_then_input_buckets(self.layer), in_place=not FLAT_BUCKETS)
             else:
                 self.bucket = GradBucket(list(self.layer.parameters()))
         # up to about a thousand batch rows per GPU the step is bound by launch and per-step latency
@@ -312,6 +312,9 @@ def timed_loop(fn, steps, warmup, flush, sync_all):
     return [a.elapsed_time(b) for a, b in evs]
 
 
+FLAT_BUCKETS = False       # set by --buckets
+
+
 def load_peaks():
     ppath = os.path.join(REPO, "MEASURED_PEAKS.json")
     return json.load(open(ppath)) if os.path.exists(ppath) else {}
@@ -356,7 +359,8 @@ def run_c5_record(dev, rank, world, flush, sync_all, max_over_ranks, peaks):
         if wl.reducer is not None:
             bks = wl.reducer.buckets
             nbytes = sum(p.grad.numel() for b in bks for p in b.params if p.grad is not None) * 4
-            ar = max_over_ranks(timed_loop(lambda: [b.all_reduce_in_place() for b in bks], 5, 2, flush, sync_all))
+            ar = max_over_ranks(timed_loop(lambda: [(b.all_reduce() if FLAT_BUCKETS else b.all_reduce_in_place()) for b in bks],
+                                           5, 2, flush, sync_all))
         elif wl.bucket is not None:
             nbytes = sum(p.grad.numel() for p in wl.bucket.params if p.grad is not None) * 4
             ar = max_over_ranks(timed_loop(wl.bucket.all_reduce_in_place, 5, 2, flush, sync_all))
@@ -538,6 +542,11 @@ def run_device(args):
         "clocks": clocks,
         "roofline": roofline,
     }
+    if world > 1:
+        line["collective"] = {"op": "all-reduce (sum) of the weight gradients, NCCL",
+                              "buckets": ("two, overlapped with the backward pass" if args.overlap else "one, after the backward pass")
+                                         + (", flat copies" if FLAT_BUCKETS else ", coalesced in place"),
+                              "NCCL_NVLS_ENABLE": os.environ.get("NCCL_NVLS_ENABLE", "unset")}
     if c5 is not None:
         line["c5"] = c5
     if world == 1 and not args.no_cpu_baseline:
@@ -746,7 +755,12 @@ def main():
                     help="N > 1: one gradient bucket reduced after the backward pass instead of two overlapped ones")
     ap.add_argument("--graph-all", dest="graph", action="store_const", const="all",
                     help="capture the step in a CUDA graph whatever its size (default: small problems only)")
+    ap.add_argument("--buckets", choices=["flat", "in-place"], default="in-place",
+                    help="N > 1: all-reduce each bucket through a flat copy, or as one coalesced collective over "
+                         "the gradient tensors where they lie")
     args = ap.parse_args()
+    global FLAT_BUCKETS
+    FLAT_BUCKETS = args.buckets == "flat"
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     if args.impl == "reference":
         run_reference(args)
