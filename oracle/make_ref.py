@@ -9,7 +9,7 @@ the same install tree directly: ``<reference>/src/gru_qat`` -> ``oracle/_ref/gru
 checker and CPU baseline: by ``tests/``, by ``bench.py``'s ``cpu_baseline`` / ``--impl reference``
 legs, and by ``tests/golden/make_golden_butterfly_gpu.py``.  Nothing in the product imports it.
 
-    python oracle/make_ref.py [reference checkout]     (default: $GRU_QAT_REFERENCE or /root/reference)
+    python oracle/make_ref.py [reference checkout]     (default: $GRU_QAT_REFERENCE, else DEFAULT_CHECKOUT below)
 """
 
 from __future__ import annotations
@@ -20,6 +20,7 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 DEST = os.path.join(HERE, "_ref")
+DEFAULT_CHECKOUT = "/root/reference"
 
 
 def ref_path() -> str:
@@ -33,7 +34,7 @@ def available() -> bool:
 
 def install(checkout: str | None = None, quiet: bool = False) -> bool:
     """Copy the package; returns False (and leaves any earlier install alone) if the checkout is absent."""
-    checkout = checkout or os.environ.get("GRU_QAT_REFERENCE", "/root/reference")
+    checkout = checkout or os.environ.get("GRU_QAT_REFERENCE", DEFAULT_CHECKOUT)
     src = os.path.join(checkout, "src", "gru_qat")
     if not os.path.isfile(os.path.join(src, "__init__.py")):
         if not quiet:
