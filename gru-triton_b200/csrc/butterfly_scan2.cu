@@ -15,11 +15,14 @@
 // Every wait is a bounded poll of an mbarrier; a wait that gives up sets a device flag and the
 // kernel runs to its end (results invalid, flag visible through b200gru_device_status).
 
+#include <cooperative_groups.h>
 #include <type_traits>
 
 #include "butterfly_scan.cuh"
 
 namespace b200gru {
+
+namespace cg = cooperative_groups;
 
 namespace {
 
@@ -506,6 +509,162 @@ bfly_fwd2_kernel(const BflyArgs a) {
   }
 }
 
+// Two-CTA variant of the forward kernel for hidden sizes whose three gates' twiddles miss one CTA's
+// shared memory while two gates' fit (H = 1024): a cluster of two CTAs per batch-row block.  Rank 0
+// keeps the twiddles of gates r and z resident and runs their products, rank 1 those of gate n;
+// after the passes each hands the other the half of its result vectors that the other's gate
+// phase needs (rank 0 owns units [0, H/2), rank 1 units [H/2, H)), both do the gate math of their
+// half and write the new fq_in(h) half into both CTAs' copies.  Two cluster barriers per step; no
+// twiddle leaves shared memory after the first step.  Same pass functions and gate math as the
+// one-CTA kernel, so the results are bit-identical to it.
+// shared memory: as bfly_fwd2_kernel with a resident block of 2 * nstages * half twiddles.
+template <int BT>
+__global__ void __launch_bounds__(NT)
+bfly_fwd2_pair_kernel(const BflyArgs a) {
+  extern __shared__ __align__(128) float smem[];
+  __shared__ BflyPass spass[BFLY_MAX_PASSES];
+  cg::cluster_group cluster = cg::this_cluster();
+  if (threadIdx.x == 0) {
+#pragma unroll
+    for (int i = 0; i < BFLY_MAX_PASSES; ++i) spass[i] = a.passes[i];
+  }
+  __syncthreads();
+  const int H = a.H, Hpad = a.Hpad, half = Hpad >> 1, RSZ = a.RSZ, Hh = H >> 1;
+  const int rank = (int)cluster.block_rank();              // 0: gates r, z; 1: gate n
+  const int row0 = (blockIdx.x >> 1) * BT;
+  const int tid = threadIdx.x;
+  const int nrows = min(BT, a.B - row0);
+  const int g0 = rank == 0 ? 0 : 2, ng = rank == 0 ? 2 : 1;  // own gates
+  const int u0 = rank * Hh;                                  // own units [u0, u0 + Hh)
+
+  const unsigned bar0 = smem_u32(smem);
+  float4* twbuf = reinterpret_cast<float4*>(smem + 8);
+  const size_t tw_f4 = (size_t)2 * a.nstages * half;
+  float* st = smem + 8 + 4 * tw_f4;
+  float* hq = st + 3 * BT * RSZ;
+  float* hraw = hq + BT * RSZ;
+  float* gbuf = hraw + BT * H;
+  float* bias = gbuf + 3 * BT * H;
+  const unsigned gbar = bar0 + 16;
+  float* peer_st = cluster.map_shared_rank(st, rank ^ 1);
+  float* peer_hq = cluster.map_shared_rank(hq, rank ^ 1);
+
+  const size_t gi_step = (size_t)a.B * 3 * H;
+  const size_t out_step = (size_t)a.B * H;
+  const size_t comp = (size_t)a.T * out_step;
+  const unsigned half_bytes = (unsigned)Hh * sizeof(float);
+
+  auto issue_gi = [&](int t) {          // thread 0: the own half of every gate's row
+    mbar_arm(gbar, 3u * nrows * half_bytes);
+    for (int g = 0; g < 3; ++g)
+      for (int b = 0; b < nrows; ++b)
+        bulk_load(smem_u32(gbuf + (g * BT + b) * H + u0),
+                  a.gi + (size_t)t * gi_step + (size_t)(row0 + b) * 3 * H + (size_t)g * H + u0, half_bytes, gbar);
+  };
+
+  if (tid == 0) {
+    mbar_init(gbar);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    issue_gi(0);
+  }
+  {
+    const float4* gtw = reinterpret_cast<const float4*>(a.twp) + (size_t)g0 * a.nstages * half;
+    const int n4 = ng * a.nstages * half;
+    for (int i = tid; i < n4; i += NT) twbuf[i] = gtw[i];
+  }
+  for (int i = tid; i < 3 * H; i += NT) bias[i] = a.bh[i];
+  for (int idx = tid; idx < BT * RSZ; idx += NT) hq[idx] = 0.f;
+  __syncthreads();
+  for (int idx = tid; idx < BT * H; idx += NT) {
+    const int b = idx / H, i = idx - b * H;
+    const int row = row0 + b;
+    float v = 0.f;
+    if (row < a.B)
+      v = (row < a.h0_rows) ? a.h0[(size_t)row * H + i] : a.h0_tail[(size_t)(row - a.h0_rows) * H + i];
+    hraw[idx] = v;
+    hq[b * RSZ + sw(i)] = a.qin.enabled ? fake_quant<true>(v, a.qin) : v;
+  }
+  cluster.sync();            // both CTAs run and hold h_{-1} before anything crosses between them
+
+  float* st_own = st + g0 * BT * RSZ;
+  const int tw_gate_res = a.nstages * half;
+  const int Hh4 = Hh >> 2;
+  bool dead = false;
+
+  PHASE_DECL;
+  for (int t = 0; t < a.T; ++t) {
+    PHASE_START();
+    for (int p = 0; p < a.npasses; ++p) {
+      run_pass2_s<BT, false, true>(spass[p], p == 0 ? hq : st_own, p == 0 ? 0 : BT * RSZ, st_own, BT * RSZ, twbuf,
+                                   tw_gate_res, 0, Hpad, RSZ, a.logn, ng, NT);
+      PHASE_MARK(p < 4 ? p : 4);
+      __syncthreads();
+      PHASE_MARK(5);
+    }
+    // hand the peer's half of the own result vectors over (float4 runs of the swizzled rows)
+    for (int idx = tid; idx < ng * nrows * Hh4; idx += NT) {
+      const int g = idx / (nrows * Hh4), rem = idx - g * (nrows * Hh4);
+      const int b = rem / Hh4, i = (Hh - u0) + (rem - b * Hh4) * 4;      // a unit of the peer's half
+      const int off = ((g0 + g) * BT + b) * RSZ + sw(i);
+      *reinterpret_cast<float4*>(peer_st + off) = *reinterpret_cast<const float4*>(st + off);
+    }
+    PHASE_MARK(6);
+    cluster.sync();
+    PHASE_MARK(7);
+    mbar_wait(gbar, (unsigned)t & 1u, dead);
+    PHASE_MARK(8);
+
+    auto gate_phase = [&](auto vtag) {
+      constexpr int V = decltype(vtag)::value;
+      const int HV = Hh / V;
+      for (int idx = tid; idx < nrows * HV; idx += NT) {
+        const int b = idx / HV, i = u0 + (idx - b * HV) * V;
+        const int row = row0 + b;
+        const int ps = b * RSZ + sw(i);
+        float sr[V], sz[V], sn[V], gr[V], gz[V], gn[V], hv[V], bb[V];
+        ldv<V>(st + 0 * BT * RSZ + ps, sr); ldv<V>(bias + i, bb);
+#pragma unroll
+        for (int v = 0; v < V; ++v) sr[v] += bb[v];
+        ldv<V>(st + 1 * BT * RSZ + ps, sz); ldv<V>(bias + H + i, bb);
+#pragma unroll
+        for (int v = 0; v < V; ++v) sz[v] += bb[v];
+        ldv<V>(st + 2 * BT * RSZ + ps, sn); ldv<V>(bias + 2 * H + i, bb);
+#pragma unroll
+        for (int v = 0; v < V; ++v) sn[v] += bb[v];
+        ldv<V>(gbuf + (0 * BT + b) * H + i, gr);
+        ldv<V>(gbuf + (1 * BT + b) * H + i, gz);
+        ldv<V>(gbuf + (2 * BT + b) * H + i, gn);
+        ldv<V>(hraw + b * H + i, hv);
+        float hn[V], hqv[V], rr[V], zz[V], nn[V];
+#pragma unroll
+        for (int v = 0; v < V; ++v) {
+          const GateOut go = gru_gates(gr[v], gz[v], gn[v], sr[v], sz[v], sn[v], hv[v]);
+          hn[v] = a.qout.enabled ? fake_quant<true>(go.h_raw, a.qout) : go.h_raw;
+          hqv[v] = a.qin.enabled ? fake_quant<true>(hn[v], a.qin) : hn[v];
+          rr[v] = go.r; zz[v] = go.z; nn[v] = go.n;
+        }
+        const size_t o = (size_t)t * out_step + (size_t)row * H + i;
+        if (a.out != nullptr) stv<V, false>(a.out + o, hn);
+        if (a.save != nullptr) {
+          stv<V, true>(a.save + o, rr);
+          stv<V, true>(a.save + comp + o, zz);
+          stv<V, true>(a.save + 2 * comp + o, nn);
+          stv<V, true>(a.save + 3 * comp + o, sn);
+        }
+        stv<V, false>(hraw + b * H + i, hn);
+        stv<V, false>(hq + ps, hqv);
+        stv<V, false>(peer_hq + ps, hqv);
+      }
+    };
+    if (2 * nrows * Hh4 <= NT) gate_phase(std::integral_constant<int, 2>{});
+    else gate_phase(std::integral_constant<int, 4>{});
+    PHASE_MARK(9);
+    cluster.sync();          // both halves of fq_in(h_t) are in both CTAs; gbuf and st are free again
+    PHASE_MARK(10);
+    if (tid == 0 && t + 1 < a.T) issue_gi(t + 1);
+  }
+}
+
 template <int BT, bool TW_SMEM>
 __global__ void __launch_bounds__(NT)
 bfly_bwd2_kernel(const BflyArgs a) {
@@ -891,6 +1050,13 @@ static size_t optin_smem2() {
   return (size_t)v;
 }
 
+static int sm_count2() {
+  int dev = 0, v = 0;
+  cudaGetDevice(&dev);
+  if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+  return v;
+}
+
 static int rsz_of(int Hpad) { return (Hpad + (Hpad >> 3) + 3) & ~3; }
 
 static size_t smem2(bool fwd, int BT, int H, int Hpad, int nstages, int mode) {
@@ -941,6 +1107,26 @@ int bfly2_launch_forward(BflyArgs a, int want_bt, cudaStream_t st) {
   int BT, mode; size_t smem;
   if (!plan2(true, a, want_bt, &BT, &mode, &smem)) return -1;
   a.tw_mode = mode; a.RSZ = rsz_of(a.Hpad);
+  if (mode != 1 && a.H % 8 == 0 && 2 * a.B <= sm_count2()) {
+    // three gates' twiddles do not fit one CTA: a pair of CTAs per row if two gates' do and all pairs
+    // run at once (with more rows the one-CTA kernel with several rows per CTA uses the GPU better)
+    const size_t pair_smem = 32 + (size_t)2 * a.nstages * (a.Hpad / 2) * 16 +
+                             ((size_t)4 * a.RSZ + (size_t)4 * a.H + (size_t)3 * a.H) * sizeof(float);
+    if (pair_smem <= optin_smem2()) {
+      int rc = set_smem2(bfly_fwd2_pair_kernel<1>, pair_smem);
+      if (rc) return rc;
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(2u * (unsigned)a.B); cfg.blockDim = dim3(NT); cfg.dynamicSmemBytes = pair_smem; cfg.stream = st;
+      cudaLaunchAttribute at[1];
+      at[0].id = cudaLaunchAttributeClusterDimension;
+      at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+      cfg.attrs = at; cfg.numAttrs = 1;
+      a.tw_mode = 1;
+      cudaLaunchKernelEx(&cfg, bfly_fwd2_pair_kernel<1>, a);
+      note_launch();
+      return check_launch("bfly_fwd2_pair_kernel");
+    }
+  }
   const unsigned grid = (unsigned)cdiv(a.B, BT);
   int rc = 0;
   switch (BT) {
