@@ -441,6 +441,32 @@ def test_baseline_config_shapes_forward_backward():
         check_backward(kind, sub, gi[:, :bsub], h0[:bsub], W, bh, out[:, :bsub], dout[:, :bsub], quant)
 
 
+@pytest.mark.parametrize("T,B,H,quant", [(5, 3, 1000, Q8), (7, 2, 1024, None), (3, 74, 1024, Q8_ASYM), (6, 1, 1016, None)])
+def test_butterfly_two_cta_forward(T, B, H, quant):
+    """H around 1024 with at most 74 rows runs the forward as a pair of CTAs per row (gates r, z in one,
+    n in the other, halves exchanged through distributed shared memory): parity with the oracle,
+    bit-identity with the one-CTA kernel (the same rows inside a batch too large for pairs), and the
+    backward without saved activations, whose gate recompute runs the same forward kernel."""
+    fwd, bwd, _ = _mods()["butterfly"]
+    gi, h0, W, bh, dout = orc.make_problem("butterfly", T, B, H, seed=11, h0_scale=0.3)
+    kw = dict(h_in_quant=quant[0], h_out_quant=quant[1]) if quant else {}
+    d = _cuda(gi, h0, W, bh, dout)
+    out = fwd(*d[:4], **kw)
+    bsub = min(B, 3)
+    check_forward("butterfly", out[:, :bsub], gi[:, :bsub], h0[:bsub], W, bh, quant)
+    big = 80                                                 # 2 * 80 CTAs exceed the SM count: one CTA per row block
+    reps = (big + B - 1) // B
+    gi_big = d[0].repeat(1, reps, 1)[:, :big].contiguous()
+    h0_big = d[1].repeat(reps, 1)[:big].contiguous()
+    out_big = fwd(gi_big, h0_big, d[2], d[3], **kw)
+    assert torch.equal(out_big[:, :B], out)
+    grads = bwd(*d[:4], out, d[4], **kw)                     # no `save`: recomputes the gates
+    sub = [g[:, :bsub] if g.dim() == 3 else g for g in grads[:1]] + [grads[1][:bsub]]
+    ref = orc.scan_backward("butterfly", gi[:, :bsub], h0[:bsub], W, bh, out[:, :bsub].cpu(), dout[:, :bsub],
+                            *(quant if quant else (None, None)))
+    assert rel_err(sub[0].cpu(), ref[0]) <= GRAD_TOL and rel_err(sub[1].cpu(), ref[1]) <= GRAD_TOL
+
+
 def test_baseline_config5_shard_shape():
     """C5 as one of eight GPUs sees it (B=512, H=1024, int8 weights and hidden state), T cut to 8:
     the full launch runs on the device, the oracle checks a slice of the independent batch rows
