@@ -591,7 +591,12 @@ bfly_fwd2_pair_kernel(const BflyArgs a) {
   const int Hh4 = Hh >> 2;
   bool dead = false;
 
+#if defined(B200GRU_PHASE_TIMING) && defined(B200GRU_PHASE_CTA)
+  long long ph_last = 0;
+  const bool ph_on = (blockIdx.x == B200GRU_PHASE_CTA && threadIdx.x == 0);     // time the other rank of the pair
+#else
   PHASE_DECL;
+#endif
   for (int t = 0; t < a.T; ++t) {
     PHASE_START();
     for (int p = 0; p < a.npasses; ++p) {
@@ -1121,10 +1126,13 @@ int bfly2_launch_forward(BflyArgs a, int want_bt, cudaStream_t st) {
       at[0].id = cudaLaunchAttributeClusterDimension;
       at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
       cfg.attrs = at; cfg.numAttrs = 1;
-      a.tw_mode = 1;
-      cudaLaunchKernelEx(&cfg, bfly_fwd2_pair_kernel<1>, a);
-      note_launch();
-      return check_launch("bfly_fwd2_pair_kernel");
+      BflyArgs pa = a;
+      pa.tw_mode = 1;
+      if (cudaLaunchKernelEx(&cfg, bfly_fwd2_pair_kernel<1>, pa) == cudaSuccess) {
+        note_launch();
+        return check_launch("bfly_fwd2_pair_kernel");
+      }
+      cudaGetLastError();        // no cluster launch on this device / partition: the one-CTA kernel below
     }
   }
   const unsigned grid = (unsigned)cdiv(a.B, BT);
