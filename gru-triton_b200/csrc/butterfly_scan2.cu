@@ -58,6 +58,27 @@ __device__ __forceinline__ void mbar_wait(unsigned bar, unsigned parity, bool& d
 
 __device__ __forceinline__ int sw(int i) { return i + ((i >> 6) << 3); }
 
+// ---- distributed shared memory: stores into the peer CTA that count their bytes on its mbarrier ----
+__device__ __forceinline__ unsigned map_to_rank(unsigned addr, unsigned rank) {
+  unsigned r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void st_async_v4(unsigned raddr, float4 v, unsigned rbar) {
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.b32 [%0], {%1, %2, %3, %4}, [%5];"
+               ::"r"(raddr), "r"(__float_as_uint(v.x)), "r"(__float_as_uint(v.y)), "r"(__float_as_uint(v.z)),
+                 "r"(__float_as_uint(v.w)), "r"(rbar) : "memory");
+}
+template <int V>
+__device__ __forceinline__ void st_async_v(unsigned raddr, const float (&x)[V], unsigned rbar) {
+  if constexpr (V == 4) {
+    st_async_v4(raddr, make_float4(x[0], x[1], x[2], x[3]), rbar);
+  } else {
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v2.b32 [%0], {%1, %2}, [%3];"
+                 ::"r"(raddr), "r"(__float_as_uint(x[0])), "r"(__float_as_uint(x[1])), "r"(rbar) : "memory");
+  }
+}
+
 // V (2 or 4) adjacent floats as one vector access; STREAM: evict-first store
 template <int V>
 __device__ __forceinline__ void ldv(const float* p, float (&x)[V]) {
@@ -514,8 +535,11 @@ bfly_fwd2_kernel(const BflyArgs a) {
 // keeps the twiddles of gates r and z resident and runs their products, rank 1 those of gate n;
 // after the passes each hands the other the half of its result vectors that the other's gate
 // phase needs (rank 0 owns units [0, H/2), rank 1 units [H/2, H)), both do the gate math of their
-// half and write the new fq_in(h) half into both CTAs' copies.  Two cluster barriers per step; no
-// twiddle leaves shared memory after the first step.  Same pass functions and gate math as the
+// half and write the new fq_in(h) half into both CTAs' copies.  Both hand-overs are st.async stores
+// counted on an mbarrier of the receiver (no fence, no cluster barrier inside the time loop: a
+// release at a cluster barrier would wait for the step's global stores); a buffer is only written
+// again after its reader has sent the data the writer needs first.  No twiddle leaves shared
+// memory after the first step.  Same pass functions and gate math as the
 // one-CTA kernel, so the results are bit-identical to it.
 // shared memory: as bfly_fwd2_kernel with a resident block of 2 * nstages * half twiddles.
 template <int BT>
@@ -546,8 +570,14 @@ bfly_fwd2_pair_kernel(const BflyArgs a) {
   float* gbuf = hraw + BT * H;
   float* bias = gbuf + 3 * BT * H;
   const unsigned gbar = bar0 + 16;
-  float* peer_st = cluster.map_shared_rank(st, rank ^ 1);
-  float* peer_hq = cluster.map_shared_rank(hq, rank ^ 1);
+  // the peer's copies and mbarriers, as addresses in the cluster's shared window
+  const unsigned pbar = bar0, hbar = bar0 + 8;             // products / new h of the peer have landed here
+  const unsigned peer_st = map_to_rank(smem_u32(st), (unsigned)(rank ^ 1));
+  const unsigned peer_hq = map_to_rank(smem_u32(hq), (unsigned)(rank ^ 1));
+  const unsigned peer_pbar = map_to_rank(pbar, (unsigned)(rank ^ 1));
+  const unsigned peer_hbar = map_to_rank(hbar, (unsigned)(rank ^ 1));
+  const unsigned recv_p = (unsigned)((3 - ng) * nrows * Hh) * 4u;   // bytes per step: the peer's gates, own half
+  const unsigned recv_h = (unsigned)(nrows * Hh) * 4u;              // the peer's half of fq_in(h_t)
 
   const size_t gi_step = (size_t)a.B * 3 * H;
   const size_t out_step = (size_t)a.B * H;
@@ -563,8 +593,10 @@ bfly_fwd2_pair_kernel(const BflyArgs a) {
   };
 
   if (tid == 0) {
-    mbar_init(gbar);
+    mbar_init(pbar); mbar_init(hbar); mbar_init(gbar);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    mbar_arm(pbar, recv_p);
+    if (a.T > 1) mbar_arm(hbar, recv_h);
     issue_gi(0);
   }
   {
@@ -584,7 +616,7 @@ bfly_fwd2_pair_kernel(const BflyArgs a) {
     hraw[idx] = v;
     hq[b * RSZ + sw(i)] = a.qin.enabled ? fake_quant<true>(v, a.qin) : v;
   }
-  cluster.sync();            // both CTAs run and hold h_{-1} before anything crosses between them
+  cluster.sync();            // both CTAs run, their mbarriers are armed, before anything crosses between them
 
   float* st_own = st + g0 * BT * RSZ;
   const int tw_gate_res = a.nstages * half;
@@ -606,15 +638,19 @@ bfly_fwd2_pair_kernel(const BflyArgs a) {
       __syncthreads();
       PHASE_MARK(5);
     }
-    // hand the peer's half of the own result vectors over (float4 runs of the swizzled rows)
-    for (int idx = tid; idx < ng * nrows * Hh4; idx += NT) {
-      const int g = idx / (nrows * Hh4), rem = idx - g * (nrows * Hh4);
-      const int b = rem / Hh4, i = (Hh - u0) + (rem - b * Hh4) * 4;      // a unit of the peer's half
-      const int off = ((g0 + g) * BT + b) * RSZ + sw(i);
-      *reinterpret_cast<float4*>(peer_st + off) = *reinterpret_cast<const float4*>(st + off);
-    }
+    // hand the peer's half of the own result vectors over (float4 runs of the swizzled rows); the
+    // stores count their bytes on the peer's mbarrier, so nobody fences or meets at a barrier
+    for (int g = 0; g < ng; ++g)
+      for (int b = 0; b < nrows; ++b)
+        for (int j = tid; j < Hh4; j += NT) {               // no division on the chain
+          const int i = (Hh - u0) + j * 4;                  // a unit of the peer's half
+          const int off = ((g0 + g) * BT + b) * RSZ + sw(i);
+          const float4 v = *reinterpret_cast<const float4*>(st + off);
+          st_async_v4(peer_st + 4u * (unsigned)off, v, peer_pbar);
+        }
     PHASE_MARK(6);
-    cluster.sync();
+    mbar_wait(pbar, (unsigned)t & 1u, dead);
+    if (tid == 0 && t + 1 < a.T) mbar_arm(pbar, recv_p);
     PHASE_MARK(7);
     mbar_wait(gbar, (unsigned)t & 1u, dead);
     PHASE_MARK(8);
@@ -622,8 +658,9 @@ bfly_fwd2_pair_kernel(const BflyArgs a) {
     auto gate_phase = [&](auto vtag) {
       constexpr int V = decltype(vtag)::value;
       const int HV = Hh / V;
-      for (int idx = tid; idx < nrows * HV; idx += NT) {
-        const int b = idx / HV, i = u0 + (idx - b * HV) * V;
+      for (int b = 0; b < nrows; ++b)
+      for (int j = tid; j < HV; j += NT) {
+        const int i = u0 + j * V;
         const int row = row0 + b;
         const int ps = b * RSZ + sw(i);
         float sr[V], sz[V], sn[V], gr[V], gz[V], gn[V], hv[V], bb[V];
@@ -658,16 +695,21 @@ bfly_fwd2_pair_kernel(const BflyArgs a) {
         }
         stv<V, false>(hraw + b * H + i, hn);
         stv<V, false>(hq + ps, hqv);
-        stv<V, false>(peer_hq + ps, hqv);
+        if (t + 1 < a.T) st_async_v<V>(peer_hq + 4u * (unsigned)ps, hqv, peer_hbar);
       }
     };
     if (2 * nrows * Hh4 <= NT) gate_phase(std::integral_constant<int, 2>{});
     else gate_phase(std::integral_constant<int, 4>{});
     PHASE_MARK(9);
-    cluster.sync();          // both halves of fq_in(h_t) are in both CTAs; gbuf and st are free again
+    __syncthreads();         // own half of fq_in(h_t) is in place; gbuf and the result vectors are free again
+    if (t + 1 < a.T) {
+      if (tid == 0) issue_gi(t + 1);
+      mbar_wait(hbar, (unsigned)t & 1u, dead);             // the peer's half
+      if (tid == 0 && t + 2 < a.T) mbar_arm(hbar, recv_h);
+    }
     PHASE_MARK(10);
-    if (tid == 0 && t + 1 < a.T) issue_gi(t + 1);
   }
+  cluster.sync();            // nobody leaves while the peer could still address its shared memory
 }
 
 template <int BT, bool TW_SMEM>
