@@ -483,7 +483,7 @@ bfly_fwd2_kernel(const BflyArgs a) {
       constexpr int V = decltype(vtag)::value;
       const int HV = H / V;
       for (int idx = tid; idx < nrows * HV; idx += NT) {
-        const int b = idx / HV, i = (idx - b * HV) * V;
+        const int b = (BT == 1) ? 0 : idx / HV, i = (idx - b * HV) * V;   // one row: no division on the chain
         const int row = row0 + b;
         const int ps = b * RSZ + sw(i);
         float sr[V], sz[V], sn[V], gr[V], gz[V], gn[V], hv[V], bb[V];
@@ -790,7 +790,7 @@ bfly_bwd2_kernel(const BflyArgs a) {
 
     // gate gradients -> st (and zero the padded tail, which the transposed passes dirty)
     for (int idx = tid; idx < nrows * P4g; idx += NT) {
-      const int b = idx / P4g, i = (idx - b * P4g) << 2;
+      const int b = (BT == 1) ? 0 : idx / P4g, i = (idx - b * P4g) << 2;
       const int row = row0 + b;
       const int ps = b * RSZ + sw(i);
       float x0[4] = {0.f, 0.f, 0.f, 0.f}, x1[4] = {0.f, 0.f, 0.f, 0.f}, x2[4] = {0.f, 0.f, 0.f, 0.f};
@@ -853,7 +853,7 @@ bfly_bwd2_kernel(const BflyArgs a) {
     }
 
     for (int idx = tid; idx < nrows * H4g; idx += NT) {
-      const int b = idx / H4g, i = (idx - b * H4g) << 2;
+      const int b = (BT == 1) ? 0 : idx / H4g, i = (idx - b * H4g) << 2;
       const int ps = b * RSZ + sw(i);
       const int e = b * H + i;
       const float4 s0 = *reinterpret_cast<const float4*>(st + 0 * BT * RSZ + ps);
@@ -1045,7 +1045,7 @@ bfly_wgrad2_kernel(const BflyArgs a, float* __restrict__ partial, int rows_per_s
     const int nrows = min(RB, r_end - r0);
 #pragma unroll 4
     for (int idx = tid; idx < RB * P4; idx += WG_NT) {
-      const int b = idx / P4, i = (idx - b * P4) << 2;
+      const int b = idx >> (a.logn - 2), i = (idx & (P4 - 1)) << 2;     // P4 = Hpad / 4, a power of two
       const int tb = r0 + b;
       float4 hv = make_float4(0.f, 0.f, 0.f, 0.f), dv = hv;
       if (b < nrows && i < H) {
