@@ -9,8 +9,9 @@ on the tensor-core GEMM core, the CUDA scan, the weight gradients.  Default (eve
 dense fp32 train step at T=64, B=32 per GPU, I=H=512; with N > 1 each rank runs its own batch
 (weak scaling) and the weight gradients are all-reduced over NCCL through
 ``data_parallel.OverlappedReducer`` (hidden-path bucket, then input-path bucket, each on a side
-stream as soon as the backward pass has produced it; ``--no-overlap``: one ``GradBucket`` at the end).  Metric: sequence-steps/s = T*B*N / step time.  Each line also
-carries a ``c5`` record: config 5 (dense int8 QAT, T=512, H=1024, B=4096 split over the N GPUs),
+stream as soon as the backward pass has produced it, reduced where the gradients lie as one
+coalesced collective; ``--buckets flat``: through a flat copy; ``--no-overlap``: one ``GradBucket``
+at the end).  Metric: sequence-steps/s = T*B*N / step time.  Each line also carries a ``c5`` record: config 5 (dense int8 QAT, T=512, H=1024, B=4096 split over the N GPUs),
 three timed steps.
 
 One JSON line on stdout (rank 0).  ``--impl reference`` times the reference's own CPU code
