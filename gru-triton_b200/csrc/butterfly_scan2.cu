@@ -877,6 +877,199 @@ bfly_bwd2_kernel(const BflyArgs a) {
   }
 }
 
+// Two-CTA variant of the backward kernel, for the same problems as bfly_fwd2_pair_kernel.  Both CTAs
+// of a pair load the step's operands and compute the gate gradients of all units (elementwise, so
+// the full vectors dgh_g exist in both without an exchange); rank 0 stores dgi_r, dgi_z and runs
+// the transposed products of gates r and z from resident twiddles, rank 1 does the same for gate n.
+// After the passes rank 0 sends s_r + s_z and rank 1 s_n (st.async stores counted on an mbarrier of
+// the receiver, into a buffer that alternates with the step), and both form
+// dh = direct + ((s_r + s_z) + s_n) * mask in the order of the one-CTA kernel: bit-identical results.
+template <int BT>
+__global__ void __launch_bounds__(NT)
+bfly_bwd2_pair_kernel(const BflyArgs a) {
+  extern __shared__ __align__(128) float smem[];
+  __shared__ BflyPass spass[BFLY_MAX_PASSES];
+  cg::cluster_group cluster = cg::this_cluster();
+  if (threadIdx.x == 0) {
+#pragma unroll
+    for (int i = 0; i < BFLY_MAX_PASSES; ++i) spass[i] = a.passes[i];
+  }
+  __syncthreads();
+  const int H = a.H, Hpad = a.Hpad, half = Hpad >> 1, RSZ = a.RSZ, H4g = H >> 2, P4g = Hpad >> 2;
+  const int rank = (int)cluster.block_rank();              // 0: gates r, z; 1: gate n
+  const int row0 = (blockIdx.x >> 1) * BT;
+  const int tid = threadIdx.x;
+  const int nrows = min(BT, a.B - row0);
+  const int g0 = rank == 0 ? 0 : 2, ng = rank == 0 ? 2 : 1;
+
+  const unsigned bar0 = smem_u32(smem);
+  float4* twbuf = reinterpret_cast<float4*>(smem + 8);
+  const size_t tw_f4 = (size_t)2 * a.nstages * half;
+  float* st = smem + 8 + 4 * tw_f4;
+  float* pbuf = st + 3 * BT * RSZ;       // [6][BT][H]: dout, r, z, n, gh_n, h_prev
+  float* dhacc = pbuf + 6 * BT * H;
+  float* dhdir = dhacc + BT * H;
+  float* mk = dhdir + BT * H;
+  float* recv = mk + BT * H;             // [2][BT][H]: the peer's partial sum, buffer = step parity
+  const unsigned xbar = bar0, pbar = bar0 + 16;
+  const unsigned peer_recv = map_to_rank(smem_u32(recv), (unsigned)(rank ^ 1));
+  const unsigned peer_xbar = map_to_rank(xbar, (unsigned)(rank ^ 1));
+  const unsigned recv_bytes = (unsigned)(nrows * H) * 4u;
+
+  const size_t gi_step = (size_t)a.B * 3 * H;
+  const size_t out_step = (size_t)a.B * H;
+  const size_t comp = (size_t)a.T * out_step;
+  const unsigned row_bytes = (unsigned)H * sizeof(float);
+
+  auto issue_operands = [&](int t) {    // thread 0
+    mbar_arm(pbar, 6u * nrows * row_bytes);
+    for (int c = 0; c < 6; ++c)
+      for (int b = 0; b < nrows; ++b) {
+        const size_t o = (size_t)t * out_step + (size_t)(row0 + b) * H;
+        const float* src;
+        if (c == 0) src = a.dout + o;
+        else if (c <= 4) src = a.S + (size_t)(c - 1) * comp + o;
+        else src = (t > 0) ? (a.out_c + o - out_step) : (a.h0 + (size_t)(row0 + b) * H);
+        bulk_load(smem_u32(pbuf + (c * BT + b) * H), src, row_bytes, pbar);
+      }
+  };
+
+  if (tid == 0) {
+    mbar_init(xbar); mbar_init(pbar);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    mbar_arm(xbar, recv_bytes);
+    issue_operands(a.T - 1);
+  }
+  {
+    const float4* gtw = reinterpret_cast<const float4*>(a.twp) + (size_t)g0 * a.nstages * half;
+    const int n4 = ng * a.nstages * half;
+    for (int i = tid; i < n4; i += NT) twbuf[i] = gtw[i];
+  }
+  for (int idx = tid; idx < BT * H; idx += NT) dhacc[idx] = 0.f;
+  for (int idx = tid; idx < 3 * BT * RSZ; idx += NT) st[idx] = 0.f;
+  cluster.sync();            // both CTAs run and their mbarriers are armed before anything crosses
+
+  float* st_own = st + g0 * BT * RSZ;
+  const int tw_gate_res = a.nstages * half;
+  bool dead = false;
+
+  for (int t = a.T - 1; t >= 0; --t) {
+    const unsigned par = (unsigned)(a.T - 1 - t) & 1u;
+    mbar_wait(pbar, par, dead);
+
+    // gate gradients of all units; the own gates' dgh go to st (padded tail zeroed: the transposed
+    // passes dirty it), the own gates' dgi to global memory
+    for (int idx = tid; idx < nrows * P4g; idx += NT) {
+      const int b = (BT == 1) ? 0 : idx / P4g, i = (idx - b * P4g) << 2;
+      const int row = row0 + b;
+      const int ps = b * RSZ + sw(i);
+      float x0[4] = {0.f, 0.f, 0.f, 0.f}, x1[4] = {0.f, 0.f, 0.f, 0.f}, x2[4] = {0.f, 0.f, 0.f, 0.f};
+      if (i < H) {
+        const int e = b * H + i;
+        const float4 d4 = *reinterpret_cast<const float4*>(pbuf + 0 * BT * H + e);
+        const float4 r4 = *reinterpret_cast<const float4*>(pbuf + 1 * BT * H + e);
+        const float4 z4 = *reinterpret_cast<const float4*>(pbuf + 2 * BT * H + e);
+        const float4 n4 = *reinterpret_cast<const float4*>(pbuf + 3 * BT * H + e);
+        const float4 g4 = *reinterpret_cast<const float4*>(pbuf + 4 * BT * H + e);
+        const float4 h4 = *reinterpret_cast<const float4*>(pbuf + 5 * BT * H + e);
+        const float4 a4 = *reinterpret_cast<const float4*>(dhacc + e);
+        const float dd[4] = {d4.x, d4.y, d4.z, d4.w}, rr[4] = {r4.x, r4.y, r4.z, r4.w};
+        const float zz[4] = {z4.x, z4.y, z4.z, z4.w}, nn[4] = {n4.x, n4.y, n4.z, n4.w};
+        const float gg[4] = {g4.x, g4.y, g4.z, g4.w}, hh[4] = {h4.x, h4.y, h4.z, h4.w};
+        const float aa[4] = {a4.x, a4.y, a4.z, a4.w};
+        float dir[4], msk[4], dgn[4];
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          float dh = dd[v] + aa[v];
+          if (a.qout.enabled) {
+            const float h_raw = (1.0f - zz[v]) * nn[v] + zz[v] * hh[v];
+            dh = dh * ste_mask<true>(h_raw, a.qout);
+          }
+          const GateGrad q4 = gru_gate_grads(dh, rr[v], zz[v], nn[v], gg[v], hh[v]);
+          dir[v] = q4.dh_direct;
+          msk[v] = a.qin.enabled ? ste_mask<true>(hh[v], a.qin) : 1.0f;
+          x0[v] = q4.dgr; x1[v] = q4.dgz; x2[v] = q4.dghn; dgn[v] = q4.dgn;
+        }
+        *reinterpret_cast<float4*>(dhdir + e) = make_float4(dir[0], dir[1], dir[2], dir[3]);
+        *reinterpret_cast<float4*>(mk + e) = make_float4(msk[0], msk[1], msk[2], msk[3]);
+        float* d = a.dgi + (size_t)t * gi_step + (size_t)row * 3 * H + i;
+        if (rank == 0) {
+          __stcs(reinterpret_cast<float4*>(d), make_float4(x0[0], x0[1], x0[2], x0[3]));
+          __stcs(reinterpret_cast<float4*>(d + H), make_float4(x1[0], x1[1], x1[2], x1[3]));
+        } else {
+          __stcs(reinterpret_cast<float4*>(d + 2 * H), make_float4(dgn[0], dgn[1], dgn[2], dgn[3]));
+        }
+      }
+      if (rank == 0) {
+        *reinterpret_cast<float4*>(st + 0 * BT * RSZ + ps) = make_float4(x0[0], x0[1], x0[2], x0[3]);
+        *reinterpret_cast<float4*>(st + 1 * BT * RSZ + ps) = make_float4(x1[0], x1[1], x1[2], x1[3]);
+      } else {
+        *reinterpret_cast<float4*>(st + 2 * BT * RSZ + ps) = make_float4(x2[0], x2[1], x2[2], x2[3]);
+      }
+    }
+    __syncthreads();
+    if (tid == 0 && t > 0) issue_operands(t - 1);
+
+    for (int p = a.npasses - 1; p >= 0; --p) {
+      run_pass2_s<BT, true, true>(spass[p], st_own, BT * RSZ, st_own, BT * RSZ, twbuf, tw_gate_res, 0, Hpad, RSZ,
+                                  a.logn, ng, NT);
+      __syncthreads();
+    }
+
+    // the own partial sum of every unit goes to the peer's buffer of this step's parity
+    for (int idx = tid; idx < nrows * H4g; idx += NT) {
+      const int b = (BT == 1) ? 0 : idx / H4g, i = (idx - b * H4g) << 2;
+      const int ps = b * RSZ + sw(i);
+      float4 v;
+      if (rank == 0) {
+        const float4 s0 = *reinterpret_cast<const float4*>(st + 0 * BT * RSZ + ps);
+        const float4 s1 = *reinterpret_cast<const float4*>(st + 1 * BT * RSZ + ps);
+        v = make_float4(s0.x + s1.x, s0.y + s1.y, s0.z + s1.z, s0.w + s1.w);
+      } else {
+        v = *reinterpret_cast<const float4*>(st + 2 * BT * RSZ + ps);
+      }
+      st_async_v4(peer_recv + 4u * (unsigned)((par * BT + b) * H + i), v, peer_xbar);
+    }
+    mbar_wait(xbar, par, dead);
+    if (tid == 0 && t > 0) mbar_arm(xbar, recv_bytes);
+
+    const float* rc = recv + par * BT * H;
+    for (int idx = tid; idx < nrows * H4g; idx += NT) {
+      const int b = (BT == 1) ? 0 : idx / H4g, i = (idx - b * H4g) << 2;
+      const int ps = b * RSZ + sw(i);
+      const int e = b * H + i;
+      const float4 pr = *reinterpret_cast<const float4*>(rc + e);
+      float4 s01, s2;
+      if (rank == 0) {
+        const float4 s0 = *reinterpret_cast<const float4*>(st + 0 * BT * RSZ + ps);
+        const float4 s1 = *reinterpret_cast<const float4*>(st + 1 * BT * RSZ + ps);
+        s01 = make_float4(s0.x + s1.x, s0.y + s1.y, s0.z + s1.z, s0.w + s1.w);
+        s2 = pr;
+      } else {
+        s01 = pr;
+        s2 = *reinterpret_cast<const float4*>(st + 2 * BT * RSZ + ps);
+      }
+      const float4 dr = *reinterpret_cast<const float4*>(dhdir + e);
+      const float4 m4 = *reinterpret_cast<const float4*>(mk + e);
+      float4 r;
+      r.x = dr.x + (s01.x + s2.x) * m4.x;
+      r.y = dr.y + (s01.y + s2.y) * m4.y;
+      r.z = dr.z + (s01.z + s2.z) * m4.z;
+      r.w = dr.w + (s01.w + s2.w) * m4.w;
+      *reinterpret_cast<float4*>(dhacc + e) = r;
+    }
+    __syncthreads();
+  }
+
+  if (rank == 0) {
+    for (int idx = tid; idx < nrows * H4g; idx += NT) {
+      const int b = (BT == 1) ? 0 : idx / H4g, i = (idx - b * H4g) << 2;
+      *reinterpret_cast<float4*>(a.dh0 + (size_t)(row0 + b) * H + i) = *reinterpret_cast<const float4*>(dhacc + b * H + i);
+    }
+  }
+  cluster.sync();            // nobody leaves while the peer could still address its shared memory
+}
+
 
 // ---------------------------------------------------------------------------
 // twiddle gradients: dt[g][l][pair][m_new][m_old] = sum over rows (t, b) of d_new[m_new] * old[m_old]
@@ -1200,6 +1393,28 @@ int bfly2_launch_backward(BflyArgs a, int want_bt, cudaStream_t st) {
   int BT, mode; size_t smem;
   if (!plan2(false, a, want_bt, &BT, &mode, &smem)) return -1;
   a.tw_mode = mode; a.RSZ = rsz_of(a.Hpad);
+  if (mode != 1 && a.H % 8 == 0 && 2 * a.B <= sm_count2()) {
+    // as in the forward: a pair of CTAs per row when two gates' twiddles fit one CTA and all pairs run at once
+    const size_t pair_smem = 32 + (size_t)2 * a.nstages * (a.Hpad / 2) * 16 +
+                             ((size_t)3 * a.RSZ + (size_t)11 * a.H) * sizeof(float);
+    if (pair_smem <= optin_smem2()) {
+      int rc = set_smem2(bfly_bwd2_pair_kernel<1>, pair_smem);
+      if (rc) return rc;
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(2u * (unsigned)a.B); cfg.blockDim = dim3(NT); cfg.dynamicSmemBytes = pair_smem; cfg.stream = st;
+      cudaLaunchAttribute at[1];
+      at[0].id = cudaLaunchAttributeClusterDimension;
+      at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+      cfg.attrs = at; cfg.numAttrs = 1;
+      BflyArgs pa = a;
+      pa.tw_mode = 1;
+      if (cudaLaunchKernelEx(&cfg, bfly_bwd2_pair_kernel<1>, pa) == cudaSuccess) {
+        note_launch();
+        return check_launch("bfly_bwd2_pair_kernel");
+      }
+      cudaGetLastError();        // no cluster launch on this device / partition: the one-CTA kernel below
+    }
+  }
   const unsigned grid = (unsigned)cdiv(a.B, BT);
   int rc = 0;
   switch (BT) {

@@ -446,7 +446,8 @@ def test_butterfly_two_cta_forward(T, B, H, quant):
     """H around 1024 with at most 74 rows runs the forward as a pair of CTAs per row (gates r, z in one,
     n in the other, halves exchanged through distributed shared memory): parity with the oracle,
     bit-identity with the one-CTA kernel (the same rows inside a batch too large for pairs), and the
-    backward without saved activations, whose gate recompute runs the same forward kernel."""
+    backward without saved activations, whose gate recompute runs the same forward kernel and whose
+    scan runs as pairs as well (gates r, z in one CTA, n in the other, partial sums exchanged)."""
     fwd, bwd, _ = _mods()["butterfly"]
     gi, h0, W, bh, dout = orc.make_problem("butterfly", T, B, H, seed=11, h0_scale=0.3)
     kw = dict(h_in_quant=quant[0], h_out_quant=quant[1]) if quant else {}
@@ -465,6 +466,10 @@ def test_butterfly_two_cta_forward(T, B, H, quant):
     ref = orc.scan_backward("butterfly", gi[:, :bsub], h0[:bsub], W, bh, out[:, :bsub].cpu(), dout[:, :bsub],
                             *(quant if quant else (None, None)))
     assert rel_err(sub[0].cpu(), ref[0]) <= GRAD_TOL and rel_err(sub[1].cpu(), ref[1]) <= GRAD_TOL
+    # the backward scan runs as pairs too; the same rows inside the large batch take the one-CTA kernel
+    dout_big = d[4].repeat(1, reps, 1)[:, :big].contiguous()
+    grads_big = bwd(gi_big, h0_big, d[2], d[3], out_big, dout_big, **kw)
+    assert torch.equal(grads_big[0][:, :B], grads[0]) and torch.equal(grads_big[1][:B], grads[1])
 
 
 def test_baseline_config5_shard_shape():
