@@ -441,7 +441,8 @@ def test_baseline_config_shapes_forward_backward():
         check_backward(kind, sub, gi[:, :bsub], h0[:bsub], W, bh, out[:, :bsub], dout[:, :bsub], quant)
 
 
-@pytest.mark.parametrize("T,B,H,quant", [(5, 3, 1000, Q8), (7, 2, 1024, None), (3, 74, 1024, Q8_ASYM), (6, 1, 1016, None)])
+@pytest.mark.parametrize("T,B,H,quant", [(5, 3, 1000, Q8), (7, 2, 1024, None), (3, 74, 1024, Q8_ASYM), (6, 1, 1016, None),
+                                          (1, 1, 1024, None), (2, 3, 1024, None)])
 def test_butterfly_two_cta_forward(T, B, H, quant):
     """H around 1024 with at most 74 rows runs the forward as a pair of CTAs per row (gates r, z in one,
     n in the other, halves exchanged through distributed shared memory): parity with the oracle,
